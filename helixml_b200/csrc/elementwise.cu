@@ -1,0 +1,252 @@
+// Memory-bound helpers around the scan: causal depthwise conv + SiLU, RMSNorm (+ residual add),
+// byte-embedding gather, SiLU.  All are single-pass, 128-bit vectorised where the layout allows.
+#include "hx_common.cuh"
+
+namespace hx {
+namespace ew {
+
+template <typename T> struct Vec;  // 16-byte vector of T
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    float v[4];
+    __device__ __forceinline__ void load(const float *p) {
+        const float4 f = *reinterpret_cast<const float4 *>(p);
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    }
+    __device__ __forceinline__ void store(float *p) const {
+        *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    float v[8];
+    __device__ __forceinline__ void load(const __nv_bfloat16 *p) {
+        const uint4 r = *reinterpret_cast<const uint4 *>(p);
+        const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            v[2 * k] = __uint_as_float(w[k] << 16);
+            v[2 * k + 1] = __uint_as_float(w[k] & 0xffff0000u);
+        }
+    }
+    __device__ __forceinline__ void store(__nv_bfloat16 *p) const {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+            w[k] = *reinterpret_cast<const uint32_t *>(&h);
+        }
+        *reinterpret_cast<uint4 *>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+// ---------------------------------------------------------------- conv1d + SiLU
+// Thread = one 16-byte channel group x TB consecutive time steps (sliding window over the taps).
+template <typename T, bool VEC, int TB>
+__global__ void __launch_bounds__(128)
+conv_silu_kernel(const T *x, int64_t xb, int64_t xr, const float *cw, const float *cb, T *u, int64_t ub, int64_t ur,
+                 int L, int D, int K) {
+    constexpr int VN = VEC ? Vec<T>::N : 1;
+    const int g = blockIdx.x * blockDim.x + threadIdx.x;
+    const int d = g * VN;
+    if (d >= D) return;
+    const int t0 = blockIdx.y * TB;
+    const int b = blockIdx.z;
+    float w[VN][4], bias[VN];
+#pragma unroll
+    for (int e = 0; e < VN; ++e) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w[e][j] = 0.f;
+        for (int j = 0; j < K; ++j) w[e][4 - K + j] = cw[(int64_t)(d + e) * K + j];
+        bias[e] = cb ? cb[d + e] : 0.f;
+    }
+    const T *xp = x + b * xb + d;
+    T *up = u + b * ub + d;
+    float win[3][VN];  // x[t-3], x[t-2], x[t-1]
+#pragma unroll
+    for (int j = 0; j < 3; ++j) {
+        const int t = t0 - 3 + j;
+        if (t >= 0) {
+            if constexpr (VEC) {
+                Vec<T> v;
+                v.load(xp + t * xr);
+#pragma unroll
+                for (int e = 0; e < VN; ++e) win[j][e] = v.v[e];
+            } else {
+                win[j][0] = ld_f32(xp + t * xr);
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < VN; ++e) win[j][e] = 0.f;
+        }
+    }
+#pragma unroll 4
+    for (int k = 0; k < TB; ++k) {
+        const int t = t0 + k;
+        if (t >= L) break;
+        float cur[VN], out[VN];
+        if constexpr (VEC) {
+            Vec<T> v;
+            v.load(xp + t * xr);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) cur[e] = v.v[e];
+        } else {
+            cur[0] = ld_f32(xp + t * xr);
+        }
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+            float c = bias[e];
+            c += w[e][0] * win[0][e];
+            c += w[e][1] * win[1][e];
+            c += w[e][2] * win[2][e];
+            c += w[e][3] * cur[e];
+            out[e] = silu_acc(c);
+            win[0][e] = win[1][e];
+            win[1][e] = win[2][e];
+            win[2][e] = cur[e];
+        }
+        if constexpr (VEC) {
+            Vec<T> v;
+#pragma unroll
+            for (int e = 0; e < VN; ++e) v.v[e] = out[e];
+            v.store(up + t * ur);
+        } else {
+            st_f32(up + t * ur, out[0]);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- RMSNorm (+ residual add)
+// One warp per row.  residual (fp32) is updated in place with x when both are given.
+template <typename TX, typename TY>
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const TX *x, float *residual, const float *w, TY *y, int64_t rows, int d, float eps) {
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const TX *xr = x ? x + row * d : nullptr;
+    float *rr = residual ? residual + row * d : nullptr;
+    float ss = 0.f;
+    for (int j = lane; j < d; j += 32) {
+        float v = xr ? ld_f32(xr + j) : 0.f;
+        if (rr) {
+            v += rr[j];
+            rr[j] = v;
+        }
+        ss += v * v;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+    for (int j = lane; j < d; j += 32) {
+        const float v = rr ? rr[j] : ld_f32(xr + j);
+        st_f32(y + row * d + j, v * inv * w[j]);
+    }
+}
+
+// ---------------------------------------------------------------- embedding gather
+template <typename TE, typename TO>
+__global__ void __launch_bounds__(256)
+embedding_kernel(const uint8_t *tok, const TE *emb, TO *out, int64_t n, int d) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * d) return;
+    const int64_t r = i / d;
+    const int j = (int)(i - r * d);
+    st_f32(out + i, ld_f32(emb + (int64_t)tok[r] * d + j));
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) silu_kernel(const T *x, T *y, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) st_f32(y + i, silu_acc(ld_f32(x + i)));
+}
+
+}  // namespace ew
+}  // namespace hx
+
+extern "C" {
+
+hx_status hx_conv1d_silu_fwd(const void *x, int64_t xb, int64_t xr, const float *conv_w, const float *conv_b, void *u,
+                             int64_t ub, int64_t ur, int32_t batch, int32_t seq_len, int32_t d_inner, int32_t d_conv,
+                             int32_t io_dtype, void *stream) {
+    using namespace hx::ew;
+    HX_REQUIRE(batch >= 0 && seq_len >= 0 && d_inner >= 0, HX_ERR_INVALID_DIMENSION, "negative dimension");
+    HX_REQUIRE(d_conv >= 1 && d_conv <= 4, HX_ERR_INVALID_DIMENSION, "d_conv %d outside [1, 4]", d_conv);
+    HX_REQUIRE(io_dtype == HX_F32 || io_dtype == HX_BF16, HX_ERR_DTYPE_MISMATCH, "io_dtype %d unsupported", io_dtype);
+    if (batch == 0 || seq_len == 0 || d_inner == 0) return HX_OK;
+    HX_REQUIRE(x && u && conv_w, HX_ERR_INVALID_INPUT, "x, u and conv_w must not be NULL");
+    HX_REQUIRE(xr >= d_inner && ur >= d_inner, HX_ERR_SHAPE_MISMATCH, "row stride smaller than d_inner");
+    HX_REQUIRE(batch <= 65535, HX_ERR_INVALID_DIMENSION, "batch %d exceeds the grid limit", batch);
+    cudaStream_t st = (cudaStream_t)stream;
+    constexpr int TB = 16;
+    const int es = io_dtype == HX_BF16 ? 2 : 4, vn = 16 / es;
+    const bool vec = d_inner % vn == 0 && xr % vn == 0 && ur % vn == 0 && xb % vn == 0 && ub % vn == 0 &&
+                     (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(u) & 15) == 0;
+    const int groups = vec ? d_inner / vn : d_inner;
+    dim3 grid((groups + 127) / 128, (seq_len + TB - 1) / TB, batch), block(128);
+    if (io_dtype == HX_BF16) {
+        auto xp = static_cast<const __nv_bfloat16 *>(x);
+        auto up = static_cast<__nv_bfloat16 *>(u);
+        if (vec) conv_silu_kernel<__nv_bfloat16, true, TB><<<grid, block, 0, st>>>(xp, xb, xr, conv_w, conv_b, up, ub, ur, seq_len, d_inner, d_conv);
+        else conv_silu_kernel<__nv_bfloat16, false, TB><<<grid, block, 0, st>>>(xp, xb, xr, conv_w, conv_b, up, ub, ur, seq_len, d_inner, d_conv);
+    } else {
+        auto xp = static_cast<const float *>(x);
+        auto up = static_cast<float *>(u);
+        if (vec) conv_silu_kernel<float, true, TB><<<grid, block, 0, st>>>(xp, xb, xr, conv_w, conv_b, up, ub, ur, seq_len, d_inner, d_conv);
+        else conv_silu_kernel<float, false, TB><<<grid, block, 0, st>>>(xp, xb, xr, conv_w, conv_b, up, ub, ur, seq_len, d_inner, d_conv);
+    }
+    return hx::check_launch("conv_silu_kernel");
+}
+
+hx_status hx_rmsnorm_fwd(const void *x, int32_t x_dtype, float *residual, const float *w, void *y, int32_t y_dtype,
+                         int64_t rows, int32_t d, float eps, void *stream) {
+    using namespace hx::ew;
+    HX_REQUIRE(rows >= 0 && d >= 1, HX_ERR_INVALID_DIMENSION, "bad dimensions rows %lld, d %d", (long long)rows, d);
+    if (rows == 0) return HX_OK;
+    HX_REQUIRE((x || residual) && w && y, HX_ERR_INVALID_INPUT, "x or residual, w and y must not be NULL");
+    HX_REQUIRE((x_dtype == HX_F32 || x_dtype == HX_BF16) && (y_dtype == HX_F32 || y_dtype == HX_BF16),
+               HX_ERR_DTYPE_MISMATCH, "dtype unsupported");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int wpb = 8;
+    dim3 grid((unsigned)((rows + wpb - 1) / wpb)), block(wpb * 32);
+    const bool xb = x_dtype == HX_BF16, yb = y_dtype == HX_BF16;
+    if (xb && yb) rmsnorm_kernel<<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), residual, w, static_cast<__nv_bfloat16 *>(y), rows, d, eps);
+    else if (xb) rmsnorm_kernel<<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), residual, w, static_cast<float *>(y), rows, d, eps);
+    else if (yb) rmsnorm_kernel<<<grid, block, 0, st>>>(static_cast<const float *>(x), residual, w, static_cast<__nv_bfloat16 *>(y), rows, d, eps);
+    else rmsnorm_kernel<<<grid, block, 0, st>>>(static_cast<const float *>(x), residual, w, static_cast<float *>(y), rows, d, eps);
+    return hx::check_launch("rmsnorm_kernel");
+}
+
+hx_status hx_embedding_fwd(const uint8_t *tokens, const void *emb, int32_t emb_dtype, void *out, int32_t out_dtype,
+                           int64_t n_tokens, int32_t d_model, void *stream) {
+    using namespace hx::ew;
+    HX_REQUIRE(n_tokens >= 0 && d_model >= 1, HX_ERR_INVALID_DIMENSION, "bad dimensions");
+    if (n_tokens == 0) return HX_OK;
+    HX_REQUIRE(tokens && emb && out, HX_ERR_INVALID_INPUT, "tokens, emb and out must not be NULL");
+    HX_REQUIRE((emb_dtype == HX_F32 || emb_dtype == HX_BF16) && (out_dtype == HX_F32 || out_dtype == HX_BF16),
+               HX_ERR_DTYPE_MISMATCH, "dtype unsupported");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t total = n_tokens * d_model;
+    dim3 grid((unsigned)((total + 255) / 256)), block(256);
+    const bool eb = emb_dtype == HX_BF16, ob = out_dtype == HX_BF16;
+    if (eb && ob) embedding_kernel<<<grid, block, 0, st>>>(tokens, static_cast<const __nv_bfloat16 *>(emb), static_cast<__nv_bfloat16 *>(out), n_tokens, d_model);
+    else if (eb) embedding_kernel<<<grid, block, 0, st>>>(tokens, static_cast<const __nv_bfloat16 *>(emb), static_cast<float *>(out), n_tokens, d_model);
+    else if (ob) embedding_kernel<<<grid, block, 0, st>>>(tokens, static_cast<const float *>(emb), static_cast<__nv_bfloat16 *>(out), n_tokens, d_model);
+    else embedding_kernel<<<grid, block, 0, st>>>(tokens, static_cast<const float *>(emb), static_cast<float *>(out), n_tokens, d_model);
+    return hx::check_launch("embedding_kernel");
+}
+
+hx_status hx_silu_fwd(const void *x, void *y, int64_t n, int32_t io_dtype, void *stream) {
+    using namespace hx::ew;
+    HX_REQUIRE(n >= 0, HX_ERR_INVALID_DIMENSION, "negative size");
+    if (n == 0) return HX_OK;
+    HX_REQUIRE(x && y, HX_ERR_INVALID_INPUT, "x and y must not be NULL");
+    HX_REQUIRE(io_dtype == HX_F32 || io_dtype == HX_BF16, HX_ERR_DTYPE_MISMATCH, "io_dtype %d unsupported", io_dtype);
+    cudaStream_t st = (cudaStream_t)stream;
+    dim3 grid((unsigned)((n + 255) / 256)), block(256);
+    if (io_dtype == HX_BF16) silu_kernel<<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), static_cast<__nv_bfloat16 *>(y), n);
+    else silu_kernel<<<grid, block, 0, st>>>(static_cast<const float *>(x), static_cast<float *>(y), n);
+    return hx::check_launch("silu_kernel");
+}
+
+}  // extern "C"

@@ -1,0 +1,318 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05) for sm_100a:
+//   C[M,N] = A[M,K] . W[N,K]^T (+ bias[N]) (+ activation), fp32 accumulation in tensor memory.
+// Both operands are K-major (row-major A, row-major nn::Linear weight [out, in]), so no transposes.
+//
+// Persistent kernel, one CTA per SM, 6 warps:
+//   warp 0      TMA producer: [128 x 64] A boxes and [BN x 64] W boxes, 128-byte swizzle, into a
+//               multi-stage shared-memory ring (full/empty mbarriers).
+//   warp 1      allocates tensor memory; one lane issues tcgen05.mma (M=128, N=BN, K=16, four per
+//               64-wide k-block) and commits completion to the ring's empty barriers and, at the end
+//               of a tile, to the accumulator-full barrier.  Two accumulators (2*BN columns) let the
+//               next tile's main loop overlap this tile's epilogue.
+//   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, bias/activation in registers,
+//               16-byte stores to C.
+// Out-of-range rows/columns/k are zero-filled by TMA and masked in the epilogue, so M, N, K need
+// not be tile multiples (K and the leading dimensions must be multiples of 8 for the 16-byte rule).
+// Every wait is bounded; a wait that runs out raises the per-device status word, the CTA drains,
+// frees its tensor memory and returns.
+#include "gemm.cuh"
+#include "hx_tma.cuh"
+
+namespace hx {
+namespace gemm {
+
+// Status word of this translation unit: a bounded wait that ran out ORs kWaitGemm in.
+__device__ int g_gemm_status = 0;
+constexpr int kWaitGemm = 32;
+constexpr int BM = 128, BK = 64;
+
+__device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
+    for (int i = 0; i < kMaxTries; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicOr(&g_gemm_status, kWaitGemm);
+    return false;
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows are 128 bytes apart,
+// 8-row groups 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);  // start address, bits [0,14)
+    d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset, bits [32,46)
+    d |= (uint64_t)1 << 46;                        // version
+    d |= (uint64_t)2 << 61;                        // 128-byte swizzle
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int BN> struct TcCfg {
+    static constexpr int STAGES = BN == 256 ? 4 : 6;
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int TMEM_COLS = 2 * BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+    static constexpr int THREADS = 192;
+};
+
+template <int BN, typename TC, int EPI>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w, const float *bias, TC *C,
+               int64_t ldc, int M, int N, int K, int vec_ok) {
+    using Cfg = TcCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ char smem_raw[];
+    char *smem = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * Cfg::STAGE_BYTES);
+    // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]; then the TMEM base and the abort flag
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar_full = [&](int s) { return bar0 + 8u * s; };
+    auto bar_empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto bar_acc_full = [&](int a) { return bar0 + 8u * (2 * STAGES + a); };
+    auto bar_acc_empty = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
+    const int tiles = num_m * num_n;
+    const int kblocks = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_empty(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_acc_full(a), 1);
+            mbar_init(bar_acc_empty(a), 4);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"((uint32_t)Cfg::TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ============================================================ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_a);
+            tma_prefetch_desc(&tm_w);
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int m0 = (tile / num_n) * BM, n0 = (tile % num_n) * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!wait_or_abort(bar_empty(s), ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                    mbar_expect_tx(bar_full(s), Cfg::STAGE_BYTES);
+                    tma_load_2d(sa, &tm_a, bar_full(s), kb * BK, m0);
+                    tma_load_2d(sa + Cfg::A_BYTES, &tm_w, bar_full(s), kb * BK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ============================================================ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                       ((uint32_t)(BM >> 4) << 24);
+            int it = 0, tc = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tc) {
+                const int acc = tc & 1;
+                if (!wait_or_abort(bar_acc_empty(acc), ((tc >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!wait_or_abort(bar_full(s), (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                    const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + Cfg::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+                    umma_commit(bar_empty(s));  // the stage is free once these MMAs have read it
+                }
+                if (ok) umma_commit(bar_acc_full(acc));
+            }
+        }
+    } else {
+        // ============================================================ epilogue warps
+        const int wq = warp & 3;  // TMEM lane quarter this warp may read
+        int tc = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tc) {
+            const int acc = tc & 1;
+            const int m0 = (tile / num_n) * BM, n0 = (tile % num_n) * BN;
+            if (!wait_or_abort(bar_acc_full(acc), (tc >> 1) & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const int m = m0 + wq * 32 + lane;
+            TC *crow = C + (int64_t)m * ldc;
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ++ch) {
+                const int nb = n0 + ch * 32;
+                if (nb >= N) break;  // warp-uniform
+                uint32_t r[32];
+                tmem_ld32(tmem_base + acc * BN + ch * 32 + ((uint32_t)(wq * 32) << 16), r);
+                tmem_ld_wait();
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    float x = __uint_as_float(r[j]);
+                    if (bias) x += (nb + j < N) ? __ldg(bias + nb + j) : 0.f;
+                    v[j] = apply_epilogue<EPI>(x);
+                }
+                if (m < M) {
+                    if (vec_ok && nb + 32 <= N) {
+                        if constexpr (sizeof(TC) == 2) {
+#pragma unroll
+                            for (int q4 = 0; q4 < 4; ++q4) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[q4 * 8 + 2 * e], v[q4 * 8 + 2 * e + 1]);
+                                    w[e] = *reinterpret_cast<const uint32_t *>(&h2);
+                                }
+                                *reinterpret_cast<uint4 *>(crow + nb + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int q4 = 0; q4 < 8; ++q4)
+                                *reinterpret_cast<float4 *>(crow + nb + q4 * 4) =
+                                    make_float4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (nb + j < N) st_f32(crow + nb + j, v[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_acc_empty(acc));
+        }
+    }
+
+    // teardown: everybody meets, then the allocating warp frees tensor memory
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
+                     : "memory");
+    }
+}
+
+template <int BN, typename TC, int EPI>
+static hx_status launch_tc_inst(const CUtensorMap &ma, const CUtensorMap &mw, const float *bias, void *C, int64_t ldc, int M,
+                                int N, int K, int vec_ok, cudaStream_t st) {
+    using Cfg = TcCfg<BN>;
+    auto kern = gemm_tc_kernel<BN, TC, EPI>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    HX_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        HX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        attr_set[dev] = true;
+    }
+    const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(ma, mw, bias, static_cast<TC *>(C), ldc, M, N, K, vec_ok);
+    return check_launch("gemm_tc_kernel");
+}
+
+template <int BN, typename TC>
+static hx_status launch_tc_epi(const CUtensorMap &ma, const CUtensorMap &mw, const float *bias, void *C, int64_t ldc, int M,
+                               int N, int K, int vec_ok, int epi, cudaStream_t st) {
+    switch (epi) {
+        case kEpiNone: return launch_tc_inst<BN, TC, kEpiNone>(ma, mw, bias, C, ldc, M, N, K, vec_ok, st);
+        case kEpiSilu: return launch_tc_inst<BN, TC, kEpiSilu>(ma, mw, bias, C, ldc, M, N, K, vec_ok, st);
+        case kEpiSoftplus: return launch_tc_inst<BN, TC, kEpiSoftplus>(ma, mw, bias, C, ldc, M, N, K, vec_ok, st);
+        default: return fail(HX_ERR_INVALID_INPUT, "unknown epilogue %d", epi);
+    }
+}
+
+}  // namespace gemm
+
+hx_status read_status_gemm(int *v, bool clear) {
+    HX_CUDA(cudaMemcpyFromSymbol(v, gemm::g_gemm_status, sizeof(int)));
+    if (clear && *v != 0) {
+        const int zero = 0;
+        HX_CUDA(cudaMemcpyToSymbol(gemm::g_gemm_status, &zero, sizeof(int)));
+    }
+    return HX_OK;
+}
+
+}  // namespace hx
+
+extern "C" hx_status hx_gemm_bf16(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias, void *C,
+                                  int64_t ldc, int32_t c_dtype, int32_t M, int32_t N, int32_t K, int32_t epilogue,
+                                  void *stream) {
+    using namespace hx::gemm;
+    hx_status s = validate_gemm(A, lda, W, ldw, C, ldc, M, N, K);
+    if (s != HX_OK) return s;
+    if (M == 0 || N == 0) return HX_OK;
+    HX_REQUIRE(c_dtype == HX_F32 || c_dtype == HX_BF16, HX_ERR_DTYPE_MISMATCH, "c_dtype %d unsupported", c_dtype);
+    HX_REQUIRE(K >= 1, HX_ERR_INVALID_DIMENSION, "K must be positive");
+    HX_REQUIRE(K % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0, HX_ERR_UNSUPPORTED_OPERATION,
+               "hx_gemm_bf16 needs K, lda and ldw to be multiples of 8 (got %d, %lld, %lld)", K, (long long)lda,
+               (long long)ldw);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int BN = N > 128 ? 256 : 128;
+    CUtensorMap ma, mw;
+    const uint64_t dims_a[2] = {(uint64_t)K, (uint64_t)M}, dims_w[2] = {(uint64_t)K, (uint64_t)N};
+    const uint64_t str_a[1] = {(uint64_t)lda * 2}, str_w[1] = {(uint64_t)ldw * 2};
+    const uint32_t box_a[2] = {(uint32_t)BK, (uint32_t)BM}, box_w[2] = {(uint32_t)BK, (uint32_t)BN};
+    if ((s = hx::encode_tensor_map(&ma, HX_BF16, 2, A, dims_a, str_a, box_a, true)) != HX_OK) return s;
+    if ((s = hx::encode_tensor_map(&mw, HX_BF16, 2, W, dims_w, str_w, box_w, true)) != HX_OK) return s;
+    const int es = c_dtype == HX_BF16 ? 2 : 4;
+    const int vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * es) % 16 == 0) ? 1 : 0;
+    if (BN == 256) {
+        if (c_dtype == HX_BF16) return launch_tc_epi<256, __nv_bfloat16>(ma, mw, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
+        return launch_tc_epi<256, float>(ma, mw, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
+    }
+    if (c_dtype == HX_BF16) return launch_tc_epi<128, __nv_bfloat16>(ma, mw, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
+    return launch_tc_epi<128, float>(ma, mw, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
+}

@@ -1,0 +1,116 @@
+// One Mamba block forward as a sequence of launches on caller-owned buffers:
+//   in_proj GEMM -> causal conv + SiLU -> x_proj GEMM -> dt_proj GEMM -> fused scan
+//   (softplus, decay, recurrence, D skip, SiLU(z) gate) -> out_proj GEMM.
+// The scan reads u, z, B and C in place: z is the second half of the in_proj output row and B, C
+// are column slices of the x_proj output row, all passed as strided views without copies.
+#include <cstring>
+
+#include "hx_common.cuh"
+
+namespace hx {
+namespace block {
+
+struct Layout {
+    size_t xz, u, dbc, dtl, y, total;
+    int64_t W;  // row width of the x_proj output
+};
+
+static Layout plan(const hx_mamba_block_args *a) {
+    const size_t es = dtype_size(a->io_dtype);
+    const size_t T = (size_t)a->batch * a->seq_len;
+    const size_t E = a->d_inner;
+    Layout l;
+    l.W = a->dt_rank + 2 * a->d_state;
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    size_t off = 0;
+    l.xz = off; off += up(T * 2 * E * es);
+    l.u = off; off += up(T * E * es);
+    l.dbc = off; off += up(T * l.W * es);
+    l.dtl = off; off += up(T * E * es);
+    l.y = off; off += up(T * E * es);
+    l.total = off + 256;
+    return l;
+}
+
+static hx_status validate(const hx_mamba_block_args *a) {
+    HX_REQUIRE(a != nullptr, HX_ERR_INVALID_INPUT, "hx_mamba_block_fwd: args is NULL");
+    HX_REQUIRE(a->batch >= 0 && a->seq_len >= 0, HX_ERR_INVALID_DIMENSION, "negative batch or seq_len");
+    HX_REQUIRE(a->d_model >= 1 && a->d_inner >= 1 && a->d_state >= 1 && a->d_state <= 256 && a->dt_rank >= 1,
+               HX_ERR_INVALID_DIMENSION, "bad block dimensions (d_model %d, d_inner %d, d_state %d, dt_rank %d)",
+               a->d_model, a->d_inner, a->d_state, a->dt_rank);
+    HX_REQUIRE(a->d_conv >= 1 && a->d_conv <= 4, HX_ERR_INVALID_DIMENSION, "d_conv %d outside [1, 4]", a->d_conv);
+    HX_REQUIRE(a->io_dtype == HX_F32 || a->io_dtype == HX_BF16, HX_ERR_DTYPE_MISMATCH, "io_dtype %d unsupported",
+               a->io_dtype);
+    return HX_OK;
+}
+
+}  // namespace block
+}  // namespace hx
+
+extern "C" {
+
+hx_status hx_mamba_block_workspace_bytes(const hx_mamba_block_args *a, size_t *bytes) {
+    HX_REQUIRE(bytes != nullptr, HX_ERR_INVALID_INPUT, "bytes is NULL");
+    hx_status s = hx::block::validate(a);
+    if (s != HX_OK) return s;
+    *bytes = hx::block::plan(a).total;
+    return HX_OK;
+}
+
+hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
+    using namespace hx::block;
+    hx_status s = validate(a);
+    if (s != HX_OK) return s;
+    if (a->batch == 0 || a->seq_len == 0) return HX_OK;
+    HX_REQUIRE(a->x && a->out && a->W_in && a->W_x && a->W_dt && a->W_out && a->conv_w && a->b_dt && a->A && a->Dskip,
+               HX_ERR_INVALID_INPUT, "a required block operand is NULL");
+    const Layout l = plan(a);
+    HX_REQUIRE(a->workspace && a->workspace_bytes >= l.total, HX_ERR_INVALID_INPUT,
+               "hx_mamba_block_fwd needs a workspace of %zu bytes (got %zu)", l.total, a->workspace_bytes);
+    char *ws = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(a->workspace) + 255) & ~uintptr_t(255));
+    const size_t es = hx::dtype_size(a->io_dtype);
+    const int64_t T = (int64_t)a->batch * a->seq_len;
+    HX_REQUIRE(T <= 0x7fffffff, HX_ERR_INVALID_DIMENSION, "batch * seq_len exceeds 2^31");
+    const int E = a->d_inner, M = a->d_model, N = a->d_state, R = a->dt_rank, W = (int)l.W;
+    void *xz = ws + l.xz, *u = ws + l.u, *dbc = ws + l.dbc, *dtl = ws + l.dtl, *y = ws + l.y;
+    const bool bf = a->io_dtype == HX_BF16;
+
+    // bf16: tensor-core GEMM where its alignment rules hold, CUDA-core GEMM otherwise; fp32: CUDA cores
+    auto gemm = [&](const void *A, int64_t lda, const void *Wt, int64_t ldw, void *C, int64_t ldc, int m, int n,
+                    int k) -> hx_status {
+        if (bf && k % 8 == 0 && lda % 8 == 0 && ldw % 8 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 &&
+            (reinterpret_cast<uintptr_t>(Wt) & 15) == 0)
+            return hx_gemm_bf16(A, lda, Wt, ldw, nullptr, C, ldc, HX_BF16, m, n, k, 0, stream);
+        return hx_gemm_simt(A, lda, Wt, ldw, nullptr, C, ldc, a->io_dtype, a->io_dtype, m, n, k, 0, stream);
+    };
+
+    // 1. xz = x W_in^T                                  [T, 2E]
+    if ((s = gemm(a->x, M, a->W_in, M, xz, 2 * E, (int)T, 2 * E, M)) != HX_OK) return s;
+    // 2. u = silu(conv(xs)), xs = xz[:, :E]            [T, E]
+    if ((s = hx_conv1d_silu_fwd(xz, (int64_t)a->seq_len * 2 * E, 2 * E, a->conv_w, a->conv_b, u, (int64_t)a->seq_len * E,
+                                E, a->batch, a->seq_len, E, a->d_conv, a->io_dtype, stream)) != HX_OK)
+        return s;
+    // 3. [dt_low | B | C] = u W_x^T                     [T, R + 2N]
+    if ((s = gemm(u, E, a->W_x, E, dbc, W, (int)T, W, E)) != HX_OK) return s;
+    // 4. dt_lin = dt_low W_dt^T                          [T, E]   (bias and softplus happen inside the scan)
+    if ((s = gemm(dbc, W, a->W_dt, R, dtl, E, (int)T, E, R)) != HX_OK) return s;
+    // 5. fused scan on strided views
+    hx_scan_args sa;
+    memset(&sa, 0, sizeof(sa));
+    sa.batch = a->batch; sa.seq_len = a->seq_len; sa.d_inner = E; sa.d_state = N; sa.d_conv = a->d_conv;
+    sa.io_dtype = a->io_dtype; sa.dt_softplus = 1; sa.variant = a->scan_variant;
+    sa.x = u; sa.x_batch_stride = (int64_t)a->seq_len * E; sa.x_row_stride = E;
+    sa.dt = dtl; sa.dt_batch_stride = (int64_t)a->seq_len * E; sa.dt_row_stride = E;
+    sa.z = static_cast<char *>(xz) + (size_t)E * es; sa.z_batch_stride = (int64_t)a->seq_len * 2 * E; sa.z_row_stride = 2 * E;
+    sa.Bm = static_cast<char *>(dbc) + (size_t)R * es; sa.B_batch_stride = (int64_t)a->seq_len * W; sa.B_row_stride = W;
+    sa.Cm = static_cast<char *>(dbc) + (size_t)(R + N) * es; sa.C_batch_stride = (int64_t)a->seq_len * W; sa.C_row_stride = W;
+    sa.y = y; sa.y_batch_stride = (int64_t)a->seq_len * E; sa.y_row_stride = E;
+    sa.A = a->A; sa.Dskip = a->Dskip; sa.dt_bias = a->b_dt;
+    sa.conv_w = nullptr; sa.conv_b = nullptr;  // u is already activated
+    sa.a_geometric = a->a_geometric;
+    if ((s = hx_selective_scan_fwd(&sa, stream)) != HX_OK) return s;
+    // 6. out = y W_out^T                                 [T, M]
+    return gemm(y, E, a->W_out, E, a->out, M, (int)T, M, E);
+}
+
+}  // extern "C"

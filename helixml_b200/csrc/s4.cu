@@ -1,0 +1,246 @@
+// S4 recurrences for sm_100a.
+//
+// s4_diag_kernel: the per-channel diagonal form  h_t = abar h_{t-1} + bbar u_t,  y = C.h + D u.
+//   The system is time-invariant, so the sequence is cut into 8 segments that run in parallel
+//   inside one CTA (one warp per segment):
+//     pass 1  every segment runs the recurrence from a zero state (no output) to get its end state,
+//     combine the start state of segment g is the Horner sum of the earlier end states with
+//             abar^segment_length, exchanged through shared memory,
+//     pass 2  every segment reruns from its true start state and emits y.
+//   With g = h / bbar the update is one FMA per state (g = abar g + u) and the output one more
+//   (y += (C bbar) g).  16 states per lane, the lanes of a channel are adjacent and combine their
+//   partial dot products with shuffles.
+//
+// s4_ref_*: the reference-literal recurrence of nn::ssm::S4Block::forward_ssm
+//   (crates/nn/src/ssm.rs:138-186): one d_state-wide state driven by all d_model inputs.
+//   It is computed as  V = dt * (B . U)  ->  diagonal scan over time on V (same 3-pass scheme,
+//   all segments in one CTA)  ->  Y = X . C^T + D * U.
+#include "hx_tma.cuh"
+
+namespace hx {
+namespace s4 {
+
+constexpr int kSeg = 8;   // segments per sequence (= warps per CTA) in s4_diag_kernel
+constexpr int kNSL = 16;  // states per lane
+
+template <typename T, int LPC>
+__global__ void __launch_bounds__(kSeg * 32)
+s4_diag_kernel(const T *u, const float *A, const float *Bp, const float *Cp, const float *delta, const float *Dskip, T *y,
+               int L, int D, int N) {
+    constexpr int CW = 32 / LPC;  // channels per warp
+    constexpr int TU = 8;         // steps loaded ahead of the arithmetic
+    __shared__ float ends[kSeg][32][kNSL];  // [segment][lane][state of the lane]
+    const int g = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int c = lane / LPC, q = lane % LPC;
+    const int d = blockIdx.x * CW + c;
+    const int b = blockIdx.y;
+    const bool chan_ok = d < D;
+    const int seg_len = (L + kSeg - 1) / kSeg;
+    const int t0 = min(L, g * seg_len), t1 = min(L, t0 + seg_len);
+
+    float2 a[kNSL / 2], k[kNSL / 2], aT[kNSL / 2];
+    const float dl = chan_ok ? delta[d] : 0.f;
+#pragma unroll
+    for (int j = 0; j < kNSL; ++j) {
+        const int n = q * kNSL + j;
+        float av = 0.f, kv = 0.f, atv = 0.f;
+        if (chan_ok && n < N) {
+            const float an = A[(int64_t)d * N + n];
+            av = expf(dl * an);
+            atv = expf(dl * an * (float)seg_len);
+            kv = Cp[(int64_t)d * N + n] * (dl * Bp[(int64_t)d * N + n]);
+        }
+        if (j & 1) { a[j / 2].y = av; k[j / 2].y = kv; aT[j / 2].y = atv; }
+        else { a[j / 2].x = av; k[j / 2].x = kv; aT[j / 2].x = atv; }
+    }
+    const T *up = u + ((int64_t)b * L) * D + (chan_ok ? d : 0);
+    T *yp = y + ((int64_t)b * L) * D + (chan_ok ? d : 0);
+    const float dsk = (chan_ok && Dskip) ? Dskip[d] : 0.f;
+
+    // ---- pass 1: end state of the segment from a zero start
+    float2 h[kNSL / 2];
+#pragma unroll
+    for (int j = 0; j < kNSL / 2; ++j) h[j] = make_float2(0.f, 0.f);
+    for (int t = t0; t < t1; t += TU) {
+        float ub[TU];
+#pragma unroll
+        for (int e = 0; e < TU; ++e) ub[e] = (t + e < t1 && chan_ok) ? ld_f32(up + (int64_t)(t + e) * D) : 0.f;
+#pragma unroll
+        for (int e = 0; e < TU; ++e) {
+            if (t + e < t1) {
+                const float2 u2 = splat2(ub[e]);
+#pragma unroll
+                for (int j = 0; j < kNSL / 2; ++j) h[j] = fma2(a[j], h[j], u2);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < kNSL / 2; ++j) {
+        ends[g][lane][2 * j] = h[j].x;
+        ends[g][lane][2 * j + 1] = h[j].y;
+    }
+    __syncthreads();
+    // ---- combine: start state of segment g (all earlier segments are full length)
+#pragma unroll
+    for (int j = 0; j < kNSL / 2; ++j) h[j] = make_float2(0.f, 0.f);
+    for (int gp = 0; gp < g; ++gp) {
+#pragma unroll
+        for (int j = 0; j < kNSL / 2; ++j)
+            h[j] = fma2(aT[j], h[j], make_float2(ends[gp][lane][2 * j], ends[gp][lane][2 * j + 1]));
+    }
+    // ---- pass 2: the real run
+    for (int t = t0; t < t1; t += TU) {
+        float ub[TU];
+#pragma unroll
+        for (int e = 0; e < TU; ++e) ub[e] = (t + e < t1 && chan_ok) ? ld_f32(up + (int64_t)(t + e) * D) : 0.f;
+#pragma unroll
+        for (int e = 0; e < TU; ++e) {
+            if (t + e < t1) {  // warp-uniform
+                const float2 u2 = splat2(ub[e]);
+                float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+                for (int j = 0; j < kNSL / 2; ++j) {
+                    h[j] = fma2(a[j], h[j], u2);
+                    acc = fma2(k[j], h[j], acc);
+                }
+                float s = acc.x + acc.y;
+#pragma unroll
+                for (int o = LPC / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                if (chan_ok && q == (e % LPC)) st_f32(yp + (int64_t)(t + e) * D, s + dsk * ub[e]);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- reference-literal S4
+// V[t][n] = sum_m (dt * B[n][m]) * u[m][t]   (m ascending, as the reference's matvec)
+__global__ void __launch_bounds__(128)
+s4_ref_in_kernel(const float *u, const float *Bm, float dt, float *V, int M, int L, int N) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    const int n = blockIdx.y;
+    if (t >= L) return;
+    float sum = 0.f;
+    for (int m = 0; m < M; ++m) sum += (Bm[(int64_t)n * M + m] * dt) * u[(int64_t)m * L + t];
+    V[(int64_t)t * N + n] = sum;
+}
+
+// In-place diagonal scan over time on V [L][N]: X_t = a X_{t-1} + V_t, a = exp(dt A_re) cos(dt A_im).
+// One CTA; thread = (state n, segment g); same 3-pass scheme through shared memory.
+__global__ void __launch_bounds__(1024)
+s4_ref_scan_kernel(float *V, const float *A_real, const float *A_imag, float dt, int L, int N, int G) {
+    extern __shared__ float ends_s[];  // [G][N]
+    const int n = threadIdx.x % N, g = threadIdx.x / N;
+    const bool active = g < G;
+    const float a = active ? expf(A_real[n] * dt) * cosf(A_imag[n] * dt) : 0.f;
+    const int seg_len = (L + G - 1) / G;
+    const int t0 = min(L, g * seg_len), t1 = min(L, t0 + seg_len);
+    float h = 0.f;
+    if (active)
+        for (int t = t0; t < t1; ++t) h = a * h + V[(int64_t)t * N + n];
+    if (active) ends_s[g * N + n] = h;
+    __syncthreads();
+    if (!active) return;
+    float aT = 1.f, base = a;  // a^seg_len by binary exponentiation (a may be negative)
+    for (int e = seg_len; e > 0; e >>= 1) {
+        if (e & 1) aT *= base;
+        base *= base;
+    }
+    h = 0.f;
+    for (int gp = 0; gp < g; ++gp) h = aT * h + ends_s[gp * N + n];
+    for (int t = t0; t < t1; ++t) {
+        h = a * h + V[(int64_t)t * N + n];
+        V[(int64_t)t * N + n] = h;
+    }
+}
+
+// y[t][m] = sum_n C[m][n] X[t][n] + D[m] u[m][t]   (n ascending)
+__global__ void __launch_bounds__(128)
+s4_ref_out_kernel(const float *X, const float *Cm, const float *Dv, const float *u, float *y, int M, int L, int N) {
+    extern __shared__ float xs[];  // X[t][:]
+    const int t = blockIdx.y;
+    for (int n = threadIdx.x; n < N; n += blockDim.x) xs[n] = X[(int64_t)t * N + n];
+    __syncthreads();
+    const int m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m >= M) return;
+    float sum = 0.f;
+    for (int n = 0; n < N; ++n) sum += Cm[(int64_t)m * N + n] * xs[n];
+    y[(int64_t)t * M + m] = sum + Dv[m] * u[(int64_t)m * L + t];
+}
+
+template <typename T>
+static hx_status launch_diag(const void *u, const float *A, const float *Bp, const float *Cp, const float *delta,
+                             const float *Dskip, void *y, int B, int L, int D, int N, cudaStream_t st) {
+    int lpc = 1;
+    while (lpc * kNSL < N) lpc *= 2;
+    auto up = static_cast<const T *>(u);
+    auto yp = static_cast<T *>(y);
+    dim3 block(kSeg * 32);
+#define HX_S4_CASE(LPC)                                                                                   \
+    case LPC: {                                                                                           \
+        dim3 grid((D + 32 / LPC - 1) / (32 / LPC), B);                                                    \
+        s4_diag_kernel<T, LPC><<<grid, block, 0, st>>>(up, A, Bp, Cp, delta, Dskip, yp, L, D, N);         \
+        break;                                                                                            \
+    }
+    switch (lpc) {
+        HX_S4_CASE(1) HX_S4_CASE(2) HX_S4_CASE(4) HX_S4_CASE(8) HX_S4_CASE(16)
+        default: return fail(HX_ERR_INVALID_DIMENSION, "d_state %d exceeds 256", N);
+    }
+#undef HX_S4_CASE
+    return check_launch("s4_diag_kernel");
+}
+
+}  // namespace s4
+}  // namespace hx
+
+extern "C" {
+
+hx_status hx_s4_diag_fwd(const void *u, const float *A, const float *Bp, const float *Cp, const float *delta,
+                         const float *Dskip, void *y, int32_t batch, int32_t seq_len, int32_t d_model, int32_t d_state,
+                         int32_t io_dtype, void *stream) {
+    HX_REQUIRE(batch >= 0 && seq_len >= 0 && d_model >= 0, HX_ERR_INVALID_DIMENSION, "negative dimension");
+    HX_REQUIRE(d_state >= 1 && d_state <= 256, HX_ERR_INVALID_DIMENSION, "d_state %d outside [1, 256]", d_state);
+    HX_REQUIRE(io_dtype == HX_F32 || io_dtype == HX_BF16, HX_ERR_DTYPE_MISMATCH, "io_dtype %d unsupported", io_dtype);
+    if (batch == 0 || seq_len == 0 || d_model == 0) return HX_OK;
+    HX_REQUIRE(u && A && Bp && Cp && delta && y, HX_ERR_INVALID_INPUT, "u, A, Bp, Cp, delta and y must not be NULL");
+    HX_REQUIRE(batch <= 65535, HX_ERR_INVALID_DIMENSION, "batch %d exceeds the grid limit", batch);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (io_dtype == HX_BF16)
+        return hx::s4::launch_diag<__nv_bfloat16>(u, A, Bp, Cp, delta, Dskip, y, batch, seq_len, d_model, d_state, st);
+    return hx::s4::launch_diag<float>(u, A, Bp, Cp, delta, Dskip, y, batch, seq_len, d_model, d_state, st);
+}
+
+size_t hx_s4_ref_workspace_bytes(int32_t seq_len, int32_t d_state) {
+    if (seq_len <= 0 || d_state <= 0) return 0;
+    return (size_t)seq_len * d_state * sizeof(float);
+}
+
+hx_status hx_s4_ref_forward_ssm(const float *u, const float *A_real, const float *A_imag, const float *Bm,
+                                const float *Cm, const float *Dv, float dt, float *y, int32_t d_model, int32_t seq_len,
+                                int32_t d_state, void *workspace, size_t workspace_bytes, void *stream) {
+    using namespace hx::s4;
+    HX_REQUIRE(d_model >= 0 && seq_len >= 0, HX_ERR_INVALID_DIMENSION, "negative dimension");
+    HX_REQUIRE(d_state >= 1 && d_state <= 256, HX_ERR_INVALID_DIMENSION, "d_state %d outside [1, 256]", d_state);
+    if (d_model == 0 || seq_len == 0) return HX_OK;
+    HX_REQUIRE(u && A_real && A_imag && Bm && Cm && Dv && y, HX_ERR_INVALID_INPUT, "NULL operand");
+    HX_REQUIRE(seq_len <= 65535, HX_ERR_INVALID_DIMENSION, "seq_len %d exceeds the grid limit", seq_len);
+    const size_t need = hx_s4_ref_workspace_bytes(seq_len, d_state);
+    HX_REQUIRE(workspace && workspace_bytes >= need, HX_ERR_INVALID_INPUT,
+               "hx_s4_ref_forward_ssm needs a workspace of %zu bytes (got %zu)", need, workspace_bytes);
+    cudaStream_t st = (cudaStream_t)stream;
+    float *V = static_cast<float *>(workspace);
+    s4_ref_in_kernel<<<dim3((seq_len + 127) / 128, d_state), 128, 0, st>>>(u, Bm, dt, V, d_model, seq_len, d_state);
+    hx_status s = hx::check_launch("s4_ref_in_kernel");
+    if (s != HX_OK) return s;
+    int G = 1024 / d_state;
+    if (G > 32) G = 32;
+    if (G > seq_len) G = seq_len;
+    if (G < 1) G = 1;
+    s4_ref_scan_kernel<<<1, G * d_state, (size_t)G * d_state * sizeof(float), st>>>(V, A_real, A_imag, dt, seq_len,
+                                                                                  d_state, G);
+    if ((s = hx::check_launch("s4_ref_scan_kernel")) != HX_OK) return s;
+    s4_ref_out_kernel<<<dim3((d_model + 127) / 128, seq_len), 128, d_state * sizeof(float), st>>>(V, Cm, Dv, u, y, d_model,
+                                                                                                 seq_len, d_state);
+    return hx::check_launch("s4_ref_out_kernel");
+}
+
+}  // extern "C"

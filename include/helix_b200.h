@@ -1,0 +1,247 @@
+/*
+ * helix_b200.h -- C ABI of the B200 (sm_100a) state-space hot path.
+ *
+ * This is the seam a Rust `extern "C"` block in crates/backend-cuda binds.  The reference
+ * has no usable FFI for this path: its build script compiles kernels.cu into a static
+ * library of C++-mangled __global__ functions with no host launchers
+ * (crates/backend-cuda/build.rs:26-52), `execute_ssm_kernel` returns Ok(()) without doing
+ * anything (crates/backend-cuda/src/cuda_backend.rs:238-247) and `SsmKernel::execute_forward`
+ * copies its input to its output (crates/backend-cuda/src/cuda_kernels.rs:169-180).  Each
+ * entry point below names the reference interface it stands in for.
+ *
+ * Conventions
+ *  - Plain pointers and sizes only.  Device pointers unless a name says `host`.
+ *  - The caller owns every buffer (inputs, outputs, workspaces); the library keeps no
+ *    pointer after a call returns.  Compute entry points never allocate device memory.
+ *  - `stream` is a cudaStream_t passed as void* (NULL = default stream).  Launches are
+ *    asynchronous with respect to the host and ordered on that stream.
+ *  - Every entry point returns an hx_status whose values map one to one onto the
+ *    reference's TensorError variants (crates/tensor-core/src/error.rs:7-37); bad input is
+ *    reported, never trapped.  hx_last_error() gives the calling thread's last message.
+ *  - All entry points are re-entrant and thread-safe.
+ *  - Strides are in ELEMENTS of the tensor's dtype.  The innermost (channel) stride is 1.
+ */
+#ifndef HELIX_B200_H
+#define HELIX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define HX_API __attribute__((visibility("default")))
+#else
+#define HX_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* crates/tensor-core/src/error.rs:7-37, same order. */
+typedef enum hx_status {
+    HX_OK = 0,
+    HX_ERR_SHAPE_MISMATCH = 1,
+    HX_ERR_INVALID_DIMENSION = 2,
+    HX_ERR_DEVICE_MISMATCH = 3,
+    HX_ERR_DTYPE_MISMATCH = 4,
+    HX_ERR_UNSUPPORTED_OPERATION = 5,
+    HX_ERR_ALLOCATION_FAILED = 6,
+    HX_ERR_BACKEND = 7,
+    HX_ERR_SERIALIZATION = 8,
+    HX_ERR_INVALID_CHECKPOINT = 9,
+    HX_ERR_INVALID_INPUT = 10
+} hx_status;
+
+/* Storage types.  The reference's DType has no bf16 (crates/tensor-core/src/dtype.rs:8-37);
+ * HX_BF16 is the addition the device tensor type needs. */
+typedef enum hx_dtype { HX_F32 = 0, HX_BF16 = 1, HX_U8 = 2 } hx_dtype;
+
+/* Kernel selection for hx_selective_scan_fwd. */
+typedef enum hx_scan_variant {
+    HX_SCAN_AUTO = 0,     /* pick the fastest kernel that supports the arguments */
+    HX_SCAN_SIMPLE = 1,   /* one thread per (batch, channel); any d_state <= 256; the parity baseline */
+    HX_SCAN_TILED = 2,    /* state split over lanes, shared-memory staged tiles; d_state == 16 */
+    HX_SCAN_SEQSPLIT = 3  /* HX_SCAN_TILED with the sequence split over CTAs and carries passed
+                             through `workspace` by a bounded look-back */
+} hx_scan_variant;
+
+HX_API const char *hx_version(void);
+/* Message of the last failing call made by this thread ("" if none). */
+HX_API const char *hx_last_error(void);
+HX_API const char *hx_status_name(hx_status s);
+
+/* ---- device memory (stands in for CudaBackend::allocate / deallocate / copy_to / copy_from,
+ *      which store tensors in a host HashMap, crates/backend-cuda/src/cuda_backend.rs:26,449-520) */
+HX_API hx_status hx_device_count(int *count);
+HX_API hx_status hx_set_device(int device);
+HX_API hx_status hx_alloc(void **dptr, size_t bytes);
+HX_API hx_status hx_free(void *dptr);
+HX_API hx_status hx_host_alloc(void **hptr, size_t bytes);   /* pinned host memory */
+HX_API hx_status hx_host_free(void *hptr);
+HX_API hx_status hx_memcpy_h2d(void *dst, const void *src_host, size_t bytes, void *stream);
+HX_API hx_status hx_memcpy_d2h(void *dst_host, const void *src, size_t bytes, void *stream);
+HX_API hx_status hx_memset(void *dptr, int value, size_t bytes, void *stream);
+HX_API hx_status hx_stream_synchronize(void *stream);
+
+/* ---- fused selective scan (the centrepiece).
+ * Stands in for nn::ssm::MambaBlock::{conv1d, selective_ssm} (crates/nn/src/ssm.rs:467-483),
+ * the SSMOp::{Conv1d, Discretize, SelectiveScan} names (crates/tensor-core/src/ops.rs:148-153)
+ * and CudaBackend::execute_ssm_kernel (crates/backend-cuda/src/cuda_backend.rs:238-247).
+ *
+ *   c[b,t,d]  = conv_b[d] + sum_j conv_w[d,j] * x[b, t-(K-1)+j, d]     (conv_w != NULL)
+ *   u         = c / (1 + exp(-c))                                       (u = x when conv_w == NULL)
+ *   dt        = softplus(dt_raw + dt_bias)  (softplus(v) = v for v > 20; plain sum if dt_softplus == 0)
+ *   h_t[n]    = exp(dt * A[d,n]) * h_{t-1}[n] + (dt * u) * Bm[b,t,n],   h_{-1} = 0
+ *   y[b,t,d]  = (sum_n Cm[b,t,n] * h_t[n] + Dskip[d] * u) * silu(z[b,t,d])
+ * State and all arithmetic are fp32 whatever io_dtype is. */
+typedef struct hx_scan_args {
+    int32_t batch, seq_len, d_inner, d_state;
+    int32_t d_conv;           /* taps K of the causal depthwise conv (1..4); ignored when conv_w == NULL */
+    int32_t io_dtype;         /* hx_dtype of x, dt, z, Bm, Cm, y: HX_F32 or HX_BF16 */
+    int32_t dt_softplus;      /* 1: dt = softplus(dt_raw + dt_bias) */
+    int32_t variant;          /* hx_scan_variant */
+    const void *x;            /* [batch, seq_len, d_inner] */
+    const void *dt;           /* [batch, seq_len, d_inner] raw (pre-softplus) step sizes */
+    const void *z;            /* [batch, seq_len, d_inner] gate input, or NULL */
+    const void *Bm;           /* [batch, seq_len, d_state] */
+    const void *Cm;           /* [batch, seq_len, d_state] */
+    void *y;                  /* [batch, seq_len, d_inner] */
+    int64_t x_batch_stride, x_row_stride;
+    int64_t dt_batch_stride, dt_row_stride;
+    int64_t z_batch_stride, z_row_stride;
+    int64_t B_batch_stride, B_row_stride;
+    int64_t C_batch_stride, C_row_stride;
+    int64_t y_batch_stride, y_row_stride;
+    const float *A;           /* [d_inner, d_state] fp32, A = -exp(A_log) */
+    const float *Dskip;       /* [d_inner] fp32 or NULL */
+    const float *conv_w;      /* [d_inner, d_conv] fp32 or NULL */
+    const float *conv_b;      /* [d_inner] fp32 or NULL */
+    const float *dt_bias;     /* [d_inner] fp32 or NULL */
+    float *h_last;            /* [batch, d_inner, d_state] fp32 final state, or NULL */
+    void *workspace;          /* HX_SCAN_SEQSPLIT only: hx_selective_scan_workspace_bytes() bytes */
+    size_t workspace_bytes;
+    int32_t seq_splits;       /* HX_SCAN_SEQSPLIT: number of sequence segments (0 = choose) */
+    int32_t a_geometric;      /* 1: the caller asserts A[d][n] == (n+1) * A[d][0] (checked once with
+                                 hx_scan_check_geometric); then exp(dt*A[d][n]) is evaluated as a power of
+                                 exp(dt*A[d][0]), one exp per point instead of d_state */
+    int32_t lanes_per_channel;/* HX_SCAN_TILED / SEQSPLIT: lanes that share one channel's 16 states
+                                 (1, 2 or 4; 0 = choose from the problem size) */
+    int32_t reserved;
+} hx_scan_args;
+
+HX_API hx_status hx_selective_scan_fwd(const hx_scan_args *args, void *stream);
+/* Bytes of `workspace` HX_SCAN_SEQSPLIT needs for these dimensions (0 for the other variants). */
+HX_API hx_status hx_selective_scan_workspace_bytes(const hx_scan_args *args, size_t *bytes);
+/* The same operation on HOST activations: x, dt, z, Bm, Cm are read from (preferably pinned) host memory
+ * with the strides given in args, staged into `dev_workspace` (caller-owned device memory of
+ * hx_selective_scan_host_workspace_bytes() bytes), scanned, and y is copied back to the host pointer
+ * args->y.  A, Dskip, conv_w, conv_b, dt_bias and h_last remain device pointers (they are parameters,
+ * resident on the device).  Copies and the kernel are queued on `stream`; synchronise it before reading y.
+ * This is the call a host-tensor backend (the reference's CudaBackend keeps tensors in host memory,
+ * crates/backend-cuda/src/cuda_backend.rs:26) makes per forward. */
+HX_API hx_status hx_selective_scan_host(const hx_scan_args *args, void *dev_workspace, size_t dev_workspace_bytes,
+                                 void *stream);
+HX_API hx_status hx_selective_scan_host_workspace_bytes(const hx_scan_args *args, size_t *bytes);
+/* Synchronous helper, meant for weight-load time: *is_geometric = 1 when every row of A [d_inner, d_state]
+ * satisfies A[d][n] == (n+1) * A[d][0] to fp32 rounding (true for the S4D-real initialisation
+ * A_log[d][n] = log(n+1)).  Copies A to the host. */
+HX_API hx_status hx_scan_check_geometric(const float *A, int32_t d_inner, int32_t d_state, int32_t *is_geometric);
+/* Device-side wait failures (a bounded wait on a barrier or a flag that ran out) are recorded in a
+ * per-device status word instead of trapping.  Synchronises the device, returns the word (0 = none) and
+ * clears it when `clear` is non-zero.  A non-zero word means the outputs of the launches since the last
+ * clear are not valid; map it to TensorError::BackendError. */
+HX_API hx_status hx_device_status(int32_t *status, int32_t clear);
+
+/* ---- causal depthwise conv + SiLU alone: u = silu(conv(x)).  In the full block the x_proj GEMM
+ *      consumes u before the scan can run.  Stands in for nn::ssm::MambaBlock::conv1d
+ *      (crates/nn/src/ssm.rs:467-471, `input.clone()` in the reference). */
+HX_API hx_status hx_conv1d_silu_fwd(const void *x, int64_t x_batch_stride, int64_t x_row_stride,
+                             const float *conv_w, const float *conv_b, void *u,
+                             int64_t u_batch_stride, int64_t u_row_stride, int32_t batch,
+                             int32_t seq_len, int32_t d_inner, int32_t d_conv, int32_t io_dtype,
+                             void *stream);
+
+/* ---- diagonal S4 recurrence, one (abar, bbar, C) triple per (channel, state):
+ *   h_t = exp(delta[d] A[d,n]) h_{t-1} + delta[d] Bp[d,n] u[b,t,d];  y = sum_n Cp[d,n] h_t[n] + Dskip[d] u.
+ * Stands in for nn::ssm::S4Block::forward_ssm + discretize (crates/nn/src/ssm.rs:103-186) in the
+ * per-channel form of the benchmark configuration.  u, y: [batch, seq_len, d_model], dense. */
+HX_API hx_status hx_s4_diag_fwd(const void *u, const float *A, const float *Bp, const float *Cp,
+                         const float *delta, const float *Dskip, void *y, int32_t batch,
+                         int32_t seq_len, int32_t d_model, int32_t d_state, int32_t io_dtype,
+                         void *stream);
+
+/* ---- the reference-literal S4 recurrence (crates/nn/src/ssm.rs:138-186): one shared state vector
+ * of d_state entries driven by all d_model inputs.
+ *   a = exp(dt A_real) cos(dt A_imag);  state_t = a state_{t-1} + (dt Bm) u_t;  y_t = Cm state_t + Dv u_t
+ * u is [d_model, seq_len] fp32 (the layout forward_ssm requires, ssm.rs:142-147); y is the time-major
+ * buffer [seq_len, d_model] the reference's stack() produces (crates/backend-cpu/src/lib.rs:281-296).
+ * workspace: hx_s4_ref_workspace_bytes(seq_len, d_state) bytes of device memory. */
+HX_API hx_status hx_s4_ref_forward_ssm(const float *u, const float *A_real, const float *A_imag,
+                                const float *Bm, const float *Cm, const float *Dv, float dt,
+                                float *y, int32_t d_model, int32_t seq_len, int32_t d_state,
+                                void *workspace, size_t workspace_bytes, void *stream);
+HX_API size_t hx_s4_ref_workspace_bytes(int32_t seq_len, int32_t d_state);
+
+/* ---- dense projections: C[M,N] = A[M,K] . W[N,K]^T (+ bias[N]), bf16 operands, fp32 accumulation
+ *      in tensor memory (tcgen05), C written as bf16 or fp32.  Stands in for nn::Linear::forward
+ *      (crates/nn/src/lib.rs:120-134) and the orphan cuBLAS sgemm call
+ *      (crates/backend-cuda/src/ops_impl.rs:222-236).
+ *      lda / ldw / ldc are row strides in elements; K, lda, ldw must be multiples of 8 and the
+ *      base pointers 16-byte aligned (TMA rules).  epilogue: 0 none, 1 SiLU, 2 softplus. */
+HX_API hx_status hx_gemm_bf16(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias,
+                       void *C, int64_t ldc, int32_t c_dtype, int32_t M, int32_t N, int32_t K,
+                       int32_t epilogue, void *stream);
+/* Same contract on CUDA cores in fp32 (any alignment, fp32 or bf16 operands): the small-shape and
+ * fp32 path (the reference is fp32 throughout). */
+HX_API hx_status hx_gemm_simt(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias,
+                       void *C, int64_t ldc, int32_t ab_dtype, int32_t c_dtype, int32_t M,
+                       int32_t N, int32_t K, int32_t epilogue, void *stream);
+
+/* ---- RMSNorm over the last axis with optional fused residual add.  The residual stream is fp32:
+ *   if (residual) { residual += x (x may be NULL: nothing added); src = residual } else src = x
+ *   y = src / sqrt(mean(src^2) + eps) * w
+ * Stands in for nn::RMSNorm::forward (crates/nn/src/lib.rs:258-285). */
+HX_API hx_status hx_rmsnorm_fwd(const void *x, int32_t x_dtype, float *residual, const float *w, void *y,
+                         int32_t y_dtype, int64_t rows, int32_t d, float eps, void *stream);
+
+/* ---- byte embedding gather: out[i, :] = emb[tokens[i], :]
+ *      (examples/ssm_byte_lm feeds byte ids to its model, examples/ssm_byte_lm/src/main.rs:104-130). */
+HX_API hx_status hx_embedding_fwd(const uint8_t *tokens, const void *emb, int32_t emb_dtype, void *out,
+                           int32_t out_dtype, int64_t n_tokens, int32_t d_model, void *stream);
+
+/* ---- elementwise helpers the exported reference block needs (crates/nn/src/lib.rs:888-906):
+ *      y = silu(x)  (TensorActivation::silu, crates/backend-cpu/src/lib.rs:1154-1170). */
+HX_API hx_status hx_silu_fwd(const void *x, void *y, int64_t n, int32_t io_dtype, void *stream);
+
+/* ---- one whole Mamba block forward on device buffers (in_proj -> conv+SiLU -> x_proj -> dt_proj ->
+ *      fused scan -> out_proj).  Stands in for MambaBlock::forward (crates/nn/src/lib.rs:910,
+ *      crates/nn/src/ssm.rs:436).  Weights are row-major [out, in] like nn::Linear.
+ *      io_dtype HX_BF16: weights and activations bf16, tensor-core GEMMs.
+ *      io_dtype HX_F32 : everything fp32, CUDA-core GEMMs. */
+typedef struct hx_mamba_block_args {
+    int32_t batch, seq_len, d_model, d_inner, d_state, d_conv, dt_rank;
+    int32_t io_dtype;
+    const void *x;            /* [batch*seq_len, d_model] */
+    void *out;                /* [batch*seq_len, d_model] */
+    const void *W_in;         /* [2*d_inner, d_model] */
+    const void *W_x;          /* [dt_rank + 2*d_state, d_inner] */
+    const void *W_dt;         /* [d_inner, dt_rank] */
+    const void *W_out;        /* [d_model, d_inner] */
+    const float *conv_w;      /* [d_inner, d_conv] */
+    const float *conv_b;      /* [d_inner] or NULL */
+    const float *b_dt;        /* [d_inner] */
+    const float *A;           /* [d_inner, d_state] */
+    const float *Dskip;       /* [d_inner] */
+    void *workspace;          /* hx_mamba_block_workspace_bytes() bytes */
+    size_t workspace_bytes;
+    int32_t scan_variant;     /* hx_scan_variant */
+    int32_t a_geometric;      /* as hx_scan_args.a_geometric */
+} hx_mamba_block_args;
+
+HX_API hx_status hx_mamba_block_fwd(const hx_mamba_block_args *args, void *stream);
+HX_API hx_status hx_mamba_block_workspace_bytes(const hx_mamba_block_args *args, size_t *bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HELIX_B200_H */

@@ -1,0 +1,187 @@
+"""GPU parity of the other kernels on the path (S4 recurrences, conv, GEMMs, RMSNorm, embedding, the
+whole Mamba block) against the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+from conftest import BF16_TOL, FP32_TOL, fp32_tol_err, rel_l2, to_dev, to_np
+from helixml_b200 import synth
+from oracle import cbind
+
+pytestmark = pytest.mark.gpu
+
+
+def _status_ok():
+    from helixml_b200 import _lib
+    assert _lib.device_status() == 0, "a bounded device-side wait ran out"
+
+
+# ------------------------------------------------------------------ S4
+@pytest.mark.parametrize("B,L,D,N", [(2, 61, 10, 64), (1, 7, 3, 16), (3, 200, 40, 64), (1, 130, 5, 100), (2, 9, 33, 1)])
+def test_s4_diag(B, L, D, N):
+    from helixml_b200 import ops
+    s = synth.s4_inputs(1, B, L, D, N)
+    got = ops.s4_diag(*(to_dev(s[k]) for k in ("u", "A", "B", "C", "delta", "D")))
+    ref = cbind.s4_diag(s["u"], s["A"], s["B"], s["C"], s["delta"], s["D"])
+    assert fp32_tol_err(to_np(got), ref) <= FP32_TOL
+
+
+def test_s4_diag_config1_full():
+    """Benchmark configuration 1 at full size: batch 8, L 2048, d_model 256, d_state 64, f32, seed 1."""
+    from helixml_b200 import ops
+    s = synth.s4_inputs(1, 8, 2048, 256, 64)
+    got = ops.s4_diag(*(to_dev(s[k]) for k in ("u", "A", "B", "C", "delta", "D")))
+    ref = cbind.s4_diag(s["u"], s["A"], s["B"], s["C"], s["delta"], s["D"])
+    assert fp32_tol_err(to_np(got), ref) <= FP32_TOL
+
+
+def test_s4_diag_golden(golden):
+    from helixml_b200 import ops
+    g = golden("s4_diag_small.npz")
+    got = ops.s4_diag(*(to_dev(g[k]) for k in ("u", "A", "B", "C", "delta", "D")))
+    assert fp32_tol_err(to_np(got), g["y"]) <= FP32_TOL
+
+
+@pytest.mark.parametrize("M,L,N", [(12, 45, 16), (64, 64, 16), (256, 300, 64), (5, 1, 8)])
+def test_s4_reference_literal(M, L, N):
+    """nn::ssm::S4Block::forward_ssm (crates/nn/src/ssm.rs:138-186): [d_model, L] in, time-major [L, d_model] out."""
+    from helixml_b200 import ops
+    r = {"u": synth.normal(21, "u", (M, L)), "A_real": synth.uniform(21, "Ar", (N,), -0.5, 0.0),
+         "A_imag": synth.normal(21, "Ai", (N,)), "B": synth.normal(21, "B", (N, M), 0, 0.1),
+         "C": synth.normal(21, "C", (M, N), 0, 0.1), "D": synth.normal(21, "D", (M,), 0, 0.5)}
+    got = ops.s4_ref_forward_ssm(*(to_dev(r[k]) for k in ("u", "A_real", "A_imag", "B", "C", "D")))
+    ref = cbind.s4_forward_ssm(r["u"], r["A_real"], r["A_imag"], r["B"], r["C"], r["D"])
+    assert got.shape == (L, M)
+    assert fp32_tol_err(to_np(got), ref) <= FP32_TOL
+
+
+def test_s4_reference_literal_golden(golden):
+    from helixml_b200 import ops
+    g = golden("s4_ref_small.npz")
+    got = ops.s4_ref_forward_ssm(*(to_dev(g[k]) for k in ("u", "A_real", "A_imag", "B", "C", "D")))
+    assert fp32_tol_err(to_np(got), g["y"]) <= FP32_TOL
+
+
+# ------------------------------------------------------------------ conv, norm, embedding, silu
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("B,L,D,K", [(2, 50, 64, 4), (1, 3, 24, 4), (3, 17, 7, 2), (1, 100, 128, 3)])
+def test_conv1d_silu(dtype, B, L, D, K):
+    from helixml_b200 import ops
+    x = synth.normal(51, "x", (B, L, D))
+    w = synth.uniform(51, "w", (D, K), -0.5, 0.5)
+    b = synth.uniform(51, "b", (D,), -0.2, 0.2)
+    if dtype == "bf16":
+        x = synth.round_bf16(x)
+    got = ops.conv1d_silu(to_dev(x, "bf16" if dtype == "bf16" else None), to_dev(w), to_dev(b))
+    ref = cbind.conv_silu(x, w, b)
+    if dtype == "bf16":
+        assert rel_l2(to_np(got), ref) <= BF16_TOL
+    else:
+        assert fp32_tol_err(to_np(got), ref) <= FP32_TOL
+
+
+def test_rmsnorm_and_residual():
+    import torch
+    from helixml_b200 import ops
+    x = synth.normal(52, "x", (37, 96))
+    w = synth.uniform(52, "w", (96,), 0.5, 1.5)
+    ref = cbind.rmsnorm(x, w, 1e-5)
+    assert fp32_tol_err(to_np(ops.rmsnorm(to_dev(x), to_dev(w), 1e-5)), ref) <= FP32_TOL
+    res = synth.normal(52, "res", (37, 96))
+    r = to_dev(res)
+    y = ops.rmsnorm(to_dev(synth.round_bf16(x), "bf16"), to_dev(w), 1e-5, residual=r, out_dtype=torch.bfloat16)
+    summed = res + synth.round_bf16(x)
+    assert np.allclose(to_np(r), summed, atol=1e-6)
+    assert rel_l2(to_np(y), cbind.rmsnorm(summed, w, 1e-5)) <= BF16_TOL
+
+
+def test_embedding_and_silu():
+    import torch
+    from helixml_b200 import ops
+    emb = synth.normal(53, "emb", (256, 48), 0, 0.02)
+    tok = synth.random_bytes(53, "tok", (3, 21))
+    out = ops.embedding(to_dev(tok), to_dev(emb))
+    assert np.array_equal(to_np(out), emb[tok])
+    x = synth.normal(53, "x", (1000,))
+    assert fp32_tol_err(to_np(ops.silu(to_dev(x))), cbind.silu(x)) <= FP32_TOL
+
+
+# ------------------------------------------------------------------ GEMMs
+@pytest.mark.parametrize("M,N,K", [(100, 128, 64), (37, 50, 19), (1, 1, 1), (300, 80, 1536 // 8)])
+def test_gemm_simt_f32(M, N, K):
+    from helixml_b200 import ops
+    a, w, b = synth.normal(61, "a", (M, K)), synth.normal(61, "w", (N, K), 0, 0.1), synth.normal(61, "b", (N,))
+    got = ops.gemm(to_dev(a), to_dev(w), to_dev(b), tensor_cores=False)
+    assert fp32_tol_err(to_np(got), cbind.linear(a, w, b)) <= FP32_TOL
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (256, 256, 128), (1000, 3072, 768), (513, 80, 1536), (300, 1536, 48),
+                                   (70, 768, 1536), (4096, 256, 768), (129, 136, 72)])
+def test_gemm_tcgen05_bf16(M, N, K):
+    """The tensor-core GEMM against the oracle's Linear on bf16-exact operands; fp32 accumulation
+    leaves only the output rounding."""
+    import torch
+    from helixml_b200 import ops
+    a = synth.round_bf16(synth.normal(62, "a", (M, K)))
+    w = synth.round_bf16(synth.normal(62, "w", (N, K), 0, 0.05))
+    got32 = ops.gemm(to_dev(a, "bf16"), to_dev(w, "bf16"), out_dtype=torch.float32)
+    _status_ok()
+    ref = (a.astype(np.float64) @ w.astype(np.float64).T)
+    assert fp32_tol_err(to_np(got32), ref) <= FP32_TOL
+    got16 = ops.gemm(to_dev(a, "bf16"), to_dev(w, "bf16"))
+    _status_ok()
+    assert rel_l2(to_np(got16), ref) <= 5e-3
+
+
+def test_gemm_tcgen05_bias_epilogue_and_strides():
+    import torch
+    from helixml_b200 import _lib, ops
+    M, N, K = 200, 96, 48
+    wide = synth.round_bf16(synth.normal(63, "a", (M, 80)))
+    w = synth.round_bf16(synth.normal(63, "w", (N, K), 0, 0.1))
+    b = synth.normal(63, "b", (N,))
+    a_dev = to_dev(wide, "bf16")[:, :K]  # a column slice: lda = 80
+    got = ops.gemm(a_dev, to_dev(w, "bf16"), to_dev(b), out_dtype=torch.float32, epilogue=_lib.EPI_SOFTPLUS)
+    _status_ok()
+    lin = wide[:, :K].astype(np.float64) @ w.astype(np.float64).T + b
+    ref = np.where(lin > 20, lin, np.log1p(np.exp(lin)))
+    assert fp32_tol_err(to_np(got), ref) <= FP32_TOL
+    with pytest.raises(_lib.HxError) as e:
+        ops.gemm(to_dev(wide, "bf16")[:, :44], to_dev(w, "bf16")[:, :44].contiguous())
+    assert e.value.variant == "UnsupportedOperation"
+
+
+# ------------------------------------------------------------------ the whole block
+def test_mamba_block_config0_f32(golden):
+    """Benchmark configuration 0: batch 1, L 100, d_model 64, d_state 16, expand 2, conv 4, f32, seed 0."""
+    from helixml_b200 import ops
+    w = synth.mamba_block_weights(0, 64, 16, 4, 2)
+    x = synth.uniform(0, "x", (1, 100, 64), -1, 1)
+    got = ops.mamba_block(to_dev(x), {k: to_dev(v) for k, v in w.items()}, 16, 4)
+    _status_ok()
+    ref = cbind.mamba_block(x, w, 16, 4)
+    assert fp32_tol_err(to_np(got), ref) <= FP32_TOL
+    assert fp32_tol_err(to_np(got), golden("mamba_block_cfg0.npz")["y"]) <= FP32_TOL
+
+
+@pytest.mark.parametrize("B,L,M", [(2, 64, 128), (1, 300, 768)])
+def test_mamba_block_bf16(B, L, M):
+    from helixml_b200 import ops
+    w = synth.mamba_block_weights(3, M, 16, 4, 2, init="0.02" if M == 768 else "kaiming")
+    big = ("W_in", "W_x", "W_dt", "W_out")
+    wq = {k: (synth.round_bf16(v) if k in big else v) for k, v in w.items()}
+    x = synth.round_bf16(synth.normal(3, "x", (B, L, M)))
+    dev = {k: to_dev(v, "bf16" if k in big else None) for k, v in wq.items()}
+    got = ops.mamba_block(to_dev(x, "bf16"), dev, 16, 4)
+    _status_ok()
+    ref = cbind.mamba_block(x, wq, 16, 4)
+    assert rel_l2(to_np(got), ref) <= BF16_TOL
+
+
+def test_exported_reference_block(golden):
+    """The exported nn::MambaBlock::forward (crates/nn/src/lib.rs:888-906) is out_proj(silu(gate(x))):
+    two Linear calls and a SiLU, reproduced with the GEMM's bias and SiLU epilogue."""
+    from helixml_b200 import _lib, ops
+    g = golden("mamba_exported_cfg0.npz")
+    h = ops.gemm(to_dev(g["x"]), to_dev(g["wg"]), to_dev(g["bg"]), epilogue=_lib.EPI_SILU, tensor_cores=False)
+    y = ops.gemm(h, to_dev(g["wo"]), to_dev(g["bo"]), tensor_cores=False)
+    assert fp32_tol_err(to_np(y), g["y"]) <= FP32_TOL

@@ -1,0 +1,246 @@
+"""GPU parity of the fused selective scan (through the C ABI) against the CPU oracle.
+
+fp32 gate:  max |got - ref| / (1 + |ref|) <= 1e-4   (the chunked/packed kernels reorder sums)
+bf16 gate:  relative L2 error <= 2e-2 against the fp32 oracle run on the same bf16-exact inputs."""
+import numpy as np
+import pytest
+
+from conftest import BF16_TOL, FP32_TOL, fp32_tol_err, rel_l2, to_dev, to_np
+from helixml_b200 import synth
+from oracle import cbind
+
+pytestmark = pytest.mark.gpu
+
+
+def run_gpu(inp, dtype, *, variant, lpc=0, geom=None, gate=True, skip=True, conv=True, conv_b=None, dt_bias=None,
+            softplus=True, state=False, seq_splits=0):
+    from helixml_b200 import ops
+    cast = "bf16" if dtype == "bf16" else None
+    out = ops.selective_scan(
+        to_dev(inp["x"], cast), to_dev(inp["dt"], cast), to_dev(inp["A"]), to_dev(inp["B"], cast), to_dev(inp["C"], cast),
+        D=to_dev(inp["D"]) if skip else None, z=to_dev(inp["z"], cast) if gate else None,
+        conv_w=to_dev(inp["conv_w"]) if conv else None, conv_b=to_dev(conv_b), dt_bias=to_dev(dt_bias),
+        dt_softplus=softplus, variant=variant, a_geometric=geom, lanes_per_channel=lpc, return_state=state,
+        seq_splits=seq_splits)
+    from helixml_b200 import _lib
+    assert _lib.device_status() == 0, "a bounded device-side wait ran out"
+    if state:
+        return to_np(out[0]), to_np(out[1])
+    return to_np(out)
+
+
+def run_ref(inp, *, gate=True, skip=True, conv=True, conv_b=None, dt_bias=None, softplus=True, state=False):
+    return cbind.selective_scan(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], D=inp["D"] if skip else None,
+                                z=inp["z"] if gate else None, conv_w=inp["conv_w"] if conv else None, conv_b=conv_b,
+                                dt_bias=dt_bias, dt_softplus=softplus, return_state=state)
+
+
+def check(got, ref, dtype):
+    if dtype == "bf16":
+        assert rel_l2(got, ref) <= BF16_TOL
+    else:
+        assert fp32_tol_err(got, ref) <= FP32_TOL
+
+
+SIMPLE, TILED, SEQSPLIT = 1, 2, 3
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_simple_kernel(dtype):
+    inp = synth.scan_inputs(31, 2, 50, 40, 16, 4, bf16=dtype == "bf16")
+    got, hg = run_gpu(inp, dtype, variant=SIMPLE, state=True)
+    ref, hr = run_ref(inp, state=True)
+    check(got, ref, dtype)
+    assert fp32_tol_err(hg, hr) <= FP32_TOL
+
+
+@pytest.mark.parametrize("d_state", [1, 8, 16, 24, 64])
+def test_simple_kernel_any_d_state(d_state):
+    inp = synth.scan_inputs(32, 1, 33, 9, d_state, 4, bf16=False)
+    check(run_gpu(inp, "f32", variant=SIMPLE), run_ref(inp), "f32")
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("lpc", [1, 2, 4])
+@pytest.mark.parametrize("geom", [True, False])
+def test_tiled_kernel(dtype, lpc, geom):
+    # L is not a multiple of the chunk, D not a multiple of the tile
+    inp = synth.scan_inputs(33, 2, 150, 72, 16, 4, bf16=dtype == "bf16")
+    got, hg = run_gpu(inp, dtype, variant=TILED, lpc=lpc, geom=geom, state=True)
+    ref, hr = run_ref(inp, state=True)
+    check(got, ref, dtype)
+    assert fp32_tol_err(hg, hr) <= FP32_TOL if dtype == "f32" else rel_l2(hg, hr) <= BF16_TOL
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_tiled_general_decay(dtype):
+    # an A that is not geometric: the caller's flag is 0 and every state takes its own exponential
+    inp = synth.scan_inputs(34, 1, 90, 64, 16, 4, bf16=dtype == "bf16")
+    inp["A"] = -np.exp(synth.uniform(34, "Alog", (64, 16), -1.0, 2.0)).astype(np.float32)
+    got = run_gpu(inp, dtype, variant=TILED, lpc=4)  # geom=None: detected on the host
+    check(got, run_ref(inp), dtype)
+
+
+def test_geometric_detection():
+    import torch
+    from helixml_b200 import ops
+    A = torch.from_numpy((-np.exp(synth.a_log_s4d_real(8, 16))).astype(np.float32)).cuda()
+    assert ops.check_geometric(A)
+    A[3, 5] *= 1.01
+    assert not ops.check_geometric(A)
+
+
+@pytest.mark.parametrize("L", [1, 2, 3, 4, 7, 31, 32, 33, 64])
+def test_short_and_ragged_sequences(L):
+    inp = synth.scan_inputs(35, 3, L, 16, 16, 4, bf16=False)
+    ref = run_ref(inp)
+    for variant, lpc in ((SIMPLE, 0), (TILED, 4), (TILED, 1)):
+        check(run_gpu(inp, "f32", variant=variant, lpc=lpc), ref, "f32")
+
+
+@pytest.mark.parametrize("K", [1, 2, 3, 4])
+def test_conv_taps_and_biases(K):
+    inp = synth.scan_inputs(36, 2, 45, 24, 16, K, bf16=False)
+    cb = synth.uniform(36, "cb", (24,), -0.3, 0.3)
+    db = synth.uniform(36, "db", (24,), -1.0, 1.0)
+    ref = run_ref(inp, conv_b=cb, dt_bias=db)
+    check(run_gpu(inp, "f32", variant=SIMPLE, conv_b=cb, dt_bias=db), ref, "f32")
+    check(run_gpu(inp, "f32", variant=TILED, lpc=2, conv_b=cb, dt_bias=db), ref, "f32")
+
+
+@pytest.mark.parametrize("gate,skip,conv,softplus", [(False, True, True, True), (True, False, True, True),
+                                                      (True, True, False, True), (True, True, True, False),
+                                                      (False, False, False, False)])
+def test_optional_terms(gate, skip, conv, softplus):
+    inp = synth.scan_inputs(37, 2, 40, 32, 16, 4, bf16=False)
+    if not softplus:
+        inp["dt"] = np.abs(inp["dt"]) * 0.05  # dt is used as given: keep it a sane step size
+    ref = run_ref(inp, gate=gate, skip=skip, conv=conv, softplus=softplus)
+    for variant, lpc in ((SIMPLE, 0), (TILED, 4), (TILED, 2), (TILED, 1)):
+        check(run_gpu(inp, "f32", variant=variant, lpc=lpc, gate=gate, skip=skip, conv=conv, softplus=softplus), ref, "f32")
+
+
+def test_softplus_identity_branch():
+    inp = synth.scan_inputs(38, 1, 8, 32, 16, 4, bf16=False)
+    inp["dt"][:] = np.linspace(15, 30, 8, dtype=np.float32)[None, :, None]  # crosses the v > 20 switch
+    inp["A"] *= 1e-3  # keep exp(dt*A) away from zero so the check is not vacuous
+    ref = run_ref(inp)
+    check(run_gpu(inp, "f32", variant=TILED, lpc=4, geom=True), ref, "f32")
+    binp = {k: (synth.round_bf16(v) if k in ("x", "dt", "z", "B", "C") else v) for k, v in inp.items()}
+    check(run_gpu(binp, "bf16", variant=TILED, lpc=4, geom=True), run_ref(binp), "bf16")
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_strided_views(dtype):
+    """x and z as the two halves of one [B, L, 2D] row, B and C as column slices of a wider row:
+    the layout the Mamba block hands to the scan."""
+    import torch
+    from helixml_b200 import ops
+    Bsz, L, D, N, R = 2, 70, 64, 16, 8
+    inp = synth.scan_inputs(39, Bsz, L, D, N, 4, bf16=dtype == "bf16")
+    cast = "bf16" if dtype == "bf16" else None
+    xz = torch.cat([to_dev(inp["x"], cast), to_dev(inp["z"], cast)], dim=2)
+    pad = torch.zeros((Bsz, L, R), dtype=xz.dtype, device="cuda")
+    dbc = torch.cat([pad, to_dev(inp["B"], cast), to_dev(inp["C"], cast)], dim=2)
+    ref = run_ref(inp)
+    for variant in (SIMPLE, TILED, 0):
+        y = ops.selective_scan(xz[:, :, :D], to_dev(inp["dt"], cast), to_dev(inp["A"]), dbc[:, :, R:R + N],
+                               dbc[:, :, R + N:], D=to_dev(inp["D"]), z=xz[:, :, D:], conv_w=to_dev(inp["conv_w"]),
+                               variant=variant)
+        check(to_np(y), ref, dtype)
+
+
+def test_auto_falls_back_on_unaligned_views():
+    """A view whose base is not 16-byte aligned cannot go through TMA: the tiled variant reports
+    UnsupportedOperation, AUTO runs the simple kernel instead."""
+    import torch
+    from helixml_b200 import _lib, ops
+    inp = synth.scan_inputs(40, 1, 20, 16, 16, 4, bf16=False)
+    wide = torch.zeros((1, 20, 17 + 16), dtype=torch.float32, device="cuda")
+    wide[:, :, 1:17] = to_dev(inp["x"])
+    xv = wide[:, :, 1:17]  # base offset 4 bytes, row stride 33 elements
+    args = (to_dev(inp["dt"]), to_dev(inp["A"]), to_dev(inp["B"]), to_dev(inp["C"]))
+    with pytest.raises(_lib.HxError) as e:
+        ops.selective_scan(xv, *args, variant=TILED)
+    assert e.value.variant == "UnsupportedOperation"
+    y = ops.selective_scan(xv, *args, variant=0)
+    ref = cbind.selective_scan(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"])
+    check(to_np(y), ref, "f32")
+
+
+@pytest.mark.parametrize("dtype,lpc", [("f32", 4), ("bf16", 4), ("bf16", 1)])
+@pytest.mark.parametrize("splits", [2, 3, 5])
+def test_sequence_split_with_carry(dtype, lpc, splits):
+    inp = synth.scan_inputs(41, 2, 300, 40, 16, 4, bf16=dtype == "bf16")
+    inp["dt"] -= 2.0  # small steps: the state remembers across segment boundaries, so a lost carry would show
+    if dtype == "bf16":
+        inp["dt"] = synth.round_bf16(inp["dt"])
+    got, hg = run_gpu(inp, dtype, variant=SEQSPLIT, lpc=lpc, seq_splits=splits, state=True)
+    ref, hr = run_ref(inp, state=True)
+    check(got, ref, dtype)
+    check(hg, hr, dtype)
+    # and it is the same function as the unsplit kernel
+    one = run_gpu(inp, dtype, variant=TILED, lpc=lpc)
+    assert np.max(np.abs(one - got)) <= (1e-5 if dtype == "f32" else 1e-1)
+
+
+def test_batch_rows_and_channels_are_independent():
+    """Running a subset of batch rows / channels alone gives the same numbers (bit for bit) as the
+    full launch: the property the multi-GPU sharding relies on."""
+    import torch
+    from helixml_b200 import ops
+    inp = synth.scan_inputs(42, 4, 96, 128, 16, 4, bf16=True)
+    dev = {k: to_dev(v, "bf16" if k in ("x", "dt", "z", "B", "C") else None) for k, v in inp.items()}
+    full = ops.selective_scan(dev["x"], dev["dt"], dev["A"], dev["B"], dev["C"], D=dev["D"], z=dev["z"],
+                              conv_w=dev["conv_w"], variant=TILED, lanes_per_channel=4)
+    rows = ops.selective_scan(dev["x"][1:3], dev["dt"][1:3], dev["A"], dev["B"][1:3], dev["C"][1:3], D=dev["D"],
+                              z=dev["z"][1:3], conv_w=dev["conv_w"], variant=TILED, lanes_per_channel=4)
+    assert torch.equal(full[1:3], rows)
+    sl = slice(64, 128)
+    chans = ops.selective_scan(dev["x"][:, :, sl], dev["dt"][:, :, sl], dev["A"][sl].contiguous(), dev["B"], dev["C"],
+                               D=dev["D"][sl].contiguous(), z=dev["z"][:, :, sl], conv_w=dev["conv_w"][sl].contiguous(),
+                               variant=TILED, lanes_per_channel=4)
+    assert torch.equal(full[:, :, sl], chans)
+
+
+@pytest.mark.parametrize("name,dtype", [("scan_f32_small.npz", "f32"), ("scan_bf16_small.npz", "bf16")])
+def test_golden_vectors(golden, name, dtype):
+    g = golden(name)
+    cb = g["conv_b"] if g["conv_b"].size else None
+    db = g["dt_bias"] if g["dt_bias"].size else None
+    gate = bool(int(g["gate"]))
+    for variant, lpc in ((SIMPLE, 0), (TILED, 4), (TILED, 2), (TILED, 1)):
+        got, hg = run_gpu(g, dtype, variant=variant, lpc=lpc, gate=gate, conv_b=cb, dt_bias=db, state=True)
+        check(got, g["y"], dtype)
+        check(hg, g["h_last"], dtype)
+
+
+def test_full_size_config2_sampled_chains():
+    """Benchmark configuration 2 at full size (batch 16, L 4096, d_inner 1536, bf16): the tiled kernel
+    agrees with the simple kernel everywhere and with the CPU oracle on sampled (batch, channel) chains."""
+    import torch
+    from helixml_b200 import ops
+    Bsz, L, D, N = 16, 4096, 1536, 16
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn((Bsz, L, D), device="cuda", generator=g).to(torch.bfloat16)
+    z = torch.randn((Bsz, L, D), device="cuda", generator=g).to(torch.bfloat16)
+    dt = (torch.rand((Bsz, L, D), device="cuda", generator=g) * 3 - 4).to(torch.bfloat16)
+    Bm = torch.randn((Bsz, L, N), device="cuda", generator=g).to(torch.bfloat16)
+    Cm = torch.randn((Bsz, L, N), device="cuda", generator=g).to(torch.bfloat16)
+    A = to_dev((-np.exp(synth.a_log_s4d_real(D, N))).astype(np.float32))
+    Dk = torch.ones(D, device="cuda")
+    cw = to_dev(synth.uniform(2, "conv_w", (D, 4), -0.5, 0.5))
+    outs = {}
+    for lpc in (1, 2, 4):
+        outs[lpc] = ops.selective_scan(x, dt, A, Bm, Cm, D=Dk, z=z, conv_w=cw, variant=TILED, lanes_per_channel=lpc)
+    base = ops.selective_scan(x, dt, A, Bm, Cm, D=Dk, z=z, conv_w=cw, variant=SIMPLE)
+    from helixml_b200 import _lib
+    assert _lib.device_status() == 0
+    for lpc, y in outs.items():
+        diff = (y.float() - base.float()).norm() / base.float().norm()
+        assert float(diff) <= 1e-2, (lpc, float(diff))
+    rows, sl = [0, 7, 15], slice(704, 768)
+    ref = cbind.selective_scan(to_np(x[rows][:, :, sl]), to_np(dt[rows][:, :, sl]), to_np(A[sl]), to_np(Bm[rows]),
+                               to_np(Cm[rows]), D=to_np(Dk[sl]), z=to_np(z[rows][:, :, sl]), conv_w=to_np(cw[sl]))
+    for lpc, y in outs.items():
+        assert rel_l2(to_np(y[rows][:, :, sl]), ref) <= BF16_TOL
