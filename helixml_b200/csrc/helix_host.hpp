@@ -1,0 +1,251 @@
+// C++ host layer above the C ABI: the reference's tensor/module interface for the state-space path,
+// restated for device-resident tensors.
+//
+//   reference (Rust)                                         here (C++)
+//   tensor_core::Device           device.rs:8-60             helix::Device
+//   tensor_core::DType            dtype.rs:8-37              helix::DType (+ BF16)
+//   tensor_core::Shape            shape.rs:8-97              helix::Shape
+//   tensor_core::TensorError      error.rs:7-37              helix::TensorError (code = hx_status)
+//   Result<T>                     error.rs:40                helix::Result<T>
+//   Tensor / TensorRandom subset  tensor.rs:7-59,212-233     helix::DeviceTensor
+//   nn::Module<T>                 crates/nn/src/lib.rs:20-39 helix::Module
+//   nn::Linear / RMSNorm          lib.rs:60-218, 222-327     helix::Linear / helix::RMSNorm
+//   nn::ssm::S4Block              crates/nn/src/ssm.rs:14    helix::S4Block
+//   nn::MambaBlock                lib.rs:820-971             helix::MambaBlock
+//   examples/ssm_byte_lm model    main.rs:104-130            helix::ByteLM
+//
+// Error behaviour follows the reference: shape/dtype/device problems are returned as errors, never
+// thrown across the ABI and never trapped.  forward() takes &self and launches on the tensor's device
+// on the current (default) stream; modules are immutable during forward and may be shared by threads.
+#pragma once
+
+#include <memory>
+#include <string>
+#include <utility>
+#include <vector>
+
+#include "../../include/helix_b200.h"
+
+namespace helix {
+
+enum class DType : int { F32 = HX_F32, BF16 = HX_BF16, U8 = HX_U8 };
+inline size_t dtype_size(DType d) { return d == DType::F32 ? 4 : d == DType::BF16 ? 2 : 1; }
+
+struct Device {
+    enum Kind { Cpu, Cuda } kind = Cpu;
+    int id = 0;
+    static Device cpu() { return {Cpu, 0}; }
+    static Device cuda(int id) { return {Cuda, id}; }
+    bool is_cpu() const { return kind == Cpu; }
+    bool is_cuda() const { return kind == Cuda; }
+    bool operator==(const Device &o) const { return kind == o.kind && (kind == Cpu || id == o.id); }
+    std::string to_string() const { return kind == Cpu ? "cpu" : "cuda:" + std::to_string(id); }
+};
+
+struct TensorError {
+    hx_status code = HX_OK;
+    std::string message;
+};
+
+// Either a value or a TensorError.
+template <typename T> class Result {
+  public:
+    Result(T v) : ok_(true), value_(std::move(v)) {}
+    Result(TensorError e) : ok_(false), error_(std::move(e)) {}
+    bool ok() const { return ok_; }
+    T &value() { return value_; }
+    const T &value() const { return value_; }
+    const TensorError &error() const { return error_; }
+
+  private:
+    bool ok_;
+    T value_{};
+    TensorError error_;
+};
+struct Unit {};
+
+class Shape {
+  public:
+    Shape() = default;
+    explicit Shape(std::vector<int64_t> dims) : dims_(std::move(dims)) {}
+    size_t ndim() const { return dims_.size(); }
+    int64_t dim(size_t i) const { return dims_[i]; }
+    int64_t numel() const {
+        int64_t n = 1;
+        for (auto d : dims_) n *= d;
+        return n;
+    }
+    const std::vector<int64_t> &as_slice() const { return dims_; }
+    bool operator==(const Shape &o) const { return dims_ == o.dims_; }
+
+  private:
+    std::vector<int64_t> dims_;
+};
+
+// A dense, row-major tensor whose storage lives in device memory and is freed with its last owner.
+// Copying a DeviceTensor shares the storage; clone() makes a deep copy (the reference's Clone).
+class DeviceTensor {
+  public:
+    DeviceTensor() = default;
+    static Result<DeviceTensor> empty(const Shape &shape, DType dtype, const Device &device);
+    static Result<DeviceTensor> zeros(const Shape &shape, DType dtype, const Device &device);
+    // host data is fp32 (or bytes for U8); it is converted to `dtype` on the way in
+    static Result<DeviceTensor> from_host_f32(const float *data, const Shape &shape, DType dtype, const Device &device);
+    static Result<DeviceTensor> from_host_u8(const uint8_t *data, const Shape &shape, const Device &device);
+    Result<Unit> copy_from_host_f32(const float *data, int64_t n);
+    Result<Unit> to_host_f32(float *out, int64_t n) const;  // widens bf16
+    Result<DeviceTensor> clone() const;
+    Result<DeviceTensor> reshape(const Shape &shape) const;  // shares storage
+
+    const Shape &shape() const { return shape_; }
+    DType dtype() const { return dtype_; }
+    const Device &device() const { return device_; }
+    size_t ndim() const { return shape_.ndim(); }
+    int64_t numel() const { return shape_.numel(); }
+    void *data() const { return ptr_; }
+    bool defined() const { return storage_ != nullptr || shape_.numel() == 0; }
+
+  private:
+    std::shared_ptr<void> storage_;
+    void *ptr_ = nullptr;
+    Shape shape_;
+    DType dtype_ = DType::F32;
+    Device device_;
+};
+
+// crates/nn/src/lib.rs:20-39 (forward_with_autograd is the training path and is not part of this build)
+class Module {
+  public:
+    virtual ~Module() = default;
+    virtual Result<DeviceTensor> forward(const DeviceTensor &input) const = 0;
+    virtual std::vector<const DeviceTensor *> parameters() const = 0;
+    virtual std::vector<DeviceTensor *> parameters_mut() = 0;
+    virtual const Device &device() const = 0;
+    // Called after parameters were written through parameters_mut(): lets a module refresh what it
+    // derives from them (for example whether A is geometric).
+    virtual Result<Unit> parameters_updated() { return Unit{}; }
+    virtual const char *name() const = 0;
+};
+
+// nn::Linear (crates/nn/src/lib.rs:60-134): weight [out, in] ~ N(0, sqrt(2/in)), bias zeros; y = x W^T + b.
+class Linear : public Module {
+  public:
+    static Result<std::unique_ptr<Linear>> create(int64_t in_features, int64_t out_features, bool bias, DType dtype,
+                                                  const Device &device);
+    Result<DeviceTensor> forward(const DeviceTensor &input) const override;
+    std::vector<const DeviceTensor *> parameters() const override;
+    std::vector<DeviceTensor *> parameters_mut() override;
+    const Device &device() const override { return device_; }
+    const char *name() const override { return "Linear"; }
+    DeviceTensor weight, bias;  // bias is fp32
+    bool has_bias = false;
+
+  private:
+    Device device_;
+};
+
+// nn::RMSNorm (crates/nn/src/lib.rs:222-285): weight ones [d_model], eps.
+class RMSNorm : public Module {
+  public:
+    static Result<std::unique_ptr<RMSNorm>> create(int64_t d_model, float eps, const Device &device);
+    Result<DeviceTensor> forward(const DeviceTensor &input) const override;
+    std::vector<const DeviceTensor *> parameters() const override { return {&weight}; }
+    std::vector<DeviceTensor *> parameters_mut() override { return {&weight}; }
+    const Device &device() const override { return device_; }
+    const char *name() const override { return "RMSNorm"; }
+    DeviceTensor weight;
+    float eps = 1e-5f;
+
+  private:
+    Device device_;
+};
+
+// nn::ssm::S4Block (crates/nn/src/ssm.rs:14-186).  Parameters, in the reference's order
+// (ssm.rs:275-277): A_real [N], A_imag [N], B [N, M], C [M, N], D [M], delta [M], Lambda [N].
+//   forward_ssm(u [M, L])  -- the reference's recurrence with dt = 0.1, output buffer [L, M]
+//   forward(u [B, L, M] or [L, M]) -- the per-channel diagonal form (abar = exp(delta A), bbar = delta B)
+//                                     with A_diag [M, N], B_diag [M, N], C_diag [M, N] as extra parameters.
+class S4Block : public Module {
+  public:
+    static Result<std::unique_ptr<S4Block>> create(int64_t d_model, int64_t d_state, const Device &device);
+    Result<DeviceTensor> forward(const DeviceTensor &input) const override;
+    Result<DeviceTensor> forward_ssm(const DeviceTensor &input) const;
+    std::vector<const DeviceTensor *> parameters() const override;
+    std::vector<DeviceTensor *> parameters_mut() override;
+    const Device &device() const override { return device_; }
+    const char *name() const override { return "S4Block"; }
+    DeviceTensor A_real, A_imag, B, C, D, delta, Lambda;  // the reference's seven
+    DeviceTensor A_diag, B_diag, C_diag;                   // per-channel diagonal form
+    int64_t d_model = 0, d_state = 0;
+
+  private:
+    Device device_;
+};
+
+// nn::MambaBlock (crates/nn/src/lib.rs:820-971): new(d_model, d_state, d_conv, expand, device), forward.
+// The selective-scan block the benchmark configuration describes; parameters, in order:
+//   in_proj.weight [2E, M], conv_w [E, K], conv_b [E], x_proj.weight [R+2N, E], dt_proj.weight [E, R],
+//   dt_proj.bias [E], A [E, N] (= -exp(A_log), A_log[d,n] = log(n+1)), D [E] (ones), out_proj.weight [M, E]
+// with E = expand * d_model, R = ceil(d_model / 16).  The reference's own B_proj / C_proj of shape
+// [N*E, E] (lib.rs:864-865) are never read by its forward and are not reproduced.
+class MambaBlock : public Module {
+  public:
+    static Result<std::unique_ptr<MambaBlock>> create(int64_t d_model, int64_t d_state, int64_t d_conv, int64_t expand,
+                                                      DType dtype, const Device &device);
+    Result<DeviceTensor> forward(const DeviceTensor &input) const override;
+    // forward into caller-provided buffers (no allocation): x and out are [batch*seq_len, d_model]
+    Result<Unit> forward_into(const void *x, void *out, int64_t batch, int64_t seq_len, void *workspace,
+                              size_t workspace_bytes, void *stream) const;
+    size_t workspace_bytes(int64_t batch, int64_t seq_len) const;
+    std::vector<const DeviceTensor *> parameters() const override;
+    std::vector<DeviceTensor *> parameters_mut() override;
+    Result<Unit> parameters_updated() override;
+    const Device &device() const override { return device_; }
+    const char *name() const override { return "MambaBlock"; }
+    DeviceTensor W_in, conv_w, conv_b, W_x, W_dt, b_dt, A, D, W_out;
+    int64_t d_model = 0, d_state = 0, d_conv = 0, expand = 0, d_inner = 0, dt_rank = 0;
+    DType dtype = DType::F32;
+    bool a_geometric = false;
+
+  private:
+    Device device_;
+};
+
+// Byte-level LM: tied embedding [256, M], n_layer x (RMSNorm -> MambaBlock -> residual add), final
+// RMSNorm, logits = h . emb^T.  forward takes U8 tokens [B, L] and returns logits [B, L, 256].
+class ByteLM : public Module {
+  public:
+    static Result<std::unique_ptr<ByteLM>> create(int64_t n_layer, int64_t d_model, int64_t d_state, int64_t d_conv,
+                                                  int64_t expand, DType dtype, const Device &device);
+    ~ByteLM() override;
+    Result<DeviceTensor> forward(const DeviceTensor &tokens) const override;
+    // The serving call: tokens from (pinned) host memory, logits back to (pinned) host memory in the
+    // model dtype.  Activations live in buffers sized on first use for (batch, seq_len) and kept.
+    Result<Unit> forward_host(const uint8_t *tokens_host, void *logits_host, int64_t batch, int64_t seq_len, void *stream);
+    // Same on device buffers: tokens_dev [B*L] u8, logits_dev [B*L, 256] model dtype.
+    Result<Unit> forward_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream);
+    int64_t launches_per_forward() const;
+    std::vector<const DeviceTensor *> parameters() const override;
+    std::vector<DeviceTensor *> parameters_mut() override;
+    Result<Unit> parameters_updated() override;
+    const Device &device() const override { return device_; }
+    const char *name() const override { return "ByteLM"; }
+    DeviceTensor embedding, norm_f;
+    std::vector<std::unique_ptr<RMSNorm>> norms;
+    std::vector<std::unique_ptr<MambaBlock>> blocks;
+    int64_t d_model = 0;
+    DType dtype = DType::F32;
+    float eps = 1e-5f;
+
+  private:
+    Result<Unit> ensure_buffers(int64_t batch, int64_t seq_len);
+    Device device_;
+    struct Buffers;
+    Buffers *buf_ = nullptr;
+};
+
+// Seed of the parameter initialisers (the reference draws from an unseeded thread_rng,
+// crates/backend-cpu/src/lib.rs:1209; here initialisation is reproducible).
+void manual_seed(uint64_t seed);
+
+}  // namespace helix
