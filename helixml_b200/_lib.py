@@ -96,6 +96,32 @@ _PROTOS = {
     "hx_silu_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "hx_mamba_block_fwd": (C.c_int, [C.POINTER(MambaBlockArgs), C.c_void_p]),
     "hx_mamba_block_workspace_bytes": (C.c_int, [C.POINTER(MambaBlockArgs), C.POINTER(C.c_size_t)]),
+    # ---- module-level API
+    "hx_manual_seed": (None, [C.c_uint64]),
+    "hx_tensor_from_host": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_tensor_from_host_u8": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_tensor_to_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
+    "hx_tensor_copy_from_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64]),
+    "hx_tensor_info": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int64), C.POINTER(C.c_int32),
+                                 C.POINTER(C.c_int32)]),
+    "hx_tensor_data": (C.c_void_p, [C.c_void_p]),
+    "hx_tensor_free": (None, [C.c_void_p]),
+    "hx_mamba_block_new": (C.c_int, [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_s4_block_new": (C.c_int, [C.c_int64, C.c_int64, C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_linear_new": (C.c_int, [C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_rmsnorm_new": (C.c_int, [C.c_int64, C.c_float, C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_byte_lm_new": (C.c_int, [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
+                                 C.POINTER(C.c_void_p)]),
+    "hx_module_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "hx_s4_block_forward_ssm": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "hx_byte_lm_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
+    "hx_byte_lm_forward_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
+    "hx_byte_lm_launches_per_forward": (C.c_int64, [C.c_void_p]),
+    "hx_module_num_parameters": (C.c_int32, [C.c_void_p]),
+    "hx_module_parameter": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_module_parameters_updated": (C.c_int, [C.c_void_p]),
+    "hx_module_name": (C.c_char_p, [C.c_void_p]),
+    "hx_module_free": (None, [C.c_void_p]),
 }
 
 _lib = None

@@ -92,8 +92,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                int64_t ldc, int M, int N, int K, int vec_ok) {
     using Cfg = TcCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
-    extern __shared__ char smem_raw[];
-    char *smem = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(16) char smem_raw[];
+    char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // keeps the shared address space
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * Cfg::STAGE_BYTES);
     // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]; then the TMEM base and the abort flag
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);

@@ -125,10 +125,11 @@ struct TiledParams {
     int epoch;
 };
 
-template <typename T, int LPC_, bool GEOM_, int TC_, int STAGES_>
+template <typename T, int LPC_, bool GEOM_, int TC_, int STAGES_, bool STD_>
 struct TiledCfg {
     static constexpr int LPC = LPC_;
     static constexpr bool GEOM = GEOM_;
+    static constexpr bool STD = STD_;  // conv (4 taps), softplus and gate all present: no runtime flag tests
     static constexpr bool FAST = sizeof(T) == 2;  // bf16 I/O uses the special-function approximations
     static constexpr int TC = TC_;                // time steps per chunk
     static constexpr int STAGES = STAGES_;
@@ -142,20 +143,24 @@ struct TiledCfg {
     static constexpr int RPI = 32 / PPR;          // rows one warp-wide access covers
     static constexpr int TS = RPI * NCH;          // time steps per sub-chunk (8 for bf16, 16 for fp32)
     static constexpr int THREADS = (NW + 1) * 32;
-    static constexpr bool TWO_REC = GEOM && LPC > 1;
+    static constexpr bool POW4 = GEOM && LPC == 4;  // records carry r, r^2, r^3, r^4 as separate planes
     // shared memory carve-up (bytes)
     static constexpr int X_BYTES = ((TC + 3) * 128 + 1023) / 1024 * 1024;
     static constexpr int ROW_BYTES = TC * 128;
-    static constexpr int BC_BYTES = TC * 16 * ES;
-    static constexpr int STAGE_BYTES = X_BYTES + 2 * ROW_BYTES + 2 * ((BC_BYTES + 127) / 128 * 128);
+    static constexpr int BC_BYTES = (TC * 16 * ES + 127) / 128 * 128;  // one raw B or C tile
+    static constexpr int BCF_BYTES = TC * 16 * 4;                       // one widened (fp32) B or C tile
+    static constexpr int STAGE_BYTES = X_BYTES + 2 * ROW_BYTES + 2 * BC_BYTES + 2 * BCF_BYTES;
     static constexpr int OUT_BYTES = TC * 128;
-    static constexpr int REC_BYTES = TS * CW * 16 * (TWO_REC ? 2 : 1);
-    static constexpr int BCF_BYTES = TS * 16 * 4 * 2;
-    static constexpr int WARP_BYTES = REC_BYTES + BCF_BYTES;
+    // per-warp records of one sub-chunk: RX {decay, x} and GS {gate, skip} as float2 per point, plus
+    // (POW4) four planes of powers, each padded by 8 floats so that the planes fall in different banks
+    static constexpr int PLANE_FLOATS = TS * CW + 8;
+    static constexpr int REC_BYTES = 2 * TS * CW * 8 + (POW4 ? 4 * PLANE_FLOATS * 4 : 0);
+    static constexpr int WARP_BYTES = (REC_BYTES + 127) / 128 * 128;
     static constexpr int BAR_BYTES = 128;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BYTES + NW * WARP_BYTES + BAR_BYTES + 1024;
     static_assert(TC % TS == 0, "chunk must hold whole sub-chunks");
     static_assert(DT % CW == 0 && NW >= 1, "tile must hold whole warps");
+    static_assert(3 * STAGES + 4 <= BAR_BYTES / 8, "barrier area too small");
 };
 
 // byte offset of (row, channel) inside a 128-byte-wide tile written by TMA with the 128-byte
@@ -187,20 +192,27 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                   const TiledParams p) {
     constexpr int LPC = Cfg::LPC, S = Cfg::S, CW = Cfg::CW, NW = Cfg::NW, TC = Cfg::TC, TS = Cfg::TS;
     constexpr int ES = Cfg::ES, DT = Cfg::DT, STAGES = Cfg::STAGES, NCH = Cfg::NCH, PPR = Cfg::PPR;
-    constexpr bool GEOM = Cfg::GEOM, FAST = Cfg::FAST;
+    constexpr bool GEOM = Cfg::GEOM, FAST = Cfg::FAST, POW4 = Cfg::POW4, STD = Cfg::STD;
+    const bool has_conv = STD || p.K > 0, has_z = STD || p.has_z, use_softplus = STD || p.dt_softplus;
 
-    extern __shared__ char smem_raw[];
-    char *smem = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(16) char smem_raw[];
+    // 1024-byte alignment by pointer arithmetic (an integer round trip would turn every access into a
+    // generic load)
+    char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     char *stage_base = smem;
     char *out_base = stage_base + STAGES * Cfg::STAGE_BYTES;
     char *warp_base = out_base + 2 * Cfg::OUT_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(warp_base + NW * Cfg::WARP_BYTES);
-    // barriers: full[STAGES], empty[STAGES], out_full[2], out_empty[2]
+    // barriers: full[STAGES] (TMA landed), ready[STAGES] (B/C widened), empty[STAGES], out_full[2], out_empty[2]
     const uint32_t bar0 = smem_u32(bars);
     auto bar_full = [&](int s) { return bar0 + 8u * s; };
-    auto bar_empty = [&](int s) { return bar0 + 8u * (STAGES + s); };
-    auto bar_out_full = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
-    auto bar_out_empty = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+    auto bar_ready = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto bar_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };
+    auto bar_out_full = [&](int b) { return bar0 + 8u * (3 * STAGES + b); };
+    auto bar_out_empty = [&](int b) { return bar0 + 8u * (3 * STAGES + 2 + b); };
+    // offsets inside a stage
+    constexpr int OFF_DT = Cfg::X_BYTES, OFF_Z = OFF_DT + Cfg::ROW_BYTES, OFF_B = OFF_Z + Cfg::ROW_BYTES,
+                  OFF_C = OFF_B + Cfg::BC_BYTES, OFF_BF = OFF_C + Cfg::BC_BYTES, OFF_CF = OFF_BF + Cfg::BCF_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, b = blockIdx.y, seg = blockIdx.z;
@@ -212,6 +224,7 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full(s), 1);
+            mbar_init(bar_ready(s), 1);
             mbar_init(bar_empty(s), NW);
         }
         for (int k = 0; k < 2; ++k) {
@@ -222,60 +235,127 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
     __syncthreads();
 
-    const uint32_t stage_tx = (TC + 3) * 128 + TC * 128 * (p.has_z ? 2 : 1) + 2 * TC * 16 * ES;
+    const uint32_t stage_tx = (TC + 3) * 128 + TC * 128 * (has_z ? 2 : 1) + 2 * TC * 16 * ES;
 
     if (warp == NW) {
         // ================================================================ producer warp
-        if (lane != 0) return;
-        tma_prefetch_desc(&tm_x);
-        tma_prefetch_desc(&tm_dt);
-        tma_prefetch_desc(&tm_B);
-        tma_prefetch_desc(&tm_C);
-        tma_prefetch_desc(&tm_y);
-        if (p.has_z) tma_prefetch_desc(&tm_z);
+        // lane 0 drives TMA (loads, stores) and the barriers; all 32 lanes widen each stage's B and C
+        // tiles to fp32 once for the whole CTA, one chunk ahead of the consumers.
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_x);
+            tma_prefetch_desc(&tm_dt);
+            tma_prefetch_desc(&tm_B);
+            tma_prefetch_desc(&tm_C);
+            tma_prefetch_desc(&tm_y);
+            if (has_z) tma_prefetch_desc(&tm_z);
+        }
         auto issue = [&](int i) {
             const int s = i % STAGES;
             const int t0 = t_seg0 + i * TC;
             const uint32_t sb = smem_u32(stage_base + s * Cfg::STAGE_BYTES);
             mbar_expect_tx(bar_full(s), stage_tx);
             tma_load_3d(sb, &tm_x, bar_full(s), d0, t0 - 3, b);
-            tma_load_3d(sb + Cfg::X_BYTES, &tm_dt, bar_full(s), d0, t0, b);
-            if (p.has_z) tma_load_3d(sb + Cfg::X_BYTES + Cfg::ROW_BYTES, &tm_z, bar_full(s), d0, t0, b);
-            tma_load_3d(sb + Cfg::X_BYTES + 2 * Cfg::ROW_BYTES, &tm_B, bar_full(s), 0, t0, b);
-            tma_load_3d(sb + Cfg::X_BYTES + 2 * Cfg::ROW_BYTES + (Cfg::BC_BYTES + 127) / 128 * 128, &tm_C,
-                        bar_full(s), 0, t0, b);
+            tma_load_3d(sb + OFF_DT, &tm_dt, bar_full(s), d0, t0, b);
+            if (has_z) tma_load_3d(sb + OFF_Z, &tm_z, bar_full(s), d0, t0, b);
+            tma_load_3d(sb + OFF_B, &tm_B, bar_full(s), 0, t0, b);
+            tma_load_3d(sb + OFF_C, &tm_C, bar_full(s), 0, t0, b);
         };
         int issued = 0;
-        for (; issued < STAGES && issued < nchunks; ++issued) issue(issued);
+        if (lane == 0)
+            for (; issued < STAGES && issued < nchunks; ++issued) issue(issued);
         int fail_code = 0;
-        for (int i = 0; i < nchunks; ++i) {
-            const int ob = i & 1;
-            if (!mbar_wait(bar_out_full(ob), (i >> 1) & 1)) { fail_code = kWaitOutFull; break; }
-            tma_store_3d(&tm_y, smem_u32(out_base + ob * Cfg::OUT_BYTES), d0, t_seg0 + i * TC, b);
-            tma_store_commit();
-            if (issued < nchunks) {
-                // chunk i has been consumed (its out tile is complete), so its stage is free
-                if (!mbar_wait(bar_empty(i % STAGES), (i / STAGES) & 1)) { fail_code = kWaitEmpty; break; }
-                issue(issued);
-                ++issued;
+        // step i: widen chunk i (if any), then retire chunk i-1 (store its y tile, refill its stage)
+        for (int i = 0; i <= nchunks; ++i) {
+            if (i < nchunks) {
+                const int s = i % STAGES;
+                const bool ok = mbar_wait(bar_full(s), (i / STAGES) & 1);
+                if (!__all_sync(0xffffffffu, ok)) { fail_code = kWaitFull; break; }
+                char *st = stage_base + s * Cfg::STAGE_BYTES;
+                // TC*16 elements per array; lane handles 8 consecutive elements per round
+                constexpr int ROUNDS = TC * 16 * 2 / (32 * 8);
+#pragma unroll
+                for (int r = 0; r < ROUNDS; ++r) {
+                    const int e0 = (r * 32 + lane) * 8;  // over both arrays
+                    const int arr = e0 / (TC * 16), ea = e0 % (TC * 16);
+                    const int row = ea / 16, n0 = ea % 16;
+                    const char *src = st + (arr ? OFF_C : OFF_B) + (row * 16 + n0) * ES;
+                    float vals[8];
+                    if constexpr (ES == 2) {
+                        const uint4 raw = *reinterpret_cast<const uint4 *>(src);
+                        const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            vals[2 * k] = __uint_as_float(wds[k] << 16);
+                            vals[2 * k + 1] = __uint_as_float(wds[k] & 0xffff0000u);
+                        }
+                    } else {
+                        const float4 f0 = *reinterpret_cast<const float4 *>(src);
+                        const float4 f1 = *reinterpret_cast<const float4 *>(src + 16);
+                        vals[0] = f0.x; vals[1] = f0.y; vals[2] = f0.z; vals[3] = f0.w;
+                        vals[4] = f1.x; vals[5] = f1.y; vals[6] = f1.z; vals[7] = f1.w;
+                    }
+                    // lane q of a channel finds its S states (n = q + LPC*j) contiguous at [row][q*S + j]
+                    float *dst = reinterpret_cast<float *>(st + (arr ? OFF_CF : OFF_BF)) + row * 16;
+#pragma unroll
+                    for (int qq = 0; qq < LPC; ++qq) {
+                        // elements n0+qq, n0+qq+LPC, ... land at j = (n0+qq)/LPC + m
+                        constexpr int PER = 8 / LPC;
+                        float *d2 = dst + qq * S + n0 / LPC;
+                        if constexpr (PER == 8) {
+                            *reinterpret_cast<float4 *>(d2) = make_float4(vals[0], vals[1], vals[2], vals[3]);
+                            *reinterpret_cast<float4 *>(d2 + 4) = make_float4(vals[4], vals[5], vals[6], vals[7]);
+                        } else if constexpr (PER == 4) {
+                            *reinterpret_cast<float4 *>(d2) = make_float4(vals[qq], vals[qq + 2], vals[qq + 4], vals[qq + 6]);
+                        } else {
+                            *reinterpret_cast<float2 *>(d2) = make_float2(vals[qq], vals[qq + 4]);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_ready(s));
             }
-            tma_store_wait_read<1>();
-            if (i >= 1) mbar_arrive(bar_out_empty((i - 1) & 1));
+            if (i >= 1) {
+                const int j = i - 1, ob = j & 1;
+                int fc = 0;
+                if (lane == 0) {
+                    if (!mbar_wait(bar_out_full(ob), (j >> 1) & 1)) {
+                        fc = kWaitOutFull;
+                    } else {
+                        tma_store_3d(&tm_y, smem_u32(out_base + ob * Cfg::OUT_BYTES), d0, t_seg0 + j * TC, b);
+                        tma_store_commit();
+                        if (issued < nchunks) {
+                            // chunk j has been consumed (its out tile is complete), so its stage is free
+                            if (!mbar_wait(bar_empty(j % STAGES), (j / STAGES) & 1)) {
+                                fc = kWaitEmpty;
+                            } else {
+                                issue(issued);
+                                ++issued;
+                            }
+                        }
+                        tma_store_wait_read<1>();
+                        if (j >= 1) mbar_arrive(bar_out_empty((j - 1) & 1));
+                    }
+                }
+                fc = __shfl_sync(0xffffffffu, fc, 0);
+                if (fc) { fail_code = fc; break; }
+            }
         }
-        tma_store_wait_all<0>();
-        if (fail_code) {
-            atomicOr(&g_wait_status, fail_code);
-            // let loads already in flight land before the CTA's shared memory goes away
-            for (int i = 0; i < issued; ++i) mbar_wait(bar_full(i % STAGES), (i / STAGES) & 1);
+        if (lane == 0) {
+            tma_store_wait_all<0>();
+            if (fail_code) {
+                atomicOr(&g_wait_status, fail_code);
+                // let loads already in flight land before the CTA's shared memory goes away
+                for (int i = 0; i < issued; ++i) mbar_wait(bar_full(i % STAGES), (i / STAGES) & 1);
+            }
         }
         return;
     }
 
     // ==================================================================== consumer warps
     char *wsm = warp_base + warp * Cfg::WARP_BYTES;
-    float4 *rec0 = reinterpret_cast<float4 *>(wsm);                        // [TS][CW]
-    float4 *rec1 = reinterpret_cast<float4 *>(wsm + TS * CW * 16);         // [TS][CW] (TWO_REC only)
-    float *bcf = reinterpret_cast<float *>(wsm + Cfg::REC_BYTES);          // B: [TS][16], then C: [TS][16]
+    float2 *recRX = reinterpret_cast<float2 *>(wsm);                  // [TS][CW] {decay (r or dt), x}
+    float2 *recGS = recRX + TS * CW;                                   // [TS][CW] {gate, skip}
+    float *recP = reinterpret_cast<float *>(recGS + TS * CW);          // POW4: 4 planes [TS][CW] (+8 pad)
 
     // ---- point-wise phase: this lane's channel pair
     const int pj = lane % PPR, rs = lane / PPR;
@@ -338,17 +418,30 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         }
     }
 
+    // byte offsets of this lane's loads inside a sub-chunk, swizzle included.  A sub-chunk starts at a
+    // row that is a multiple of 8, so the swizzle phase depends on the lane and the pass only.
+    int xoff[NCH][4], doff[NCH];
+#pragma unroll
+    for (int pass = 0; pass < NCH; ++pass) {
+        const int row = rs * NCH + pass;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) xoff[pass][j] = swz<ES>(row + j, pch);
+        doff[pass] = swz<ES>(row, pch);
+    }
+    // out-tile offsets of the rows this lane finalises (row = grp*LPC + q inside a sub-chunk)
+    int yoff[TS / LPC];
+#pragma unroll
+    for (int grp = 0; grp < TS / LPC; ++grp) yoff[grp] = swz<ES>(grp * LPC + q, warp * CW + c);
+
     for (int i = 0; i < nchunks; ++i) {
         const int s = i % STAGES, ob = i & 1;
-        if (!mbar_wait(bar_full(s), (i / STAGES) & 1)) {
+        if (!mbar_wait(bar_ready(s), (i / STAGES) & 1)) {
             if (lane == 0) atomicOr(&g_wait_status, kWaitFull);
             return;
         }
         const char *sx = stage_base + s * Cfg::STAGE_BYTES;
-        const char *sdt = sx + Cfg::X_BYTES;
-        const char *sz = sdt + Cfg::ROW_BYTES;
-        const char *sB = sz + Cfg::ROW_BYTES;
-        const char *sC = sB + (Cfg::BC_BYTES + 127) / 128 * 128;
+        const float *sBf = reinterpret_cast<const float *>(sx + OFF_BF);
+        const float *sCf = reinterpret_cast<const float *>(sx + OFF_CF);
         char *so = out_base + ob * Cfg::OUT_BYTES;
         const int t_chunk0 = t_seg0 + i * TC;
 
@@ -356,33 +449,42 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         for (int sub = 0; sub < TC / TS; ++sub) {
             const int tl0 = sub * TS;  // chunk-local first step of this sub-chunk
             if (t_chunk0 + tl0 >= t_seg1) break;
+            const char *sxs = sx + tl0 * 128;       // x tile rows of this sub-chunk (row 0 = 3 steps back)
+            const char *sds = sxs + OFF_DT, *szs = sxs + OFF_Z;
+            const bool tail = t_chunk0 + tl0 + TS > t_seg1;  // some rows lie past the end of the sequence
             // ------------------------------------------------------------ point-wise phase
 #pragma unroll
             for (int pass = 0; pass < NCH; ++pass) {
                 const int row = rs * NCH + pass;  // 0..TS-1
-                const int tl = tl0 + row;
-                const bool live = (t_chunk0 + tl) < t_seg1;
                 float2 u;
                 {
-                    const float2 x0 = ld_pair<T>(sx, swz<ES>(tl + 3, pch));
-                    if (p.K > 0) {
+                    const float2 x0 = ld_pair<T>(sxs, xoff[pass][3]);
+                    if (has_conv) {
                         float2 acc = cbias;
-                        acc = fma2(cw[0], ld_pair<T>(sx, swz<ES>(tl + 0, pch)), acc);
-                        acc = fma2(cw[1], ld_pair<T>(sx, swz<ES>(tl + 1, pch)), acc);
-                        acc = fma2(cw[2], ld_pair<T>(sx, swz<ES>(tl + 2, pch)), acc);
+                        acc = fma2(cw[0], ld_pair<T>(sxs, xoff[pass][0]), acc);
+                        acc = fma2(cw[1], ld_pair<T>(sxs, xoff[pass][1]), acc);
+                        acc = fma2(cw[2], ld_pair<T>(sxs, xoff[pass][2]), acc);
                         acc = fma2(cw[3], x0, acc);
-                        u = make_float2(silu_sel<FAST>(acc.x), silu_sel<FAST>(acc.y));
+                        if constexpr (FAST) {
+                            const float2 t = mul2(acc, splat2(-kLog2e));
+                            const float2 den = add2(make_float2(ex2_approx(t.x), ex2_approx(t.y)), splat2(1.f));
+                            u = mul2(acc, make_float2(rcp_approx(den.x), rcp_approx(den.y)));
+                        } else {
+                            u = make_float2(silu_acc(acc.x), silu_acc(acc.y));
+                        }
                     } else {
                         u = x0;
                     }
                 }
-                const float2 v = add2(ld_pair<T>(sdt, swz<ES>(tl, pch)), dbias);
+                const float2 v = add2(ld_pair<T>(sds, doff[pass]), dbias);
                 float2 dtv;
-                if (p.dt_softplus) {
+                if (use_softplus) {
                     if constexpr (FAST) {
-                        const float2 e = make_float2(ex2_approx(v.x * kLog2e), ex2_approx(v.y * kLog2e));
-                        dtv.x = v.x > 20.f ? v.x : kLn2 * lg2_approx(1.f + e.x);
-                        dtv.y = v.y > 20.f ? v.y : kLn2 * lg2_approx(1.f + e.y);
+                        const float2 vl = mul2(v, splat2(kLog2e));
+                        const float2 w = add2(make_float2(ex2_approx(vl.x), ex2_approx(vl.y)), splat2(1.f));
+                        const float2 sp = mul2(make_float2(lg2_approx(w.x), lg2_approx(w.y)), splat2(kLn2));
+                        dtv.x = v.x > 20.f ? v.x : sp.x;
+                        dtv.y = v.y > 20.f ? v.y : sp.y;
                     } else {
                         dtv = make_float2(softplus_acc(v.x), softplus_acc(v.y));
                     }
@@ -390,9 +492,15 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     dtv = v;
                 }
                 float2 g = make_float2(1.f, 1.f);
-                if (p.has_z) {
-                    const float2 zz = ld_pair<T>(sz, swz<ES>(tl, pch));
-                    g = make_float2(silu_sel<FAST>(zz.x), silu_sel<FAST>(zz.y));
+                if (has_z) {
+                    const float2 zz = ld_pair<T>(szs, doff[pass]);
+                    if constexpr (FAST) {
+                        const float2 t = mul2(zz, splat2(-kLog2e));
+                        const float2 den = add2(make_float2(ex2_approx(t.x), ex2_approx(t.y)), splat2(1.f));
+                        g = mul2(zz, make_float2(rcp_approx(den.x), rcp_approx(den.y)));
+                    } else {
+                        g = make_float2(silu_acc(zz.x), silu_acc(zz.y));
+                    }
                 }
                 float2 xin = mul2(dtv, u);
                 const float2 sk = mul2(mul2(dskip, u), g);
@@ -404,57 +512,21 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 } else {
                     r1 = dtv;
                 }
-                if (!live) {  // steps past the end of the sequence leave the state untouched
+                if (tail && (t_chunk0 + tl0 + row) >= t_seg1) {  // steps past the end leave the state untouched
                     xin = make_float2(0.f, 0.f);
                     r1 = GEOM ? make_float2(1.f, 1.f) : make_float2(0.f, 0.f);
                 }
-                const int ri = row * CW + 2 * pj;
-                if constexpr (GEOM && LPC == 4) {
+                const int ri = row * CW + 2 * pj;  // records of the pair are adjacent: one 16-byte store each
+                *reinterpret_cast<float4 *>(recGS + ri) = make_float4(g.x, sk.x, g.y, sk.y);
+                if constexpr (POW4) {
                     const float2 r2 = mul2(r1, r1), r3 = mul2(r2, r1), r4 = mul2(r2, r2);
-                    rec0[ri] = make_float4(r1.x, r2.x, r3.x, r4.x);
-                    rec0[ri + 1] = make_float4(r1.y, r2.y, r3.y, r4.y);
-                    rec1[ri] = make_float4(r4.x, xin.x, g.x, sk.x);
-                    rec1[ri + 1] = make_float4(r4.y, xin.y, g.y, sk.y);
-                } else if constexpr (GEOM && LPC == 2) {
-                    const float2 r2 = mul2(r1, r1), r4 = mul2(r2, r2);
-                    rec0[ri] = make_float4(r1.x, r2.x, r4.x, xin.x);
-                    rec0[ri + 1] = make_float4(r1.y, r2.y, r4.y, xin.y);
-                    rec1[ri] = make_float4(g.x, sk.x, 0.f, 0.f);
-                    rec1[ri + 1] = make_float4(g.y, sk.y, 0.f, 0.f);
+                    *reinterpret_cast<float4 *>(recRX + ri) = make_float4(r4.x, xin.x, r4.y, xin.y);
+                    *reinterpret_cast<float2 *>(recP + 0 * Cfg::PLANE_FLOATS + ri) = r1;
+                    *reinterpret_cast<float2 *>(recP + 1 * Cfg::PLANE_FLOATS + ri) = r2;
+                    *reinterpret_cast<float2 *>(recP + 2 * Cfg::PLANE_FLOATS + ri) = r3;
+                    *reinterpret_cast<float2 *>(recP + 3 * Cfg::PLANE_FLOATS + ri) = r4;
                 } else {
-                    rec0[ri] = make_float4(r1.x, xin.x, g.x, sk.x);
-                    rec0[ri + 1] = make_float4(r1.y, xin.y, g.y, sk.y);
-                }
-            }
-            // ---- widen this sub-chunk's B and C rows to fp32, regrouped so that lane q finds its
-            //      S states (n = q + LPC*j, j ascending) contiguous: bcf[arr][row][q*S + j]
-            {
-                constexpr int EPL = TS * 16 * 2 / 32;  // elements per lane: 8 (bf16) or 16 (fp32)
-                const int arr = lane / 16;             // 0: B, 1: C
-                const int e0 = (lane % 16) * EPL;      // first element inside the [TS][16] block
-                const int row = e0 / 16, n0 = e0 % 16;
-                const char *src = (arr ? sC : sB) + ((tl0 + row) * 16 + n0) * ES;
-                float vals[EPL];
-                if constexpr (ES == 2) {
-                    const uint4 raw = *reinterpret_cast<const uint4 *>(src);
-                    const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        vals[2 * k] = __uint_as_float(wds[k] << 16);
-                        vals[2 * k + 1] = __uint_as_float(wds[k] & 0xffff0000u);
-                    }
-                } else {
-#pragma unroll
-                    for (int k = 0; k < EPL / 4; ++k) {
-                        const float4 f = *reinterpret_cast<const float4 *>(src + 16 * k);
-                        vals[4 * k] = f.x; vals[4 * k + 1] = f.y; vals[4 * k + 2] = f.z; vals[4 * k + 3] = f.w;
-                    }
-                }
-                float *dst = bcf + arr * TS * 16 + row * 16;
-#pragma unroll
-                for (int k = 0; k < EPL; ++k) {
-                    const int n = n0 + k;
-                    dst[(n % LPC) * S + n / LPC] = vals[k];
+                    *reinterpret_cast<float4 *>(recRX + ri) = make_float4(r1.x, xin.x, r1.y, xin.y);
                 }
             }
             __syncwarp();
@@ -474,28 +546,25 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     const int row = grp * LPC + k;
                     const int ri = row * CW + c;
                     float2 a[S / 2];
-                    float xin;
-                    if constexpr (GEOM && LPC == 4) {
-                        const float base = reinterpret_cast<const float *>(rec0 + ri)[q];
-                        const float2 r4x = *reinterpret_cast<const float2 *>(rec1 + ri);
-                        xin = r4x.y;
-                        const float r8 = r4x.x * r4x.x;
-                        a[0] = make_float2(base, base * r4x.x);
+                    const float2 rx = recRX[ri];
+                    const float xin = rx.y;
+                    if constexpr (GEOM && LPC == 4) {  // r^(q+1), r^(q+5), r^(q+9), r^(q+13)
+                        const float base = recP[q * Cfg::PLANE_FLOATS + ri];
+                        const float r8 = rx.x * rx.x;
+                        a[0] = make_float2(base, base * rx.x);
                         a[1] = mul2(a[0], splat2(r8));
-                    } else if constexpr (GEOM && LPC == 2) {
-                        const float4 rr = rec0[ri];  // r1, r2, r4, x
-                        xin = rr.w;
-                        const float base = q ? rr.y : rr.x;
-                        const float r8 = rr.z * rr.z;
-                        a[0] = make_float2(base, base * rr.y);
-                        a[1] = mul2(a[0], splat2(rr.z));
+                    } else if constexpr (GEOM && LPC == 2) {  // r^(q+1+2j)
+                        const float r2 = rx.x * rx.x;
+                        const float r4 = r2 * r2;
+                        const float r8 = r4 * r4;
+                        const float base = q ? r2 : rx.x;
+                        a[0] = make_float2(base, base * r2);
+                        a[1] = mul2(a[0], splat2(r4));
                         a[2] = mul2(a[0], splat2(r8));
                         a[3] = mul2(a[1], splat2(r8));
                     } else if constexpr (GEOM) {  // LPC == 1: r^1 .. r^16
-                        const float4 rr = rec0[ri];  // r, x, g, s
-                        xin = rr.y;
-                        const float r2 = rr.x * rr.x;
-                        a[0] = make_float2(rr.x, r2);
+                        const float r2 = rx.x * rx.x;
+                        a[0] = make_float2(rx.x, r2);
                         a[1] = mul2(a[0], splat2(r2));
                         const float r4 = a[1].y;
                         a[2] = mul2(a[0], splat2(r4));
@@ -504,24 +573,25 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
 #pragma unroll
                         for (int j = 0; j < 4; ++j) a[4 + j] = mul2(a[j], splat2(r8));
                     } else {
-                        const float2 dx = *reinterpret_cast<const float2 *>(rec0 + ri);  // dt, x
-                        xin = dx.y;
 #pragma unroll
                         for (int j = 0; j < S / 2; ++j) {
                             if constexpr (FAST)
-                                a[j] = make_float2(ex2_approx(dx.x * a2l[2 * j]), ex2_approx(dx.x * a2l[2 * j + 1]));
+                                a[j] = make_float2(ex2_approx(rx.x * a2l[2 * j]), ex2_approx(rx.x * a2l[2 * j + 1]));
                             else
-                                a[j] = make_float2(exp2f(dx.x * a2l[2 * j]), exp2f(dx.x * a2l[2 * j + 1]));
+                                a[j] = make_float2(exp2f(rx.x * a2l[2 * j]), exp2f(rx.x * a2l[2 * j + 1]));
                         }
                     }
-                    const float2 *Bq = reinterpret_cast<const float2 *>(bcf + row * 16 + q * S);
-                    const float2 *Cq = reinterpret_cast<const float2 *>(bcf + TS * 16 + row * 16 + q * S);
+                    const float4 *Bq = reinterpret_cast<const float4 *>(sBf + (tl0 + row) * 16 + q * S);
+                    const float4 *Cq = reinterpret_cast<const float4 *>(sCf + (tl0 + row) * 16 + q * S);
                     const float2 x2 = splat2(xin);
                     float2 yacc = make_float2(0.f, 0.f);
 #pragma unroll
-                    for (int j = 0; j < S / 2; ++j) {
-                        h[j] = fma2(a[j], h[j], mul2(x2, Bq[j]));
-                        yacc = fma2(Cq[j], h[j], yacc);
+                    for (int j4 = 0; j4 < S / 4; ++j4) {
+                        const float4 bv = Bq[j4], cv = Cq[j4];
+                        h[2 * j4] = fma2(a[2 * j4], h[2 * j4], mul2(x2, make_float2(bv.x, bv.y)));
+                        h[2 * j4 + 1] = fma2(a[2 * j4 + 1], h[2 * j4 + 1], mul2(x2, make_float2(bv.z, bv.w)));
+                        yacc = fma2(make_float2(cv.x, cv.y), h[2 * j4], yacc);
+                        yacc = fma2(make_float2(cv.z, cv.w), h[2 * j4 + 1], yacc);
                     }
                     part[k] = yacc.x + yacc.y;
                 }
@@ -542,13 +612,9 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     ysum = part[0];
                 }
                 const int row = grp * LPC + q;
-                const int ri = row * CW + c;
-                float2 gs;
-                if constexpr (GEOM && LPC == 4) gs = *(reinterpret_cast<const float2 *>(rec1 + ri) + 1);
-                else if constexpr (GEOM && LPC == 2) gs = *reinterpret_cast<const float2 *>(rec1 + ri);
-                else gs = *(reinterpret_cast<const float2 *>(rec0 + ri) + 1);
+                const float2 gs = recGS[row * CW + c];
                 const float yv = fmaf(ysum, gs.x, gs.y);
-                st_f32(reinterpret_cast<T *>(so + swz<ES>(tl0 + row, warp * CW + c)), yv);
+                st_f32(reinterpret_cast<T *>(so + tl0 * 128 + yoff[grp]), yv);
             }
             __syncwarp();
         }
@@ -669,10 +735,10 @@ static size_t workspace_bytes(const hx_scan_args *a, int n_seg) {
     return (carry + 255) / 256 * 256 + (flags + 255) / 256 * 256 + 256;
 }
 
-template <typename T, int LPC, bool GEOM, int TC, int STAGES>
+template <typename T, int LPC, bool GEOM, int TC, int STAGES, bool STD>
 static hx_status launch_tiled_inst(const hx_scan_args *a, const TiledParams &p, const CUtensorMap *maps, dim3 grid,
                                    cudaStream_t st) {
-    using Cfg = TiledCfg<T, LPC, GEOM, TC, STAGES>;
+    using Cfg = TiledCfg<T, LPC, GEOM, TC, STAGES, STD>;
     auto kern = scan_tiled_kernel<T, Cfg>;
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -759,7 +825,13 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
     dim3 grid(tiles, a->batch, n_seg);
     const int lpc = choose_lpc(a);
     const bool geom = a->a_geometric != 0;
-#define HX_TILED_CASE(T, LPC, GEOM, TCv, ST) return launch_tiled_inst<T, LPC, GEOM, TCv, ST>(a, p, maps, grid, st)
+    // the standard path (4-tap conv, softplus, gate) has its flags fixed at compile time
+    const bool stdp = a->conv_w != nullptr && a->z != nullptr && a->dt_softplus != 0;
+#define HX_TILED_CASE(T, LPC, GEOM, TCv, ST)                                                    \
+    do {                                                                                        \
+        if (stdp) return launch_tiled_inst<T, LPC, GEOM, TCv, ST, true>(a, p, maps, grid, st);  \
+        return launch_tiled_inst<T, LPC, GEOM, TCv, ST, false>(a, p, maps, grid, st);           \
+    } while (0)
     if (bf) {
         if (geom) {
             if (lpc == 1) HX_TILED_CASE(__nv_bfloat16, 1, true, kChunkBf16, 2);

@@ -1,0 +1,205 @@
+"""Python face of the module-level C API (hx_module_* / hx_tensor_*): the reference's
+`MambaBlock::new(d_model, d_state, d_conv, expand, &device)`, `S4Block::new(d_model, d_state, &device)`,
+`Linear::new`, `RMSNorm::new` and `Module::{forward, parameters}` (crates/nn/src/lib.rs:20-39, 847;
+crates/nn/src/ssm.rs:39, 138) on device-resident tensors.  Errors are `HxError`s whose `.variant` is the
+TensorError variant the reference would return."""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib as L
+
+F32, BF16, U8 = L.HX_F32, L.HX_BF16, L.HX_U8
+
+
+class Device:
+    """tensor_core::Device (crates/tensor-core/src/device.rs:8-60), CUDA variant only."""
+
+    def __init__(self, index: int = 0):
+        self.index = index
+
+    @staticmethod
+    def cuda(index: int = 0) -> "Device":
+        return Device(index)
+
+    def __repr__(self):
+        return f"Cuda({self.index})"
+
+
+class Tensor:
+    """A device-resident tensor handle (hx_tensor)."""
+
+    def __init__(self, handle):
+        self._h = C.c_void_p(handle) if not isinstance(handle, C.c_void_p) else handle
+
+    @staticmethod
+    def from_numpy(a: np.ndarray, dtype: int = F32, device: Device = Device(0)) -> "Tensor":
+        out = C.c_void_p()
+        if a.dtype == np.uint8:
+            a = np.ascontiguousarray(a)
+            dims = (C.c_int64 * a.ndim)(*a.shape)
+            L.check(L.lib().hx_tensor_from_host_u8(a.ctypes.data_as(C.c_void_p), dims, a.ndim, device.index, C.byref(out)))
+        else:
+            a = np.ascontiguousarray(a, dtype=np.float32)
+            dims = (C.c_int64 * a.ndim)(*a.shape)
+            L.check(L.lib().hx_tensor_from_host(a.ctypes.data_as(C.c_void_p), dims, a.ndim, dtype, device.index, C.byref(out)))
+        return Tensor(out)
+
+    def _info(self):
+        nd, dt, dev = C.c_int32(), C.c_int32(), C.c_int32()
+        dims = (C.c_int64 * 8)()
+        L.check(L.lib().hx_tensor_info(self._h, C.byref(nd), dims, C.byref(dt), C.byref(dev)))
+        return tuple(dims[i] for i in range(nd.value)), dt.value, dev.value
+
+    @property
+    def shape(self):
+        return self._info()[0]
+
+    @property
+    def dtype(self):
+        return self._info()[1]
+
+    def numpy(self) -> np.ndarray:
+        shape = self.shape
+        out = np.empty(shape, dtype=np.float32)
+        L.check(L.lib().hx_tensor_to_host(self._h, out.ctypes.data_as(C.c_void_p), out.size))
+        return out
+
+    def copy_from(self, a: np.ndarray) -> None:
+        a = np.ascontiguousarray(a, dtype=np.float32)
+        L.check(L.lib().hx_tensor_copy_from_host(self._h, a.ctypes.data_as(C.c_void_p), a.size))
+
+    def data_ptr(self) -> int:
+        return L.lib().hx_tensor_data(self._h) or 0
+
+    def __del__(self):
+        try:
+            if self._h:
+                L.lib().hx_tensor_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+class Module:
+    """nn::Module (crates/nn/src/lib.rs:20-39): forward, parameters."""
+
+    def __init__(self, handle):
+        self._h = handle
+
+    def forward(self, x: Tensor) -> Tensor:
+        out = C.c_void_p()
+        L.check(L.lib().hx_module_forward(self._h, x._h, C.byref(out)))
+        return Tensor(out)
+
+    __call__ = forward
+
+    def parameters(self):
+        n = L.lib().hx_module_num_parameters(self._h)
+        ps = []
+        for i in range(n):
+            out = C.c_void_p()
+            L.check(L.lib().hx_module_parameter(self._h, i, C.byref(out)))
+            ps.append(Tensor(out))
+        return ps
+
+    def load_parameters(self, arrays) -> None:
+        """Writes numpy arrays into the parameters, in parameters() order (Module::parameters_mut)."""
+        ps = self.parameters()
+        if len(arrays) != len(ps):
+            raise L.HxError(9, f"expected {len(ps)} parameters, got {len(arrays)}")
+        for p, a in zip(ps, arrays):
+            p.copy_from(a)
+        L.check(L.lib().hx_module_parameters_updated(self._h))
+
+    @property
+    def name(self) -> str:
+        return L.lib().hx_module_name(self._h).decode()
+
+    def __del__(self):
+        try:
+            if self._h:
+                L.lib().hx_module_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+def manual_seed(seed: int) -> None:
+    L.lib().hx_manual_seed(C.c_uint64(seed))
+
+
+class MambaBlock(Module):
+    """MambaBlock::new(d_model, d_state, d_conv, expand, &device) (crates/nn/src/lib.rs:847).
+    parameters(): W_in, conv_w, conv_b, W_x, W_dt, b_dt, A, D, W_out."""
+    PARAMS = ("W_in", "conv_w", "conv_b", "W_x", "W_dt", "b_dt", "A", "D", "W_out")
+
+    def __init__(self, d_model, d_state, d_conv, expand, device: Device = Device(0), dtype: int = F32):
+        h = C.c_void_p()
+        L.check(L.lib().hx_mamba_block_new(d_model, d_state, d_conv, expand, dtype, device.index, C.byref(h)))
+        super().__init__(h)
+
+    def load_weights(self, w: dict) -> None:
+        self.load_parameters([w[k] for k in self.PARAMS])
+
+
+class S4Block(Module):
+    """nn::ssm::S4Block::new(d_model, d_state, &device) (crates/nn/src/ssm.rs:39).  parameters(): A_real,
+    A_imag, B, C, D, delta, Lambda (the reference's seven), then A_diag, B_diag, C_diag."""
+
+    def __init__(self, d_model, d_state, device: Device = Device(0)):
+        h = C.c_void_p()
+        L.check(L.lib().hx_s4_block_new(d_model, d_state, device.index, C.byref(h)))
+        super().__init__(h)
+
+    def forward_ssm(self, u: Tensor) -> Tensor:
+        out = C.c_void_p()
+        L.check(L.lib().hx_s4_block_forward_ssm(self._h, u._h, C.byref(out)))
+        return Tensor(out)
+
+
+class Linear(Module):
+    def __init__(self, in_features, out_features, bias=True, device: Device = Device(0), dtype: int = F32):
+        h = C.c_void_p()
+        L.check(L.lib().hx_linear_new(in_features, out_features, 1 if bias else 0, dtype, device.index, C.byref(h)))
+        super().__init__(h)
+
+
+class RMSNorm(Module):
+    def __init__(self, d_model, eps=1e-5, device: Device = Device(0)):
+        h = C.c_void_p()
+        L.check(L.lib().hx_rmsnorm_new(d_model, C.c_float(eps), device.index, C.byref(h)))
+        super().__init__(h)
+
+
+class ByteLM(Module):
+    """Byte-level LM: tied embedding, n_layer x (RMSNorm + MambaBlock + residual), final norm, logits.
+    parameters(): embedding, then per layer [norm_w, *MambaBlock.PARAMS], then norm_f."""
+
+    def __init__(self, n_layer, d_model, d_state=16, d_conv=4, expand=2, device: Device = Device(0), dtype: int = BF16):
+        h = C.c_void_p()
+        L.check(L.lib().hx_byte_lm_new(n_layer, d_model, d_state, d_conv, expand, dtype, device.index, C.byref(h)))
+        super().__init__(h)
+        self.n_layer, self.d_model = n_layer, d_model
+
+    def load_weights(self, emb, layers, norm_f) -> None:
+        arrays = [emb]
+        for l in layers:
+            arrays.append(l["norm_w"])
+            arrays.extend(l[k] for k in MambaBlock.PARAMS)
+        arrays.append(norm_f)
+        self.load_parameters(arrays)
+
+    def forward_host(self, tokens_ptr: int, logits_ptr: int, batch: int, seq_len: int, stream: int = 0) -> None:
+        L.check(L.lib().hx_byte_lm_forward_host(self._h, C.c_void_p(tokens_ptr), C.c_void_p(logits_ptr), batch, seq_len,
+                                                C.c_void_p(stream)))
+
+    def forward_device(self, tokens_ptr: int, logits_ptr: int, batch: int, seq_len: int, stream: int = 0) -> None:
+        L.check(L.lib().hx_byte_lm_forward_device(self._h, C.c_void_p(tokens_ptr), C.c_void_p(logits_ptr), batch, seq_len,
+                                                  C.c_void_p(stream)))
+
+    @property
+    def launches_per_forward(self) -> int:
+        return int(L.lib().hx_byte_lm_launches_per_forward(self._h))

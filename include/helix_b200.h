@@ -241,6 +241,68 @@ typedef struct hx_mamba_block_args {
 HX_API hx_status hx_mamba_block_fwd(const hx_mamba_block_args *args, void *stream);
 HX_API hx_status hx_mamba_block_workspace_bytes(const hx_mamba_block_args *args, size_t *bytes);
 
+/* =============================================================================================
+ * Module-level API: opaque handles over the C++ host layer (helixml_b200/csrc/helix_host.hpp), which
+ * restates the reference's module interface for device-resident tensors:
+ *   MambaBlock::new(d_model, d_state, d_conv, expand, &device) / forward   crates/nn/src/lib.rs:847,910
+ *   S4Block::new(d_model, d_state, &device) / forward_ssm                  crates/nn/src/ssm.rs:39,138
+ *   Linear::new / RMSNorm::new / Module::{forward, parameters, parameters_mut}  crates/nn/src/lib.rs:20-39,67,242
+ * A Rust `impl Module<DeviceTensor>` forwards to these.  Handles are owned by the caller and freed with
+ * hx_tensor_free / hx_module_free.  forward() runs on the default stream of the module's device and
+ * returns a new tensor; errors come back as hx_status exactly like the reference's Result<T, TensorError>.
+ * ============================================================================================= */
+typedef struct hx_tensor hx_tensor;
+typedef struct hx_module hx_module;
+
+/* Seed of the parameter initialisers (the reference draws from an unseeded thread_rng,
+ * crates/backend-cpu/src/lib.rs:1209). */
+HX_API void hx_manual_seed(uint64_t seed);
+
+/* Tensor::from host data (fp32 values, converted to `dtype`), TensorRandom::zeros-style construction is
+ * from_host with zeros.  dims has ndim entries (<= 8). */
+HX_API hx_status hx_tensor_from_host(const float *data, const int64_t *dims, int32_t ndim, int32_t dtype,
+                              int32_t device_id, hx_tensor **out);
+HX_API hx_status hx_tensor_from_host_u8(const uint8_t *data, const int64_t *dims, int32_t ndim, int32_t device_id,
+                                 hx_tensor **out);
+HX_API hx_status hx_tensor_to_host(const hx_tensor *t, float *out, int64_t n);       /* widens bf16 to fp32 */
+HX_API hx_status hx_tensor_copy_from_host(hx_tensor *t, const float *data, int64_t n);
+HX_API hx_status hx_tensor_info(const hx_tensor *t, int32_t *ndim, int64_t *dims8, int32_t *dtype, int32_t *device_id);
+HX_API void *hx_tensor_data(const hx_tensor *t);                                      /* device pointer */
+HX_API void hx_tensor_free(hx_tensor *t);
+
+HX_API hx_status hx_mamba_block_new(int64_t d_model, int64_t d_state, int64_t d_conv, int64_t expand, int32_t dtype,
+                             int32_t device_id, hx_module **out);
+HX_API hx_status hx_s4_block_new(int64_t d_model, int64_t d_state, int32_t device_id, hx_module **out);
+HX_API hx_status hx_linear_new(int64_t in_features, int64_t out_features, int32_t bias, int32_t dtype,
+                        int32_t device_id, hx_module **out);
+HX_API hx_status hx_rmsnorm_new(int64_t d_model, float eps, int32_t device_id, hx_module **out);
+/* The byte-level LM of examples/ssm_byte_lm widened to n_layer x (RMSNorm + MambaBlock + residual), tied
+ * embedding [256, d_model] (examples/ssm_byte_lm/src/main.rs:104-130). */
+HX_API hx_status hx_byte_lm_new(int64_t n_layer, int64_t d_model, int64_t d_state, int64_t d_conv, int64_t expand,
+                         int32_t dtype, int32_t device_id, hx_module **out);
+
+/* Module::forward.  MambaBlock / Linear / RMSNorm / S4Block take [L, d] or [B, L, d]; ByteLM takes U8
+ * tokens [B, L] and returns logits [B, L, 256]. */
+HX_API hx_status hx_module_forward(const hx_module *m, const hx_tensor *input, hx_tensor **out);
+/* nn::ssm::S4Block::forward_ssm: input [d_model, L] fp32, output buffer [L, d_model]. */
+HX_API hx_status hx_s4_block_forward_ssm(const hx_module *m, const hx_tensor *input, hx_tensor **out);
+/* Serving calls of the byte LM: no allocation after the first call for a given (batch, seq_len); work is
+ * queued on `stream`.  _host: tokens from and logits to (pinned) host memory, logits in the model dtype.
+ * _device: tokens_dev [B*L] u8 and logits_dev [B*L, 256] on the device. */
+HX_API hx_status hx_byte_lm_forward_host(hx_module *m, const uint8_t *tokens_host, void *logits_host, int64_t batch,
+                                  int64_t seq_len, void *stream);
+HX_API hx_status hx_byte_lm_forward_device(hx_module *m, const uint8_t *tokens_dev, void *logits_dev, int64_t batch,
+                                    int64_t seq_len, void *stream);
+HX_API int64_t hx_byte_lm_launches_per_forward(const hx_module *m);
+
+/* Module::parameters / parameters_mut: parameter `index` as a tensor handle that SHARES the parameter's
+ * storage (write it with hx_tensor_copy_from_host, then call hx_module_parameters_updated). */
+HX_API int32_t hx_module_num_parameters(const hx_module *m);
+HX_API hx_status hx_module_parameter(hx_module *m, int32_t index, hx_tensor **out);
+HX_API hx_status hx_module_parameters_updated(hx_module *m);
+HX_API const char *hx_module_name(const hx_module *m);
+HX_API void hx_module_free(hx_module *m);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,148 @@
+"""GPU tests of the module-level API (the reference's constructors and forward): same names, same argument
+meaning, same error behaviour, outputs checked against the oracle on injected weights."""
+import numpy as np
+import pytest
+
+from conftest import BF16_TOL, FP32_TOL, fp32_tol_err, rel_l2
+from helixml_b200 import synth
+from oracle import cbind
+
+pytestmark = pytest.mark.gpu
+
+
+def test_mamba_block_creation():
+    # crates/nn/src/ssm.rs:590-598 / examples/ssm_example/src/main.rs:26: MambaBlock::new(64, 16, 4, 2, &device)
+    from helixml_b200 import nn
+    m = nn.MambaBlock(64, 16, 4, 2, nn.Device.cuda(0))
+    ps = m.parameters()
+    assert m.name == "MambaBlock" and len(ps) == 9
+    shapes = [p.shape for p in ps]
+    assert shapes == [(256, 64), (128, 4), (128,), (4 + 32, 128), (128, 4), (128,), (128, 16), (128,), (64, 128)]
+    A = ps[6].numpy()
+    assert np.allclose(A, -np.arange(1, 17, dtype=np.float32)[None, :], rtol=1e-6)  # A_log[d,n] = log(n+1)
+    assert np.all(ps[7].numpy() == 1.0)                                             # D = 1
+    dt0 = np.log1p(np.exp(ps[5].numpy()))                                           # softplus(bias) in [1e-3, 1e-1]
+    assert dt0.min() >= 0.99e-3 and dt0.max() <= 1.01e-1
+
+
+def test_mamba_block_forward_matches_oracle_config0(golden):
+    """Benchmark configuration 0 through the module API: x [100, 64] (2-D, as the reference's example feeds
+    it) and [1, 100, 64] give the same numbers as the oracle block on the same injected weights."""
+    from helixml_b200 import nn
+    w = synth.mamba_block_weights(0, 64, 16, 4, 2)
+    x = synth.uniform(0, "x", (1, 100, 64), -1, 1)
+    m = nn.MambaBlock(64, 16, 4, 2, nn.Device.cuda(0))
+    m.load_weights(w)
+    ref = golden("mamba_block_cfg0.npz")["y"]
+    y3 = m.forward(nn.Tensor.from_numpy(x)).numpy()
+    y2 = m(nn.Tensor.from_numpy(x[0])).numpy()
+    assert y3.shape == (1, 100, 64) and y2.shape == (100, 64)
+    assert fp32_tol_err(y3, ref) <= FP32_TOL and fp32_tol_err(y2, ref[0]) <= FP32_TOL
+
+
+def test_mamba_block_errors():
+    from helixml_b200 import _lib, nn
+    m = nn.MambaBlock(64, 16, 4, 2, nn.Device.cuda(0))
+    with pytest.raises(_lib.HxError) as e:
+        m.forward(nn.Tensor.from_numpy(np.zeros((10, 32), np.float32)))
+    assert e.value.variant == "ShapeMismatch"
+    with pytest.raises(_lib.HxError) as e:
+        m.forward(nn.Tensor.from_numpy(np.zeros((10, 64), np.float32), dtype=nn.BF16))
+    assert e.value.variant == "DTypeMismatch"
+    with pytest.raises(_lib.HxError) as e:
+        nn.MambaBlock(64, 16, 9, 2, nn.Device.cuda(0))
+    assert e.value.variant == "InvalidDimension"
+    with pytest.raises(_lib.HxError) as e:
+        m.load_parameters([np.zeros(3, np.float32)])
+    assert e.value.variant == "InvalidCheckpoint"
+    out = m.forward(nn.Tensor.from_numpy(np.zeros((0, 64), np.float32)))
+    assert out.shape == (0, 64)
+
+
+def test_s4_block_creation_and_forward_ssm():
+    # crates/nn/src/ssm.rs:560-567: S4Block::new(64, 16); ssm.rs:138-147: forward_ssm wants dim0 == d_model
+    from helixml_b200 import _lib, nn
+    s4 = nn.S4Block(64, 16, nn.Device.cuda(0))
+    ps = s4.parameters()
+    assert [p.shape for p in ps[:7]] == [(16,), (16,), (16, 64), (64, 16), (64,), (64,), (16,)]
+    assert np.all(ps[0].numpy() == 0) and np.all(ps[4].numpy() == 0)  # A_real and D start at zero
+    delta = ps[5].numpy()
+    assert delta.min() >= 0.001 and delta.max() <= 0.1
+    u = synth.normal(71, "u", (64, 32))
+    y = s4.forward_ssm(nn.Tensor.from_numpy(u)).numpy()
+    vals = [p.numpy() for p in ps]
+    ref = cbind.s4_forward_ssm(u, vals[0], vals[1], vals[2], vals[3], vals[4])
+    assert y.shape == (32, 64) and fp32_tol_err(y, ref) <= FP32_TOL
+    with pytest.raises(_lib.HxError) as e:
+        s4.forward_ssm(nn.Tensor.from_numpy(synth.normal(71, "u2", (32, 64))))
+    assert e.value.variant == "ShapeMismatch"
+
+
+def test_s4_block_forward_diagonal():
+    from helixml_b200 import nn
+    s = synth.s4_inputs(1, 2, 100, 32, 64)
+    s4 = nn.S4Block(32, 64, nn.Device.cuda(0))
+    ps = s4.parameters()
+    ps[4].copy_from(s["D"]); ps[5].copy_from(s["delta"]); ps[7].copy_from(s["A"]); ps[8].copy_from(s["B"]); ps[9].copy_from(s["C"])
+    y = s4.forward(nn.Tensor.from_numpy(s["u"])).numpy()
+    assert fp32_tol_err(y, cbind.s4_diag(s["u"], s["A"], s["B"], s["C"], s["delta"], s["D"])) <= FP32_TOL
+
+
+def test_linear_and_rmsnorm_modules():
+    from helixml_b200 import nn
+    lin = nn.Linear(48, 20, True, nn.Device.cuda(0))
+    w, b = [p.numpy() for p in lin.parameters()]
+    assert w.shape == (20, 48) and np.all(b == 0) and 0.1 < w.std() < 0.3  # N(0, sqrt(2/48)) = 0.204
+    x = synth.normal(72, "x", (7, 48))
+    assert fp32_tol_err(lin(nn.Tensor.from_numpy(x)).numpy(), cbind.linear(x, w, b)) <= FP32_TOL
+    norm = nn.RMSNorm(48, 1e-5, nn.Device.cuda(0))
+    assert np.all(norm.parameters()[0].numpy() == 1.0)
+    x3 = synth.normal(72, "x3", (2, 5, 48))
+    assert fp32_tol_err(norm(nn.Tensor.from_numpy(x3)).numpy(), cbind.rmsnorm(x3, np.ones(48, np.float32))) <= FP32_TOL
+
+
+def _lm_weights(seed, n_layer, M):
+    layers = []
+    for l in range(n_layer):
+        w = synth.mamba_block_weights(seed, M, 16, 4, 2, init="0.02", prefix=f"l{l}.")
+        w["norm_w"] = synth.uniform(seed, f"l{l}.norm", (M,), 0.8, 1.2)
+        layers.append(w)
+    emb = synth.normal(seed, "emb", (256, M), 0, 0.02)
+    normf = synth.uniform(seed, "normf", (M,), 0.8, 1.2)
+    return emb, layers, normf
+
+
+def test_byte_lm_f32_matches_oracle():
+    from helixml_b200 import nn
+    emb, layers, normf = _lm_weights(3, 3, 64)
+    tok = synth.random_bytes(3, "tok", (2, 50))
+    lm = nn.ByteLM(3, 64, dtype=nn.F32)
+    lm.load_weights(emb, layers, normf)
+    got = lm.forward(nn.Tensor.from_numpy(tok)).numpy()
+    ref = cbind.byte_lm(tok, emb, layers, normf, 16, 4)
+    assert got.shape == (2, 50, 256)
+    assert fp32_tol_err(got, ref) <= FP32_TOL
+
+
+def test_byte_lm_bf16_matches_oracle_and_host_call():
+    import torch
+    from helixml_b200 import _lib, nn
+    M, nl, B, L = 128, 4, 2, 96
+    emb, layers, normf = _lm_weights(3, nl, M)
+    big = ("W_in", "W_x", "W_dt", "W_out")
+    layers_q = [{k: (synth.round_bf16(v) if k in big else v) for k, v in l.items()} for l in layers]
+    emb_q = synth.round_bf16(emb)
+    tok = synth.random_bytes(3, "tok", (B, L))
+    lm = nn.ByteLM(nl, M, dtype=nn.BF16)
+    lm.load_weights(emb_q, layers_q, normf)
+    got = lm.forward(nn.Tensor.from_numpy(tok)).numpy()
+    ref = cbind.byte_lm(tok, emb_q, layers_q, normf, 16, 4)
+    assert rel_l2(got, ref) <= BF16_TOL
+    # the serving call: pinned host tokens in, pinned host logits out
+    th = torch.from_numpy(tok).pin_memory()
+    lh = torch.empty((B, L, 256), dtype=torch.bfloat16).pin_memory()
+    lm.forward_host(th.data_ptr(), lh.data_ptr(), B, L, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert np.array_equal(lh.float().numpy(), got)
+    assert _lib.device_status() == 0
+    assert lm.launches_per_forward == 1 + nl * 7 + 2
