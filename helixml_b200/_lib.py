@@ -53,7 +53,7 @@ class MambaBlockArgs(C.Structure):
         ("x", C.c_void_p), ("out", C.c_void_p), ("W_in", C.c_void_p), ("W_x", C.c_void_p), ("W_dt", C.c_void_p),
         ("W_out", C.c_void_p), ("conv_w", C.c_void_p), ("conv_b", C.c_void_p), ("b_dt", C.c_void_p),
         ("A", C.c_void_p), ("Dskip", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
-        ("scan_variant", C.c_int32), ("a_geometric", C.c_int32),
+        ("scan_variant", C.c_int32), ("a_geometric", C.c_int32), ("stage_events", C.c_void_p),
     ]
 
 
@@ -117,6 +117,8 @@ _PROTOS = {
     "hx_byte_lm_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "hx_byte_lm_forward_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "hx_byte_lm_launches_per_forward": (C.c_int64, [C.c_void_p]),
+    "hx_byte_lm_profile": (C.c_int, [C.c_void_p, C.c_int32]),
+    "hx_byte_lm_profile_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int32)]),
     "hx_module_num_parameters": (C.c_int32, [C.c_void_p]),
     "hx_module_parameter": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_void_p)]),
     "hx_module_parameters_updated": (C.c_int, [C.c_void_p]),

@@ -433,9 +433,10 @@ size_t MambaBlock::workspace_bytes(int64_t batch, int64_t seq_len) const {
 }
 
 Result<Unit> MambaBlock::forward_into(const void *x, void *out, int64_t batch, int64_t seq_len, void *workspace,
-                                      size_t ws_bytes, void *stream) const {
+                                      size_t ws_bytes, void *stream, void **stage_events) const {
     hx_mamba_block_args a = block_args(*this, batch, seq_len);
     a.x = x; a.out = out; a.workspace = workspace; a.workspace_bytes = ws_bytes;
+    a.stage_events = stage_events;
     HELIX_TRY_ABI(hx_mamba_block_fwd(&a, stream));
     return Unit{};
 }
@@ -469,7 +470,58 @@ struct ByteLM::Buffers {
     DeviceTensor tokens, resid, normed, block_out, logits, workspace;
 };
 
-ByteLM::~ByteLM() { delete buf_; }
+// Event-based stage timing: per forward, events[0] before the embedding, then per layer one event before the
+// norm and the block's seven, then events before the final norm, before the head and after it.
+struct ByteLM::Profile {
+    std::vector<cudaEvent_t> ev;       // events of the forwards not read yet, in recording order
+    std::vector<int> cls;              // stage class that STARTS at each event (-1: end marker)
+    std::vector<cudaEvent_t> pool;
+    size_t used = 0;
+    int forwards = 0;
+    cudaEvent_t next() {
+        if (used == pool.size()) {
+            cudaEvent_t e;
+            cudaEventCreate(&e);
+            pool.push_back(e);
+        }
+        return pool[used++];
+    }
+    ~Profile() {
+        for (auto e : pool) cudaEventDestroy(e);
+    }
+};
+
+ByteLM::~ByteLM() {
+    delete buf_;
+    delete prof_;
+}
+
+Result<Unit> ByteLM::set_profile(bool enable) {
+    delete prof_;
+    prof_ = enable ? new Profile() : nullptr;
+    return Unit{};
+}
+
+Result<Unit> ByteLM::read_profile(float *ms9, int *forwards) {
+    if (!ms9 || !forwards) return err(HX_ERR_INVALID_INPUT, "read_profile: NULL argument");
+    for (int i = 0; i < 9; ++i) ms9[i] = 0.f;
+    *forwards = 0;
+    if (!prof_) return Unit{};
+    HELIX_TRY(use_device(device_));
+    if (cudaDeviceSynchronize() != cudaSuccess) return err(HX_ERR_BACKEND, "cudaDeviceSynchronize failed");
+    for (size_t i = 0; i + 1 < prof_->ev.size(); ++i) {
+        if (prof_->cls[i] < 0) continue;
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, prof_->ev[i], prof_->ev[i + 1]);
+        ms9[prof_->cls[i]] += ms;
+    }
+    *forwards = prof_->forwards;
+    prof_->ev.clear();
+    prof_->cls.clear();
+    prof_->used = 0;
+    prof_->forwards = 0;
+    return Unit{};
+}
 
 Result<std::unique_ptr<ByteLM>> ByteLM::create(int64_t n_layer, int64_t d_model, int64_t d_state, int64_t d_conv,
                                                int64_t expand, DType dtype, const Device &device) {
@@ -527,18 +579,40 @@ Result<Unit> ByteLM::forward_device(const uint8_t *tokens_dev, void *logits_dev,
     HELIX_TRY(ensure_buffers(batch, seq_len));
     const int64_t T = batch * seq_len;
     float *resid = static_cast<float *>(buf_->resid.data());
+    auto mark = [&](int cls) {
+        if (!prof_) return;
+        cudaEvent_t e = prof_->next();
+        cudaEventRecord(e, (cudaStream_t)stream);
+        prof_->ev.push_back(e);
+        prof_->cls.push_back(cls);
+    };
+    mark(0);
     // h = emb[tokens] (fp32 residual stream)
     HELIX_TRY_ABI(hx_embedding_fwd(tokens_dev, embedding.data(), (int)dtype, resid, HX_F32, T, (int)d_model, stream));
     for (size_t l = 0; l < blocks.size(); ++l) {
         // residual += previous block output (none for the first layer); normed = rmsnorm(residual)
         const void *delta = l == 0 ? nullptr : buf_->block_out.data();
+        mark(1);
         HELIX_TRY_ABI(hx_rmsnorm_fwd(delta, (int)dtype, resid, static_cast<const float *>(norms[l]->weight.data()),
                                      buf_->normed.data(), (int)dtype, T, (int)d_model, eps, stream));
+        void *sev[7];
+        void **sevp = nullptr;
+        if (prof_) {
+            for (int k = 0; k < 7; ++k) {
+                cudaEvent_t e = prof_->next();
+                sev[k] = e;
+                prof_->ev.push_back(e);
+                prof_->cls.push_back(k < 6 ? 2 + k : -1);  // in_proj, conv, x_proj, dt_proj, scan, out_proj, end
+            }
+            sevp = sev;
+        }
         HELIX_TRY(blocks[l]->forward_into(buf_->normed.data(), buf_->block_out.data(), batch, seq_len, buf_->workspace.data(),
-                                          (size_t)buf_->workspace.numel(), stream));
+                                          (size_t)buf_->workspace.numel(), stream, sevp));
     }
+    mark(1);
     HELIX_TRY_ABI(hx_rmsnorm_fwd(buf_->block_out.data(), (int)dtype, resid, static_cast<const float *>(norm_f.data()),
                                  buf_->normed.data(), (int)dtype, T, (int)d_model, eps, stream));
+    mark(8);
     // tied head: logits = normed . emb^T
     if (dtype == DType::BF16 && d_model % 8 == 0)
         HELIX_TRY_ABI(hx_gemm_bf16(buf_->normed.data(), d_model, embedding.data(), d_model, nullptr, logits_dev, 256, HX_BF16,
@@ -546,6 +620,8 @@ Result<Unit> ByteLM::forward_device(const uint8_t *tokens_dev, void *logits_dev,
     else
         HELIX_TRY_ABI(hx_gemm_simt(buf_->normed.data(), d_model, embedding.data(), d_model, nullptr, logits_dev, 256, (int)dtype,
                                    (int)dtype, (int)T, 256, (int)d_model, 0, stream));
+    mark(-1);
+    if (prof_) prof_->forwards += 1;
     return Unit{};
 }
 
@@ -738,6 +814,26 @@ hx_status hx_byte_lm_forward_device(hx_module *m, const uint8_t *tokens_dev, voi
     HX_REQUIRE(lm != nullptr, HX_ERR_UNSUPPORTED_OPERATION, "forward_device on a module that is not a ByteLM");
     auto r = lm->forward_device(tokens_dev, logits_dev, batch, seq_len, stream);
     HX_RETURN_IF_ERR(r);
+    return HX_OK;
+}
+
+hx_status hx_byte_lm_profile(hx_module *m, int32_t enable) {
+    HX_REQUIRE(m != nullptr, HX_ERR_INVALID_INPUT, "hx_byte_lm_profile: module is NULL");
+    auto *lm = dynamic_cast<helix::ByteLM *>(m->m.get());
+    HX_REQUIRE(lm != nullptr, HX_ERR_UNSUPPORTED_OPERATION, "profile on a module that is not a ByteLM");
+    auto r = lm->set_profile(enable != 0);
+    HX_RETURN_IF_ERR(r);
+    return HX_OK;
+}
+
+hx_status hx_byte_lm_profile_read(hx_module *m, float *ms9, int32_t *forwards) {
+    HX_REQUIRE(m != nullptr, HX_ERR_INVALID_INPUT, "hx_byte_lm_profile_read: module is NULL");
+    auto *lm = dynamic_cast<helix::ByteLM *>(m->m.get());
+    HX_REQUIRE(lm != nullptr, HX_ERR_UNSUPPORTED_OPERATION, "profile on a module that is not a ByteLM");
+    int n = 0;
+    auto r = lm->read_profile(ms9, &n);
+    HX_RETURN_IF_ERR(r);
+    if (forwards) *forwards = n;
     return HX_OK;
 }
 

@@ -195,7 +195,7 @@ class MambaBlock : public Module {
     Result<DeviceTensor> forward(const DeviceTensor &input) const override;
     // forward into caller-provided buffers (no allocation): x and out are [batch*seq_len, d_model]
     Result<Unit> forward_into(const void *x, void *out, int64_t batch, int64_t seq_len, void *workspace,
-                              size_t workspace_bytes, void *stream) const;
+                              size_t workspace_bytes, void *stream, void **stage_events = nullptr) const;
     size_t workspace_bytes(int64_t batch, int64_t seq_len) const;
     std::vector<const DeviceTensor *> parameters() const override;
     std::vector<DeviceTensor *> parameters_mut() override;
@@ -225,6 +225,9 @@ class ByteLM : public Module {
     // Same on device buffers: tokens_dev [B*L] u8, logits_dev [B*L, 256] model dtype.
     Result<Unit> forward_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream);
     int64_t launches_per_forward() const;
+    // per-stage CUDA-event timing (see hx_byte_lm_profile in the C header)
+    Result<Unit> set_profile(bool enable);
+    Result<Unit> read_profile(float *ms9, int *forwards);
     std::vector<const DeviceTensor *> parameters() const override;
     std::vector<DeviceTensor *> parameters_mut() override;
     Result<Unit> parameters_updated() override;
@@ -242,6 +245,8 @@ class ByteLM : public Module {
     Device device_;
     struct Buffers;
     Buffers *buf_ = nullptr;
+    struct Profile;
+    Profile *prof_ = nullptr;
 };
 
 // Seed of the parameter initialisers (the reference draws from an unseeded thread_rng,

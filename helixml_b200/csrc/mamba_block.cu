@@ -84,16 +84,24 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
         return hx_gemm_simt(A, lda, Wt, ldw, nullptr, C, ldc, a->io_dtype, a->io_dtype, m, n, k, 0, stream);
     };
 
+    auto mark = [&](int i) {
+        if (a->stage_events) cudaEventRecord(static_cast<cudaEvent_t>(a->stage_events[i]), (cudaStream_t)stream);
+    };
+    mark(0);
     // 1. xz = x W_in^T                                  [T, 2E]
     if ((s = gemm(a->x, M, a->W_in, M, xz, 2 * E, (int)T, 2 * E, M)) != HX_OK) return s;
+    mark(1);
     // 2. u = silu(conv(xs)), xs = xz[:, :E]            [T, E]
     if ((s = hx_conv1d_silu_fwd(xz, (int64_t)a->seq_len * 2 * E, 2 * E, a->conv_w, a->conv_b, u, (int64_t)a->seq_len * E,
                                 E, a->batch, a->seq_len, E, a->d_conv, a->io_dtype, stream)) != HX_OK)
         return s;
+    mark(2);
     // 3. [dt_low | B | C] = u W_x^T                     [T, R + 2N]
     if ((s = gemm(u, E, a->W_x, E, dbc, W, (int)T, W, E)) != HX_OK) return s;
+    mark(3);
     // 4. dt_lin = dt_low W_dt^T                          [T, E]   (bias and softplus happen inside the scan)
     if ((s = gemm(dbc, W, a->W_dt, R, dtl, E, (int)T, E, R)) != HX_OK) return s;
+    mark(4);
     // 5. fused scan on strided views
     hx_scan_args sa;
     memset(&sa, 0, sizeof(sa));
@@ -109,8 +117,11 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     sa.conv_w = nullptr; sa.conv_b = nullptr;  // u is already activated
     sa.a_geometric = a->a_geometric;
     if ((s = hx_selective_scan_fwd(&sa, stream)) != HX_OK) return s;
+    mark(5);
     // 6. out = y W_out^T                                 [T, M]
-    return gemm(y, E, a->W_out, E, a->out, M, (int)T, M, E);
+    s = gemm(y, E, a->W_out, E, a->out, M, (int)T, M, E);
+    mark(6);
+    return s;
 }
 
 }  // extern "C"

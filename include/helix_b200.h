@@ -236,6 +236,8 @@ typedef struct hx_mamba_block_args {
     size_t workspace_bytes;
     int32_t scan_variant;     /* hx_scan_variant */
     int32_t a_geometric;      /* as hx_scan_args.a_geometric */
+    void **stage_events;      /* NULL, or 7 cudaEvent_t: recorded on `stream` before each of the six stages
+                                 (in_proj, conv, x_proj, dt_proj, scan, out_proj) and after the last one */
 } hx_mamba_block_args;
 
 HX_API hx_status hx_mamba_block_fwd(const hx_mamba_block_args *args, void *stream);
@@ -294,6 +296,12 @@ HX_API hx_status hx_byte_lm_forward_host(hx_module *m, const uint8_t *tokens_hos
 HX_API hx_status hx_byte_lm_forward_device(hx_module *m, const uint8_t *tokens_dev, void *logits_dev, int64_t batch,
                                     int64_t seq_len, void *stream);
 HX_API int64_t hx_byte_lm_launches_per_forward(const hx_module *m);
+/* Per-stage timing of the byte LM with CUDA events on the launching stream.  enable = 1 makes the following
+ * forward calls record events around every stage; hx_byte_lm_profile_read synchronises, adds the elapsed
+ * times of all forwards since the last read (0 embedding, 1 norm, 2 in_proj, 3 conv, 4 x_proj, 5 dt_proj,
+ * 6 scan, 7 out_proj, 8 tied head into ms9[9]) and resets. */
+HX_API hx_status hx_byte_lm_profile(hx_module *m, int32_t enable);
+HX_API hx_status hx_byte_lm_profile_read(hx_module *m, float *ms9, int32_t *forwards);
 
 /* Module::parameters / parameters_mut: parameter `index` as a tensor handle that SHARES the parameter's
  * storage (write it with hx_tensor_copy_from_host, then call hx_module_parameters_updated). */
