@@ -75,6 +75,7 @@ _PROTOS = {
     "hx_selective_scan_workspace_bytes": (C.c_int, [C.POINTER(ScanArgs), C.POINTER(C.c_size_t)]),
     "hx_selective_scan_host": (C.c_int, [C.POINTER(ScanArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "hx_selective_scan_host_workspace_bytes": (C.c_int, [C.POINTER(ScanArgs), C.POINTER(C.c_size_t)]),
+    "hx_selective_scan_fwd_noalloc": (C.c_int, [C.POINTER(ScanArgs), C.c_void_p]),
     "hx_scan_check_geometric": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int32)]),
     "hx_device_status": (C.c_int, [C.POINTER(C.c_int32), C.c_int32]),
     "hx_conv1d_silu_fwd": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,

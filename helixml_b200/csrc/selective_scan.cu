@@ -21,6 +21,7 @@
 // The reference has no selective scan to follow (its conv1d is the identity and selective_ssm
 // ignores B and C, crates/nn/src/ssm.rs:467-483); the arithmetic is the one written in
 // include/helix_b200.h above hx_scan_args.
+#include <mutex>
 #include <vector>
 
 #include "hx_tma.cuh"
@@ -976,6 +977,55 @@ hx_status hx_selective_scan_host(const hx_scan_args *a, void *dev_workspace, siz
         HX_CUDA(cudaMemcpy2DAsync(hp, (size_t)a->y_row_stride * es, dp, D * es, D * es, L, cudaMemcpyDeviceToHost, st));
     }
     return HX_OK;
+}
+
+// ---- allocation-free entry point -----------------------------------------------------------------
+// Scratch for hx_selective_scan_fwd_noalloc: a fixed array in the library's device image, so the call
+// never enters the CUDA allocator.  Every device that loads the library holds it until the process exits.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[HX_SCAN_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_noalloc_mu;
+void *g_noalloc_ptr[64] = {nullptr};  // device address of g_noalloc_scratch, per device ordinal
+}  // namespace
+
+hx_status hx_selective_scan_fwd_noalloc(const hx_scan_args *a, void *stream) {
+    hx_status s = hx::scan::validate(a);
+    if (s != HX_OK) return s;
+    if (a->batch == 0 || a->seq_len == 0 || a->d_inner == 0) return HX_OK;
+    hx_scan_args b = *a;
+    b.variant = HX_SCAN_SEQSPLIT;
+    size_t need = 0;
+    if ((s = hx_selective_scan_workspace_bytes(&b, &need)) != HX_OK) return s;
+    HX_REQUIRE(need <= (size_t)HX_SCAN_NOALLOC_SCRATCH_BYTES, HX_ERR_INVALID_INPUT,
+               "hx_selective_scan_fwd_noalloc: this problem needs %zu bytes of carry scratch, the built-in array holds "
+               "%zu; use fewer seq_splits, a smaller batch * d_inner, or hx_selective_scan_fwd with your own workspace",
+               need, (size_t)HX_SCAN_NOALLOC_SCRATCH_BYTES);
+    int dev = 0;
+    HX_CUDA(cudaGetDevice(&dev));
+    HX_REQUIRE(dev >= 0 && dev < 64, HX_ERR_BACKEND, "device ordinal %d out of range", dev);
+    void *ptr = nullptr;
+    {
+        // One-time set-up per device, with that device current: the array's name is only a host-side
+        // stand-in, the kernel needs the address cudaGetSymbolAddress returns for THIS device.
+        std::lock_guard<std::mutex> lock(g_noalloc_mu);
+        if (g_noalloc_ptr[dev] == nullptr) {
+            void *p = nullptr;
+            cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+            if (e != cudaSuccess || p == nullptr) {
+                cudaGetLastError();
+                return hx::fail(HX_ERR_BACKEND, "cudaGetSymbolAddress(g_noalloc_scratch) failed on device %d: %s", dev,
+                                cudaGetErrorString(e));
+            }
+            g_noalloc_ptr[dev] = p;
+        }
+        ptr = g_noalloc_ptr[dev];
+    }
+    b.workspace = ptr;
+    b.workspace_bytes = (size_t)HX_SCAN_NOALLOC_SCRATCH_BYTES;
+    // launch_tiled clears the carry flags with a memset on `stream` before the kernel, so nothing is
+    // inherited from the previous call; the carry states themselves are always written before they are read.
+    return hx::scan::launch_tiled(&b, true, (cudaStream_t)stream);
 }
 
 hx_status hx_scan_check_geometric(const float *A, int32_t d_inner, int32_t d_state, int32_t *is_geometric) {

@@ -142,6 +142,25 @@ HX_API hx_status hx_selective_scan_workspace_bytes(const hx_scan_args *args, siz
 HX_API hx_status hx_selective_scan_host(const hx_scan_args *args, void *dev_workspace, size_t dev_workspace_bytes,
                                  void *stream);
 HX_API hx_status hx_selective_scan_host_workspace_bytes(const hx_scan_args *args, size_t *bytes);
+/* ---- the sequence-split scan without any allocation.  (No counterpart in the reference: its CUDA backend
+ * never reaches a kernel.)
+ * Some callers cannot provide the carry workspace HX_SCAN_SEQSPLIT asks for, because they must not call
+ * cudaMalloc at that point: a backend that handed every byte of device memory to its own pool at start-up
+ * and whose `Module::forward(&self, &T)` receives no allocator, or a serving thread that must stay out of
+ * the CUDA allocator's lock while requests are in flight.  For them this entry point runs the same kernel
+ * as hx_selective_scan_fwd(variant = HX_SCAN_SEQSPLIT) with the carries kept in an array that is part of the
+ * library's device image (HX_SCAN_NOALLOC_SCRATCH_BYTES; each GPU that loads the library holds it until the
+ * process exits).  args->variant, args->workspace and args->workspace_bytes are ignored; inputs and outputs
+ * are the caller's as usual.  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *  - Limit: the carries need 64 * (segments - 1) * batch * d_inner bytes plus flags; a problem that needs more
+ *    than HX_SCAN_NOALLOC_SCRATCH_BYTES is refused with HX_ERR_INVALID_INPUT and a message giving both sizes.
+ *  - The first call on a device looks up the array's device address (once per device, that device must be
+ *    current); make that first call before starting any stream capture.
+ *  - All calls on a device share the one array.  The flags are cleared at the start of every call, so a call
+ *    never sees the previous call's contents, but two calls that overlap on the GPU (different streams) race
+ *    on it: keep calls to this entry point ordered on one stream per device. */
+#define HX_SCAN_NOALLOC_SCRATCH_BYTES (8u << 20)
+HX_API hx_status hx_selective_scan_fwd_noalloc(const hx_scan_args *args, void *stream);
 /* Synchronous helper, meant for weight-load time: *is_geometric = 1 when every row of A [d_inner, d_state]
  * satisfies A[d][n] == (n+1) * A[d][0] to fp32 rounding (true for the S4D-real initialisation
  * A_log[d][n] = log(n+1)).  Copies A to the host. */

@@ -1,0 +1,70 @@
+"""The allocation-free scan entry point (hx_selective_scan_fwd_noalloc), collected last.
+
+It exists for callers that may not allocate device memory when they run the scan (all memory already in
+their own pool, or a thread that must stay out of the CUDA allocator).  The carries between sequence
+segments live in an array inside the library instead of a caller workspace, so the output must equal what
+hx_selective_scan_fwd(variant = SEQSPLIT) produces with a caller workspace -- the same kernel on the same
+inputs -- and must stay equal on a second call, which reuses the array with the first call's contents in it."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import to_dev
+from helixml_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _args(L, dev, y, dtype_code, seq_splits):
+    a = L.ScanArgs()
+    Bsz, Lq, D = dev["x"].shape
+    a.batch, a.seq_len, a.d_inner, a.d_state, a.d_conv = Bsz, Lq, D, 16, 4
+    a.io_dtype, a.dt_softplus, a.seq_splits, a.a_geometric = dtype_code, 1, seq_splits, 1
+    for name, t in (("x", dev["x"]), ("dt", dev["dt"]), ("z", dev["z"]), ("y", y)):
+        setattr(a, name, t.data_ptr())
+        setattr(a, f"{name}_batch_stride", t.stride(0))
+        setattr(a, f"{name}_row_stride", t.stride(1))
+    for name, f, t in (("Bm", "B", dev["B"]), ("Cm", "C", dev["C"])):
+        setattr(a, name, t.data_ptr())
+        setattr(a, f"{f}_batch_stride", t.stride(0))
+        setattr(a, f"{f}_row_stride", t.stride(1))
+    a.A, a.Dskip, a.conv_w = dev["A"].data_ptr(), dev["D"].data_ptr(), dev["conv_w"].data_ptr()
+    return a
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f32"])
+def test_noalloc_matches_workspace_variant_twice(dtype):
+    import torch
+    from helixml_b200 import _lib as L, ops
+    lib = L.lib()
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    code = L.HX_BF16 if dtype == "bf16" else L.HX_F32
+    for call, seed in enumerate((91, 92)):  # two calls in a row, different data: the second reuses the array
+        inp = synth.scan_inputs(seed, 3, 260, 72, 16, 4, bf16=dtype == "bf16")
+        inp["dt"] = inp["dt"] - 2.0  # long memory: a wrong or stale carry would be visible
+        if dtype == "bf16":
+            inp["dt"] = synth.round_bf16(inp["dt"])
+        dev = {k: to_dev(v, "bf16" if (dtype == "bf16" and k in ("x", "dt", "z", "B", "C")) else None) for k, v in inp.items()}
+        want = ops.selective_scan(dev["x"], dev["dt"], dev["A"], dev["B"], dev["C"], D=dev["D"], z=dev["z"],
+                                  conv_w=dev["conv_w"], variant=L.SCAN_SEQSPLIT, seq_splits=4, a_geometric=True)
+        got = torch.full_like(want, float("nan"))
+        a = _args(L, dev, got, code, 4)
+        L.check(lib.hx_selective_scan_fwd_noalloc(C.byref(a), stream))
+        torch.cuda.synchronize()
+        assert L.device_status() == 0
+        # same kernel, same inputs: the tests' tolerance for two runs of one kernel is exact equality
+        assert torch.equal(got, want), f"call {call}: max diff {(got.float() - want.float()).abs().max().item()}"
+
+
+def test_noalloc_rejects_oversized_problem():
+    from helixml_b200 import _lib as L
+    lib = L.lib()
+    a = L.ScanArgs()
+    a.batch, a.seq_len, a.d_inner, a.d_state, a.io_dtype, a.seq_splits = 64, 8192, 4096, 16, L.HX_BF16, 8
+    for f in ("x", "dt", "Bm", "Cm", "y", "A"):
+        setattr(a, f, 256)  # never dereferenced: the size check comes first
+    a.x_row_stride = a.dt_row_stride = a.y_row_stride = 4096
+    a.B_row_stride = a.C_row_stride = 16
+    st = lib.hx_selective_scan_fwd_noalloc(C.byref(a), None)
+    assert st == 10 and b"holds" in lib.hx_last_error()  # InvalidInput, message names both sizes
