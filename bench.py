@@ -183,7 +183,7 @@ def run_scan(args, cfg, name):
 
     def step():
         ops.selective_scan(t["x"], t["dt"], t["A"], t["B"], t["C"], D=t["D"], z=t["z"], conv_w=t["conv_w"], variant=variant,
-                           a_geometric=True, lanes_per_channel=args.lpc, out=y)
+                           a_geometric=True, lanes_per_channel=args.lpc, out=y, tune=args.tune)
 
     def barrier():
         if world > 1:
@@ -253,7 +253,7 @@ def run_scan(args, cfg, name):
             "io_dtype": "bf16", "data": "synthetic",
             "config": {"workload": name, **{k: cfg[k] for k in ("batch", "seq_len", "d_inner", "d_state", "d_conv")},
                        "per_gpu": "full workload on every rank", "l2": "inputs (0.8 GB+) exceed the 126 MB L2, no flush",
-                       "variant": args.variant, "lanes_per_channel": args.lpc},
+                       "variant": args.variant, "lanes_per_channel": args.lpc, "tune": args.tune},
             "roofline": {"bound": "hbm", "kernel": "scan_tiled_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "algorithmic_bytes_per_launch": alg, "traffic": None},
@@ -452,6 +452,7 @@ def main():
     ap.add_argument("--workload", default="lm_cfg3", choices=sorted(WORKLOADS))
     ap.add_argument("--variant", default="auto", choices=["auto", "tiled", "simple"])
     ap.add_argument("--lpc", type=int, default=0)
+    ap.add_argument("--tune", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

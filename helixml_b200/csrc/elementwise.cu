@@ -42,8 +42,9 @@ template <> struct Vec<__nv_bfloat16> {
 
 // ---------------------------------------------------------------- conv1d + SiLU
 // Thread = one 16-byte channel group x TB consecutive time steps (sliding window over the taps).
-template <typename T, bool VEC, int TB>
-__global__ void __launch_bounds__(128)
+// FASTM (bf16 I/O): SiLU through ex2/rcp on the special-function unit; fp32 I/O keeps the accurate form.
+template <typename T, bool VEC, int TB, bool FASTM = (sizeof(T) == 2)>
+__global__ void __launch_bounds__(64)
 conv_silu_kernel(const T *x, int64_t xb, int64_t xr, const float *cw, const float *cb, T *u, int64_t ub, int64_t ur,
                  int L, int D, int K) {
     constexpr int VN = VEC ? Vec<T>::N : 1;
@@ -55,9 +56,16 @@ conv_silu_kernel(const T *x, int64_t xb, int64_t xr, const float *cw, const floa
     float w[VN][4], bias[VN];
 #pragma unroll
     for (int e = 0; e < VN; ++e) {
+        if (K == 4 && (reinterpret_cast<uintptr_t>(cw) & 15) == 0) {
+            const float4 f = *reinterpret_cast<const float4 *>(cw + (int64_t)(d + e) * 4);
+            w[e][0] = f.x; w[e][1] = f.y; w[e][2] = f.z; w[e][3] = f.w;
+        } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) w[e][j] = 0.f;
-        for (int j = 0; j < K; ++j) w[e][4 - K + j] = cw[(int64_t)(d + e) * K + j];
+            for (int j = 0; j < 4; ++j) {  // tap j of the 4-wide window is tap j-(4-K) of the K given ones
+                const int src = j - (4 - K);
+                w[e][j] = src >= 0 ? cw[(int64_t)(d + e) * K + src] : 0.f;
+            }
+        }
         bias[e] = cb ? cb[d + e] : 0.f;
     }
     const T *xp = x + b * xb + d;
@@ -80,7 +88,7 @@ conv_silu_kernel(const T *x, int64_t xb, int64_t xr, const float *cw, const floa
             for (int e = 0; e < VN; ++e) win[j][e] = 0.f;
         }
     }
-#pragma unroll 4
+#pragma unroll 8
     for (int k = 0; k < TB; ++k) {
         const int t = t0 + k;
         if (t >= L) break;
@@ -100,7 +108,7 @@ conv_silu_kernel(const T *x, int64_t xb, int64_t xr, const float *cw, const floa
             c += w[e][1] * win[1][e];
             c += w[e][2] * win[2][e];
             c += w[e][3] * cur[e];
-            out[e] = silu_acc(c);
+            out[e] = FASTM ? silu_fast(c) : silu_acc(c);
             win[0][e] = win[1][e];
             win[1][e] = win[2][e];
             win[2][e] = cur[e];
@@ -144,6 +152,81 @@ rmsnorm_kernel(const TX *x, float *residual, const float *w, TY *y, int64_t rows
     }
 }
 
+// Vector path: d is a multiple of 8 and at most 8*32*NV; every lane keeps its NV groups of 8 values in
+// registers between the two passes, so each operand crosses HBM once.
+template <typename TX, typename TY, int NV>
+__global__ void __launch_bounds__(256)
+rmsnorm_vec_kernel(const TX *x, float *residual, const float *w, TY *y, int64_t rows, int d, float eps) {
+    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const int groups = d / 8;
+    float v[NV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int g = lane + 32 * i;
+        if (g < groups) {
+            const int64_t off = row * d + g * 8;
+            if (x) {
+                if constexpr (sizeof(TX) == 2) {
+                    Vec<__nv_bfloat16> t;
+                    t.load(reinterpret_cast<const __nv_bfloat16 *>(x) + off);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) v[i][e] = t.v[e];
+                } else {
+                    Vec<float> t0, t1;
+                    t0.load(reinterpret_cast<const float *>(x) + off);
+                    t1.load(reinterpret_cast<const float *>(x) + off + 4);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { v[i][e] = t0.v[e]; v[i][4 + e] = t1.v[e]; }
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[i][e] = 0.f;
+            }
+            if (residual) {
+                Vec<float> r0, r1;
+                r0.load(residual + off);
+                r1.load(residual + off + 4);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { v[i][e] += r0.v[e]; v[i][4 + e] += r1.v[e]; }
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { r0.v[e] = v[i][e]; r1.v[e] = v[i][4 + e]; }
+                r0.store(residual + off);
+                r1.store(residual + off + 4);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float inv = 1.0f / sqrtf(ss / (float)d + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int g = lane + 32 * i;
+        if (g < groups) {
+            const int64_t off = row * d + g * 8;
+            Vec<float> w0, w1;
+            w0.load(w + g * 8);
+            w1.load(w + g * 8 + 4);
+            if constexpr (sizeof(TY) == 2) {
+                Vec<__nv_bfloat16> o;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { o.v[e] = v[i][e] * inv * w0.v[e]; o.v[4 + e] = v[i][4 + e] * inv * w1.v[e]; }
+                o.store(reinterpret_cast<__nv_bfloat16 *>(y) + off);
+            } else {
+                Vec<float> o0, o1;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { o0.v[e] = v[i][e] * inv * w0.v[e]; o1.v[e] = v[i][4 + e] * inv * w1.v[e]; }
+                o0.store(reinterpret_cast<float *>(y) + off);
+                o1.store(reinterpret_cast<float *>(y) + off + 4);
+            }
+        }
+    }
+}
+
 // ---------------------------------------------------------------- embedding gather
 template <typename TE, typename TO>
 __global__ void __launch_bounds__(256)
@@ -178,12 +261,12 @@ hx_status hx_conv1d_silu_fwd(const void *x, int64_t xb, int64_t xr, const float 
     HX_REQUIRE(xr >= d_inner && ur >= d_inner, HX_ERR_SHAPE_MISMATCH, "row stride smaller than d_inner");
     HX_REQUIRE(batch <= 65535, HX_ERR_INVALID_DIMENSION, "batch %d exceeds the grid limit", batch);
     cudaStream_t st = (cudaStream_t)stream;
-    constexpr int TB = 16;
+    constexpr int TB = 64;
     const int es = io_dtype == HX_BF16 ? 2 : 4, vn = 16 / es;
     const bool vec = d_inner % vn == 0 && xr % vn == 0 && ur % vn == 0 && xb % vn == 0 && ub % vn == 0 &&
                      (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(u) & 15) == 0;
     const int groups = vec ? d_inner / vn : d_inner;
-    dim3 grid((groups + 127) / 128, (seq_len + TB - 1) / TB, batch), block(128);
+    dim3 grid((groups + 63) / 64, (seq_len + TB - 1) / TB, batch), block(64);
     if (io_dtype == HX_BF16) {
         auto xp = static_cast<const __nv_bfloat16 *>(x);
         auto up = static_cast<__nv_bfloat16 *>(u);
@@ -210,6 +293,19 @@ hx_status hx_rmsnorm_fwd(const void *x, int32_t x_dtype, float *residual, const 
     const int wpb = 8;
     dim3 grid((unsigned)((rows + wpb - 1) / wpb)), block(wpb * 32);
     const bool xb = x_dtype == HX_BF16, yb = y_dtype == HX_BF16;
+    auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (d % 8 == 0 && d <= 8 * 32 * 4 && al16(x) && al16(residual) && al16(w) && al16(y)) {
+        // every lane holds up to 4 groups of 8 values (d <= 1024)
+#define HX_NORM_VEC(TX, TY)                                                                                      \
+        rmsnorm_vec_kernel<TX, TY, 4><<<grid, block, 0, st>>>(static_cast<const TX *>(x), residual, w, static_cast<TY *>(y), \
+                                                              rows, d, eps)
+        if (xb && yb) HX_NORM_VEC(__nv_bfloat16, __nv_bfloat16);
+        else if (xb) HX_NORM_VEC(__nv_bfloat16, float);
+        else if (yb) HX_NORM_VEC(float, __nv_bfloat16);
+        else HX_NORM_VEC(float, float);
+#undef HX_NORM_VEC
+        return hx::check_launch("rmsnorm_vec_kernel");
+    }
     if (xb && yb) rmsnorm_kernel<<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), residual, w, static_cast<__nv_bfloat16 *>(y), rows, d, eps);
     else if (xb) rmsnorm_kernel<<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), residual, w, static_cast<float *>(y), rows, d, eps);
     else if (yb) rmsnorm_kernel<<<grid, block, 0, st>>>(static_cast<const float *>(x), residual, w, static_cast<__nv_bfloat16 *>(y), rows, d, eps);

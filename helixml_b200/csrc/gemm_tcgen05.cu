@@ -82,19 +82,23 @@ template <int BN> struct TcCfg {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 256 + 1024;
+    static constexpr int OUT_STAGE_BYTES = 32 * 128;  // one epilogue warp's [32 rows x 128 bytes] staging tile
+    static constexpr int OUT_BYTES = 4 * 2 * OUT_STAGE_BYTES;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + 256 + 1024;
     static constexpr int THREADS = 192;
 };
 
 template <int BN, typename TC, int EPI>
 __global__ void __launch_bounds__(192, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w, const float *bias, TC *C,
-               int64_t ldc, int M, int N, int K, int vec_ok) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+               const __grid_constant__ CUtensorMap tm_c, const float *bias, TC *C, int64_t ldc, int M, int N, int K,
+               int vec_ok) {
     using Cfg = TcCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ __align__(16) char smem_raw[];
     char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // keeps the shared address space
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * Cfg::STAGE_BYTES);
+    char *out_stage = smem + STAGES * Cfg::STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(out_stage + Cfg::OUT_BYTES);
     // barriers: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]; then the TMEM base and the abort flag
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -180,7 +184,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     } else {
         // ============================================================ epilogue warps
         const int wq = warp & 3;  // TMEM lane quarter this warp may read
-        int tc = 0;
+        int tc = 0, sc = 0;       // tiles done; staged blocks issued (selects the staging buffer)
         bool ok = true;
         for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tc) {
             const int acc = tc & 1;
@@ -188,23 +192,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             if (!wait_or_abort(bar_acc_full(acc), (tc >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int m = m0 + wq * 32 + lane;
-            TC *crow = C + (int64_t)m * ldc;
+            if (vec_ok) {
+                // Coalesced path: 128 bytes of each of the warp's 32 rows go to a swizzled staging tile and
+                // leave with one TMA store; out-of-range rows and columns are clipped by the tensor map.
+                constexpr int CPB = 128 / (int)sizeof(TC);  // columns per staged block: 64 bf16 / 32 fp32
+                char *my_stage = out_stage + (warp - 2) * 2 * Cfg::OUT_STAGE_BYTES;
 #pragma unroll 1
-            for (int ch = 0; ch < BN / 32; ++ch) {
-                const int nb = n0 + ch * 32;
-                if (nb >= N) break;  // warp-uniform
-                uint32_t r[32];
-                tmem_ld32(tmem_base + acc * BN + ch * 32 + ((uint32_t)(wq * 32) << 16), r);
-                tmem_ld_wait();
-                float v[32];
+                for (int cb = 0; cb < BN / CPB; ++cb) {
+                    const int nb = n0 + cb * CPB;
+                    if (nb >= N) break;  // warp-uniform
+                    char *buf = my_stage + (sc & 1) * Cfg::OUT_STAGE_BYTES;
+                    ++sc;
+                    if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer is done
+                    __syncwarp();
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    float x = __uint_as_float(r[j]);
-                    if (bias) x += (nb + j < N) ? __ldg(bias + nb + j) : 0.f;
-                    v[j] = apply_epilogue<EPI>(x);
-                }
-                if (m < M) {
-                    if (vec_ok && nb + 32 <= N) {
+                    for (int half = 0; half < CPB / 32; ++half) {
+                        uint32_t r[32];
+                        tmem_ld32(tmem_base + acc * BN + cb * CPB + half * 32 + ((uint32_t)(wq * 32) << 16), r);
+                        tmem_ld_wait();
+                        float v[32];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            float x = __uint_as_float(r[j]);
+                            const int n = nb + half * 32 + j;
+                            if (bias) x += (n < N) ? __ldg(bias + n) : 0.f;
+                            v[j] = apply_epilogue<EPI>(x);
+                        }
+                        // 16-byte pieces of this lane's row, XOR-swizzled with the row index like the TMA box
                         if constexpr (sizeof(TC) == 2) {
 #pragma unroll
                             for (int q4 = 0; q4 < 4; ++q4) {
@@ -214,25 +228,50 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                                     const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[q4 * 8 + 2 * e], v[q4 * 8 + 2 * e + 1]);
                                     w[e] = *reinterpret_cast<const uint32_t *>(&h2);
                                 }
-                                *reinterpret_cast<uint4 *>(crow + nb + q4 * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                                const int chunk = half * 4 + q4;
+                                *reinterpret_cast<uint4 *>(buf + lane * 128 + ((chunk ^ (lane & 7)) << 4)) =
+                                    make_uint4(w[0], w[1], w[2], w[3]);
                             }
                         } else {
 #pragma unroll
                             for (int q4 = 0; q4 < 8; ++q4)
-                                *reinterpret_cast<float4 *>(crow + nb + q4 * 4) =
+                                *reinterpret_cast<float4 *>(buf + lane * 128 + ((q4 ^ (lane & 7)) << 4)) =
                                     make_float4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
                         }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (nb + j < N) st_f32(crow + nb + j, v[j]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&tm_c, smem_u32(buf), nb, m0 + wq * 32);
+                        tma_store_commit();
                     }
                 }
+            } else {
+            TC *crow = C + (int64_t)m * ldc;
+#pragma unroll 1
+            for (int ch = 0; ch < BN / 32; ++ch) {
+                const int nb = n0 + ch * 32;
+                if (nb >= N) break;  // warp-uniform
+                uint32_t r[32];
+                tmem_ld32(tmem_base + acc * BN + ch * 32 + ((uint32_t)(wq * 32) << 16), r);
+                tmem_ld_wait();
+                if (m < M) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float x = __uint_as_float(r[j]);
+                        if (nb + j < N) {
+                            if (bias) x += __ldg(bias + nb + j);
+                            st_f32(crow + nb + j, apply_epilogue<EPI>(x));
+                        }
+                    }
+                }
+            }
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_acc_empty(acc));
         }
+        if (lane == 0) tma_store_wait_all<0>();  // staging tiles must outlive their TMA stores
     }
 
     // teardown: everybody meets, then the allocating warp frees tensor memory
@@ -246,8 +285,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 }
 
 template <int BN, typename TC, int EPI>
-static hx_status launch_tc_inst(const CUtensorMap &ma, const CUtensorMap &mw, const float *bias, void *C, int64_t ldc, int M,
-                                int N, int K, int vec_ok, cudaStream_t st) {
+static hx_status launch_tc_inst(const CUtensorMap &ma, const CUtensorMap &mw, const CUtensorMap &mc, const float *bias, void *C,
+                                int64_t ldc, int M, int N, int K, int vec_ok, cudaStream_t st) {
     using Cfg = TcCfg<BN>;
     auto kern = gemm_tc_kernel<BN, TC, EPI>;
     static bool attr_set[64] = {false};
@@ -259,17 +298,17 @@ static hx_status launch_tc_inst(const CUtensorMap &ma, const CUtensorMap &mw, co
     }
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(ma, mw, bias, static_cast<TC *>(C), ldc, M, N, K, vec_ok);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(ma, mw, mc, bias, static_cast<TC *>(C), ldc, M, N, K, vec_ok);
     return check_launch("gemm_tc_kernel");
 }
 
 template <int BN, typename TC>
-static hx_status launch_tc_epi(const CUtensorMap &ma, const CUtensorMap &mw, const float *bias, void *C, int64_t ldc, int M,
-                               int N, int K, int vec_ok, int epi, cudaStream_t st) {
+static hx_status launch_tc_epi(const CUtensorMap &ma, const CUtensorMap &mw, const CUtensorMap &mc, const float *bias, void *C,
+                               int64_t ldc, int M, int N, int K, int vec_ok, int epi, cudaStream_t st) {
     switch (epi) {
-        case kEpiNone: return launch_tc_inst<BN, TC, kEpiNone>(ma, mw, bias, C, ldc, M, N, K, vec_ok, st);
-        case kEpiSilu: return launch_tc_inst<BN, TC, kEpiSilu>(ma, mw, bias, C, ldc, M, N, K, vec_ok, st);
-        case kEpiSoftplus: return launch_tc_inst<BN, TC, kEpiSoftplus>(ma, mw, bias, C, ldc, M, N, K, vec_ok, st);
+        case kEpiNone: return launch_tc_inst<BN, TC, kEpiNone>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, st);
+        case kEpiSilu: return launch_tc_inst<BN, TC, kEpiSilu>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, st);
+        case kEpiSoftplus: return launch_tc_inst<BN, TC, kEpiSoftplus>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, st);
         default: return fail(HX_ERR_INVALID_INPUT, "unknown epilogue %d", epi);
     }
 }
@@ -308,11 +347,19 @@ extern "C" hx_status hx_gemm_bf16(const void *A, int64_t lda, const void *W, int
     if ((s = hx::encode_tensor_map(&ma, HX_BF16, 2, A, dims_a, str_a, box_a, true)) != HX_OK) return s;
     if ((s = hx::encode_tensor_map(&mw, HX_BF16, 2, W, dims_w, str_w, box_w, true)) != HX_OK) return s;
     const int es = c_dtype == HX_BF16 ? 2 : 4;
+    // C leaves through TMA when its base and row stride meet the 16-byte rule; otherwise by plain stores
     const int vec_ok = ((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * es) % 16 == 0) ? 1 : 0;
-    if (BN == 256) {
-        if (c_dtype == HX_BF16) return launch_tc_epi<256, __nv_bfloat16>(ma, mw, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
-        return launch_tc_epi<256, float>(ma, mw, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
+    CUtensorMap mc = ma;
+    if (vec_ok) {
+        const uint64_t dims_c[2] = {(uint64_t)N, (uint64_t)M};
+        const uint64_t str_c[1] = {(uint64_t)ldc * es};
+        const uint32_t box_c[2] = {(uint32_t)(128 / es), 32};
+        if ((s = hx::encode_tensor_map(&mc, c_dtype, 2, C, dims_c, str_c, box_c, true)) != HX_OK) return s;
     }
-    if (c_dtype == HX_BF16) return launch_tc_epi<128, __nv_bfloat16>(ma, mw, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
-    return launch_tc_epi<128, float>(ma, mw, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
+    if (BN == 256) {
+        if (c_dtype == HX_BF16) return launch_tc_epi<256, __nv_bfloat16>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
+        return launch_tc_epi<256, float>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
+    }
+    if (c_dtype == HX_BF16) return launch_tc_epi<128, __nv_bfloat16>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
+    return launch_tc_epi<128, float>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
 }

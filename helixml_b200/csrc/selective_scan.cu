@@ -585,15 +585,16 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                     const float4 *Bq = reinterpret_cast<const float4 *>(sBf + (tl0 + row) * 16 + q * S);
                     const float4 *Cq = reinterpret_cast<const float4 *>(sCf + (tl0 + row) * 16 + q * S);
                     const float2 x2 = splat2(xin);
-                    float2 yacc = make_float2(0.f, 0.f);
+                    float2 yacc0 = make_float2(0.f, 0.f), yacc1 = make_float2(0.f, 0.f);  // two chains for ILP
 #pragma unroll
                     for (int j4 = 0; j4 < S / 4; ++j4) {
                         const float4 bv = Bq[j4], cv = Cq[j4];
                         h[2 * j4] = fma2(a[2 * j4], h[2 * j4], mul2(x2, make_float2(bv.x, bv.y)));
                         h[2 * j4 + 1] = fma2(a[2 * j4 + 1], h[2 * j4 + 1], mul2(x2, make_float2(bv.z, bv.w)));
-                        yacc = fma2(make_float2(cv.x, cv.y), h[2 * j4], yacc);
-                        yacc = fma2(make_float2(cv.z, cv.w), h[2 * j4 + 1], yacc);
+                        yacc0 = fma2(make_float2(cv.x, cv.y), h[2 * j4], yacc0);
+                        yacc1 = fma2(make_float2(cv.z, cv.w), h[2 * j4 + 1], yacc1);
                     }
+                    const float2 yacc = add2(yacc0, yacc1);
                     part[k] = yacc.x + yacc.y;
                 }
                 // combine the LPC partial sums of each channel so that lane q ends up with step q
@@ -766,7 +767,10 @@ static int choose_lpc(const hx_scan_args *a) {
 static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st) {
     HX_REQUIRE(a->d_state == 16, HX_ERR_UNSUPPORTED_OPERATION, "the tiled scan needs d_state == 16 (got %d)", a->d_state);
     const bool bf = a->io_dtype == HX_BF16;
-    const int ES = bf ? 2 : 4, DT = 128 / ES, TC = bf ? kChunkBf16 : kChunkF32;
+    // `reserved` picks another (chunk, stages) pair for the bf16 / geometric / standard path (tuning knob)
+    const bool stdp0 = a->conv_w != nullptr && a->z != nullptr && a->dt_softplus != 0;
+    const int tune = (bf && a->a_geometric && stdp0) ? a->reserved : 0;
+    const int ES = bf ? 2 : 4, DT = 128 / ES, TC = tune >= 1 ? 16 : (bf ? kChunkBf16 : kChunkF32);
     const int tiles = (a->d_inner + DT - 1) / DT;
     int n_seg = 1, seg_len = (a->seq_len + TC - 1) / TC * TC;
     if (split) seg_plan(a, TC, &n_seg, &seg_len);
@@ -833,6 +837,16 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
         if (stdp) return launch_tiled_inst<T, LPC, GEOM, TCv, ST, true>(a, p, maps, grid, st);  \
         return launch_tiled_inst<T, LPC, GEOM, TCv, ST, false>(a, p, maps, grid, st);           \
     } while (0)
+    if (tune == 1) {
+        if (lpc == 1) return launch_tiled_inst<__nv_bfloat16, 1, true, 16, 3, true>(a, p, maps, grid, st);
+        if (lpc == 2) return launch_tiled_inst<__nv_bfloat16, 2, true, 16, 3, true>(a, p, maps, grid, st);
+        return launch_tiled_inst<__nv_bfloat16, 4, true, 16, 3, true>(a, p, maps, grid, st);
+    }
+    if (tune == 2) {
+        if (lpc == 1) return launch_tiled_inst<__nv_bfloat16, 1, true, 16, 4, true>(a, p, maps, grid, st);
+        if (lpc == 2) return launch_tiled_inst<__nv_bfloat16, 2, true, 16, 4, true>(a, p, maps, grid, st);
+        return launch_tiled_inst<__nv_bfloat16, 4, true, 16, 4, true>(a, p, maps, grid, st);
+    }
     if (bf) {
         if (geom) {
             if (lpc == 1) HX_TILED_CASE(__nv_bfloat16, 1, true, kChunkBf16, 2);

@@ -60,7 +60,7 @@ def scan_workspace_bytes(batch, seq_len, d_inner, dtype, seq_splits=0) -> int:
 
 def selective_scan(x, dt, A, Bm, Cm, D=None, z=None, conv_w=None, conv_b=None, dt_bias=None, dt_softplus=True,
                    variant=L.SCAN_AUTO, a_geometric=None, lanes_per_channel=0, return_state=False, out=None,
-                   workspace=None, seq_splits=0):
+                   workspace=None, seq_splits=0, tune=0):
     """Fused selective scan (hx_selective_scan_fwd).  x, dt, z, y: [B, L, D]; Bm, Cm: [B, L, N]."""
     Bsz, Lq, Dm = x.shape
     N = A.shape[1]
@@ -103,6 +103,7 @@ def selective_scan(x, dt, A, Bm, Cm, D=None, z=None, conv_w=None, conv_b=None, d
     a.a_geometric = 1 if a_geometric else 0
     a.lanes_per_channel = lanes_per_channel
     a.seq_splits = seq_splits
+    a.reserved = tune
     if variant == L.SCAN_SEQSPLIT:
         n = C.c_size_t(0)
         L.check(L.lib().hx_selective_scan_workspace_bytes(C.byref(a), C.byref(n)))
