@@ -32,6 +32,8 @@ WORKLOADS = {
     # the per-GPU shard of configuration 4 at 8 GPUs (channel shard): [64, 16384, 640]
     "scan_cfg4_shard8": dict(kind="scan", batch=64, seq_len=16384, d_inner=640, d_state=16, d_conv=4, seed=4),
     # benchmark configuration 3: byte-level Mamba LM prefill, 24 blocks, d_model 768, batch 32 x seq 2048, bf16
+    # a mid-size scan for profiling: enough chains for every kernel variant, 1.6 GB on the device
+    "scan_mid": dict(kind="scan", batch=64, seq_len=2048, d_inner=1536, d_state=16, d_conv=4, seed=5),
     "lm_cfg3": dict(kind="lm", n_layer=24, d_model=768, d_state=16, d_conv=4, expand=2, batch=32, seq_len=2048, seed=3),
 }
 
@@ -179,11 +181,12 @@ def run_scan(args, cfg, name):
 
     t = gpu_inputs(torch, cfg, device, seed_offset=rank)
     y = torch.empty_like(t["x"])
-    variant = {"auto": _lib.SCAN_AUTO, "tiled": _lib.SCAN_TILED, "simple": _lib.SCAN_SIMPLE}[args.variant]
+    ws = torch.empty(64 << 20, dtype=torch.uint8, device=device) if args.splits > 1 else None
+    variant = {"auto": _lib.SCAN_AUTO, "tiled": _lib.SCAN_TILED, "simple": _lib.SCAN_SIMPLE, "direct": _lib.SCAN_DIRECT}[args.variant]
 
     def step():
         ops.selective_scan(t["x"], t["dt"], t["A"], t["B"], t["C"], D=t["D"], z=t["z"], conv_w=t["conv_w"], variant=variant,
-                           a_geometric=True, lanes_per_channel=args.lpc, out=y, tune=args.tune)
+                           a_geometric=True, lanes_per_channel=args.lpc, out=y, tune=args.tune, seq_splits=args.splits, workspace=ws)
 
     def barrier():
         if world > 1:
@@ -253,7 +256,7 @@ def run_scan(args, cfg, name):
             "io_dtype": "bf16", "data": "synthetic",
             "config": {"workload": name, **{k: cfg[k] for k in ("batch", "seq_len", "d_inner", "d_state", "d_conv")},
                        "per_gpu": "full workload on every rank", "l2": "inputs (0.8 GB+) exceed the 126 MB L2, no flush",
-                       "variant": args.variant, "lanes_per_channel": args.lpc, "tune": args.tune},
+                       "variant": args.variant, "lanes_per_channel": args.lpc, "tune": args.tune, "seq_splits": args.splits},
             "roofline": {"bound": "hbm", "kernel": "scan_tiled_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "algorithmic_bytes_per_launch": alg, "traffic": None},
@@ -450,9 +453,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="lm_cfg3", choices=sorted(WORKLOADS))
-    ap.add_argument("--variant", default="auto", choices=["auto", "tiled", "simple"])
+    ap.add_argument("--variant", default="auto", choices=["auto", "tiled", "simple", "direct"])
     ap.add_argument("--lpc", type=int, default=0)
     ap.add_argument("--tune", type=int, default=0)
+    ap.add_argument("--splits", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

@@ -10,7 +10,7 @@ LIB_PATH = os.path.join(_HERE, "libhelix_b200.so")
 
 HX_OK = 0
 HX_F32, HX_BF16, HX_U8 = 0, 1, 2
-SCAN_AUTO, SCAN_SIMPLE, SCAN_TILED, SCAN_SEQSPLIT = 0, 1, 2, 3
+SCAN_AUTO, SCAN_SIMPLE, SCAN_TILED, SCAN_SEQSPLIT, SCAN_DIRECT = 0, 1, 2, 3, 4
 EPI_NONE, EPI_SILU, EPI_SOFTPLUS = 0, 1, 2
 
 STATUS_NAMES = ["Ok", "ShapeMismatch", "InvalidDimension", "DeviceMismatch", "DTypeMismatch", "UnsupportedOperation",
@@ -73,6 +73,7 @@ _PROTOS = {
     "hx_stream_synchronize": (C.c_int, [C.c_void_p]),
     "hx_selective_scan_fwd": (C.c_int, [C.POINTER(ScanArgs), C.c_void_p]),
     "hx_selective_scan_workspace_bytes": (C.c_int, [C.POINTER(ScanArgs), C.POINTER(C.c_size_t)]),
+    "hx_selective_scan_suggest_splits": (C.c_int32, [C.POINTER(ScanArgs)]),
     "hx_selective_scan_host": (C.c_int, [C.POINTER(ScanArgs), C.c_void_p, C.c_size_t, C.c_void_p]),
     "hx_selective_scan_host_workspace_bytes": (C.c_int, [C.POINTER(ScanArgs), C.POINTER(C.c_size_t)]),
     "hx_selective_scan_fwd_noalloc": (C.c_int, [C.POINTER(ScanArgs), C.c_void_p]),

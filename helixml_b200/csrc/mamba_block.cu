@@ -11,9 +11,18 @@ namespace hx {
 namespace block {
 
 struct Layout {
-    size_t xz, u, dbc, dtl, y, total;
+    size_t xz, u, dbc, dtl, y, scan_ws, scan_ws_bytes, total;
     int64_t W;  // row width of the x_proj output
+    int splits; // sequence segments of the scan
 };
+
+static hx_scan_args scan_shape(const hx_mamba_block_args *a) {
+    hx_scan_args sa;
+    memset(&sa, 0, sizeof(sa));
+    sa.batch = a->batch; sa.seq_len = a->seq_len; sa.d_inner = a->d_inner; sa.d_state = a->d_state;
+    sa.io_dtype = a->io_dtype; sa.variant = a->scan_variant;
+    return sa;
+}
 
 static Layout plan(const hx_mamba_block_args *a) {
     const size_t es = dtype_size(a->io_dtype);
@@ -28,6 +37,13 @@ static Layout plan(const hx_mamba_block_args *a) {
     l.dbc = off; off += up(T * l.W * es);
     l.dtl = off; off += up(T * E * es);
     l.y = off; off += up(T * E * es);
+    // carries of a split scan (the split evens out the load; see hx_selective_scan_suggest_splits)
+    hx_scan_args sa = scan_shape(a);
+    l.splits = (a->scan_variant == HX_SCAN_SIMPLE || a->d_state != 16) ? 1 : hx_selective_scan_suggest_splits(&sa);
+    sa.seq_splits = l.splits;
+    l.scan_ws_bytes = 0;
+    if (l.splits > 1) hx_selective_scan_workspace_bytes(&sa, &l.scan_ws_bytes);
+    l.scan_ws = off; off += up(l.scan_ws_bytes);
     l.total = off + 256;
     return l;
 }
@@ -116,6 +132,11 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     sa.A = a->A; sa.Dskip = a->Dskip; sa.dt_bias = a->b_dt;
     sa.conv_w = nullptr; sa.conv_b = nullptr;  // u is already activated
     sa.a_geometric = a->a_geometric;
+    if (l.splits > 1) {
+        sa.seq_splits = l.splits;
+        sa.workspace = ws + l.scan_ws;
+        sa.workspace_bytes = l.scan_ws_bytes;
+    }
     if ((s = hx_selective_scan_fwd(&sa, stream)) != HX_OK) return s;
     mark(5);
     // 6. out = y W_out^T                                 [T, M]

@@ -1,0 +1,425 @@
+// scan_direct_kernel: the fused selective scan with one lane per channel.
+//
+// Profiling the lane-split kernel (scan_tiled_kernel) showed where its time goes: shared-memory results
+// return to registers at 128 bytes/clk/SM whatever the broadcast, so the fp32 B[t][n], C[t][n] operands every
+// lane needs cost one wavefront per 32 floats delivered, and the point-wise results handed between lanes
+// through shared-memory records cost as much again.  This kernel removes the records and lets one delivery
+// of B/C serve more points:
+//   * a lane owns CPL (1 or 2) adjacent channels and keeps all 16 states of each in registers (fp32,
+//     packed as 8 x f32x2 per channel); the conv window lives in registers too;
+//   * per time step the lane loads B[t][0..15] and C[t][0..15] once (8 x 128-bit broadcast loads) and uses
+//     them for its CPL channels, so the delivery per point falls as 1/CPL;
+//   * the point-wise math (conv, SiLU, softplus, decay, gate) runs in-line, packed f32x2 over the channel
+//     pair when CPL == 2; with geometric A the 16 decays are powers of one exponential;
+//   * no shuffles, no shared-memory traffic between lanes.
+// A warp therefore covers 32*CPL channels; a CTA has 4 such warps plus the producer warp, which issues the
+// TMA loads (unswizzled 128-byte-wide boxes: every warp-wide access is one contiguous row), widens B/C to
+// fp32 once per CTA and stores finished y tiles with TMA.  Barrier scheme, bounded waits, carry hand-over for
+// split sequences and the status word are those of scan_tiled_kernel.
+#pragma once
+
+namespace hx {
+namespace scan {
+
+template <typename T, int CPL_, bool GEOM_, bool STD_>
+struct DirectCfg {
+    static constexpr int CPL = CPL_;
+    static constexpr bool GEOM = GEOM_;
+    static constexpr bool STD = STD_;
+    static constexpr bool FAST = sizeof(T) == 2;
+    static constexpr int ES = sizeof(T);
+    static constexpr int TC = 16;                      // time steps per chunk
+    static constexpr int STAGES = 3;
+    static constexpr int NWARP = 4;                    // consumer warps
+    static constexpr int BOXC = 128 / ES;              // channels per 128-byte box
+    static constexpr int WC = 32 * CPL;                // channels per warp
+    static constexpr int WPB = BOXC / WC;              // warps per box (1 or 2)
+    static constexpr int NB = NWARP / WPB;             // boxes per CTA
+    static constexpr int DT = NB * BOXC;               // channels per CTA
+    static constexpr int THREADS = (NWARP + 1) * 32;
+    static constexpr int X_BYTES = (TC + 3) * 128;
+    static constexpr int ROW_BYTES = TC * 128;
+    static constexpr int BOX_BYTES = X_BYTES + 2 * ROW_BYTES;       // x, dt, z of one box
+    static constexpr int BC_BYTES = (TC * 16 * ES + 127) / 128 * 128;
+    static constexpr int BCF_BYTES = TC * 16 * 4;
+    static constexpr int STAGE_BYTES = NB * BOX_BYTES + 2 * BC_BYTES + 2 * BCF_BYTES;
+    static constexpr int OUT_BYTES = NB * ROW_BYTES;                // one out buffer (all boxes)
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BYTES + 128 + 128;
+    static_assert(WC * ES <= 128, "a warp's channels must fit one 128-byte box");
+    static_assert(3 * STAGES + 4 <= 16, "barrier area too small");
+};
+
+template <typename T> __device__ __forceinline__ float2 ld_chan2(const char *p);  // two adjacent channels
+template <> __device__ __forceinline__ float2 ld_chan2<float>(const char *p) { return *reinterpret_cast<const float2 *>(p); }
+template <> __device__ __forceinline__ float2 ld_chan2<__nv_bfloat16>(const char *p) {
+    const uint32_t v = *reinterpret_cast<const uint32_t *>(p);
+    return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+}
+template <typename T> __device__ __forceinline__ float ld_chan1(const char *p);
+template <> __device__ __forceinline__ float ld_chan1<float>(const char *p) { return *reinterpret_cast<const float *>(p); }
+template <> __device__ __forceinline__ float ld_chan1<__nv_bfloat16>(const char *p) {
+    return __uint_as_float((uint32_t)(*reinterpret_cast<const uint16_t *>(p)) << 16);
+}
+
+template <typename T, typename Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS)
+scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dt,
+                   const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_B,
+                   const __grid_constant__ CUtensorMap tm_C, const __grid_constant__ CUtensorMap tm_y,
+                   const TiledParams p) {
+    constexpr int CPL = Cfg::CPL, TC = Cfg::TC, STAGES = Cfg::STAGES, NW = Cfg::NWARP, NB = Cfg::NB, ES = Cfg::ES;
+    constexpr bool GEOM = Cfg::GEOM, FAST = Cfg::FAST, STD = Cfg::STD;
+    const bool has_conv = STD || p.K > 0, has_z = STD || p.has_z, use_softplus = STD || p.dt_softplus;
+
+    extern __shared__ __align__(16) char smem_raw[];
+    char *smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);  // 128-byte alignment, shared space kept
+    char *stage_base = smem;
+    char *out_base = stage_base + STAGES * Cfg::STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(out_base + 2 * Cfg::OUT_BYTES);
+    const uint32_t bar0 = smem_u32(bars);
+    auto bar_full = [&](int s) { return bar0 + 8u * s; };
+    auto bar_ready = [&](int s) { return bar0 + 8u * (STAGES + s); };
+    auto bar_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };
+    auto bar_out_full = [&](int b) { return bar0 + 8u * (3 * STAGES + b); };
+    auto bar_out_empty = [&](int b) { return bar0 + 8u * (3 * STAGES + 2 + b); };
+    constexpr int OFF_BC = NB * Cfg::BOX_BYTES, OFF_C = OFF_BC + Cfg::BC_BYTES, OFF_BF = OFF_C + Cfg::BC_BYTES,
+                  OFF_CF = OFF_BF + Cfg::BCF_BYTES;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, b = blockIdx.y, seg = blockIdx.z;
+    const int d0 = tile * Cfg::DT;
+    const int t_seg0 = seg * p.seg_len;
+    const int t_seg1 = min(p.L, t_seg0 + p.seg_len);
+    const int nchunks = (t_seg1 - t_seg0 + TC - 1) / TC;
+    // boxes that hold at least one real channel (the others are neither loaded nor stored)
+    const int live_boxes = min(NB, (p.D - d0 + Cfg::BOXC - 1) / Cfg::BOXC);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full(s), 1);
+            mbar_init(bar_ready(s), 1);
+            mbar_init(bar_empty(s), NW);
+        }
+        for (int k = 0; k < 2; ++k) {
+            mbar_init(bar_out_full(k), NW);
+            mbar_init(bar_out_empty(k), 1);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == NW) {
+        // ================================================================ producer warp
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_x);
+            tma_prefetch_desc(&tm_dt);
+            tma_prefetch_desc(&tm_B);
+            tma_prefetch_desc(&tm_C);
+            tma_prefetch_desc(&tm_y);
+            if (has_z) tma_prefetch_desc(&tm_z);
+        }
+        const uint32_t stage_tx = live_boxes * ((TC + 3) * 128 + TC * 128 * (has_z ? 2 : 1)) + 2 * TC * 16 * ES;
+        auto issue = [&](int i) {
+            const int s = i % STAGES;
+            const int t0 = t_seg0 + i * TC;
+            const uint32_t sb = smem_u32(stage_base + s * Cfg::STAGE_BYTES);
+            mbar_expect_tx(bar_full(s), stage_tx);
+            for (int bx = 0; bx < live_boxes; ++bx) {
+                const uint32_t bb = sb + bx * Cfg::BOX_BYTES;
+                const int dc = d0 + bx * Cfg::BOXC;
+                tma_load_3d(bb, &tm_x, bar_full(s), dc, t0 - 3, b);
+                tma_load_3d(bb + Cfg::X_BYTES, &tm_dt, bar_full(s), dc, t0, b);
+                if (has_z) tma_load_3d(bb + Cfg::X_BYTES + Cfg::ROW_BYTES, &tm_z, bar_full(s), dc, t0, b);
+            }
+            tma_load_3d(sb + OFF_BC, &tm_B, bar_full(s), 0, t0, b);
+            tma_load_3d(sb + OFF_C, &tm_C, bar_full(s), 0, t0, b);
+        };
+        int issued = 0;
+        if (lane == 0)
+            for (; issued < STAGES && issued < nchunks; ++issued) issue(issued);
+        int fail_code = 0;
+        for (int i = 0; i <= nchunks; ++i) {
+            if (i < nchunks) {
+                const int s = i % STAGES;
+                const bool ok = mbar_wait(bar_full(s), (i / STAGES) & 1);
+                if (!__all_sync(0xffffffffu, ok)) { fail_code = kWaitFull; break; }
+                char *st = stage_base + s * Cfg::STAGE_BYTES;
+                // widen B and C of this chunk to fp32: TC*16 values per array, 8 per lane per round
+                constexpr int ROUNDS = TC * 16 * 2 / (32 * 8);
+#pragma unroll
+                for (int r = 0; r < ROUNDS; ++r) {
+                    const int e0 = (r * 32 + lane) * 8;
+                    const int arr = e0 / (TC * 16), ea = e0 % (TC * 16);
+                    const char *src = st + (arr ? OFF_C : OFF_BC) + ea * ES;
+                    float *dst = reinterpret_cast<float *>(st + (arr ? OFF_CF : OFF_BF)) + ea;
+                    if constexpr (ES == 2) {
+                        const uint4 raw = *reinterpret_cast<const uint4 *>(src);
+                        *reinterpret_cast<float4 *>(dst) =
+                            make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                                        __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+                        *reinterpret_cast<float4 *>(dst + 4) =
+                            make_float4(__uint_as_float(raw.z << 16), __uint_as_float(raw.z & 0xffff0000u),
+                                        __uint_as_float(raw.w << 16), __uint_as_float(raw.w & 0xffff0000u));
+                    } else {
+                        *reinterpret_cast<float4 *>(dst) = *reinterpret_cast<const float4 *>(src);
+                        *reinterpret_cast<float4 *>(dst + 4) = *reinterpret_cast<const float4 *>(src + 16);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_ready(s));
+            }
+            if (i >= 1) {
+                const int j = i - 1, ob = j & 1;
+                int fc = 0;
+                if (lane == 0) {
+                    if (!mbar_wait(bar_out_full(ob), (j >> 1) & 1)) {
+                        fc = kWaitOutFull;
+                    } else {
+                        for (int bx = 0; bx < live_boxes; ++bx)
+                            tma_store_3d(&tm_y, smem_u32(out_base + ob * Cfg::OUT_BYTES + bx * Cfg::ROW_BYTES),
+                                         d0 + bx * Cfg::BOXC, t_seg0 + j * TC, b);
+                        tma_store_commit();
+                        if (issued < nchunks) {
+                            if (!mbar_wait(bar_empty(j % STAGES), (j / STAGES) & 1)) {
+                                fc = kWaitEmpty;
+                            } else {
+                                issue(issued);
+                                ++issued;
+                            }
+                        }
+                        tma_store_wait_read<1>();
+                        if (j >= 1) mbar_arrive(bar_out_empty((j - 1) & 1));
+                    }
+                }
+                fc = __shfl_sync(0xffffffffu, fc, 0);
+                if (fc) { fail_code = fc; break; }
+            }
+        }
+        if (lane == 0) {
+            tma_store_wait_all<0>();
+            if (fail_code) {
+                atomicOr(&g_wait_status, fail_code);
+                for (int i = 0; i < issued; ++i) mbar_wait(bar_full(i % STAGES), (i / STAGES) & 1);
+            }
+        }
+        return;
+    }
+
+    // ==================================================================== consumer warps
+    const int box = warp / Cfg::WPB;                                   // box this warp reads
+    const int lane_byte = ((warp % Cfg::WPB) * Cfg::WC + lane * CPL) * ES;  // byte offset of the lane in a box row
+    const int dch = d0 + box * Cfg::BOXC + (warp % Cfg::WPB) * Cfg::WC + lane * CPL;  // first channel of the lane
+
+    float w_[CPL][4], cb_[CPL], db_[CPL], ds_[CPL], a0_[CPL];
+    float a2l[GEOM ? 1 : CPL][16];
+#pragma unroll
+    for (int e = 0; e < CPL; ++e) {
+        const int d = dch + e;
+        const bool okc = d < p.D;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int src = j - (4 - p.K);
+            w_[e][j] = (okc && p.K > 0 && src >= 0) ? p.conv_w[(int64_t)d * p.K + src] : 0.f;
+        }
+        cb_[e] = (okc && p.K > 0 && p.conv_b) ? p.conv_b[d] : 0.f;
+        db_[e] = (okc && p.dt_bias) ? p.dt_bias[d] : 0.f;
+        ds_[e] = (okc && p.Dskip) ? p.Dskip[d] : 0.f;
+        a0_[e] = okc ? p.A[(int64_t)d * 16] * kLog2e : 0.f;
+        if constexpr (!GEOM) {
+#pragma unroll
+            for (int n = 0; n < 16; ++n) a2l[e][n] = okc ? p.A[(int64_t)d * 16 + n] * kLog2e : 0.f;
+        }
+    }
+
+    float2 h[CPL][8];
+#pragma unroll
+    for (int e = 0; e < CPL; ++e)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[e][j] = make_float2(0.f, 0.f);
+
+    if (p.n_segments > 1 && seg > 0) {
+        const int fidx = (((seg - 1) * p.B + b) * gridDim.x + tile) * 8 + warp;
+        bool ok = false;
+        for (int it = 0; it < (1 << 22); ++it) {
+            int v;
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.flags + fidx) : "memory");
+            if (v == p.epoch) { ok = true; break; }
+            __nanosleep(200);
+        }
+        if (!ok) {
+            if (lane == 0) atomicOr(&g_wait_status, kWaitCarry);
+        } else {
+#pragma unroll
+            for (int e = 0; e < CPL; ++e)
+                if (dch + e < p.D) {
+                    const float2 *src = reinterpret_cast<const float2 *>(p.carry + ((((int64_t)(seg - 1) * p.B + b) * p.D + dch + e) * 16));
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) h[e][j] = src[j];
+                }
+        }
+    }
+
+    for (int i = 0; i < nchunks; ++i) {
+        const int s = i % STAGES, ob = i & 1;
+        if (!mbar_wait(bar_ready(s), (i / STAGES) & 1)) {
+            if (lane == 0) atomicOr(&g_wait_status, kWaitFull);
+            return;
+        }
+        const char *sx = stage_base + s * Cfg::STAGE_BYTES + box * Cfg::BOX_BYTES + lane_byte;  // row 0 = 3 steps back
+        const char *sd = sx + Cfg::X_BYTES, *sz = sd + Cfg::ROW_BYTES;
+        const float4 *sBf = reinterpret_cast<const float4 *>(stage_base + s * Cfg::STAGE_BYTES + OFF_BF);
+        const float4 *sCf = reinterpret_cast<const float4 *>(stage_base + s * Cfg::STAGE_BYTES + OFF_CF);
+        char *so = out_base + ob * Cfg::OUT_BYTES + box * Cfg::ROW_BYTES + lane_byte;
+        const int steps = min(TC, t_seg1 - (t_seg0 + i * TC));
+
+        // conv window: the three steps before the chunk come from the halo rows
+        float xw[CPL][3];
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            if constexpr (CPL == 2) {
+                const float2 v = ld_chan2<T>(sx + k * 128);
+                xw[0][k] = v.x;
+                xw[1][k] = v.y;
+            } else {
+                xw[0][k] = ld_chan1<T>(sx + k * 128);
+            }
+        }
+        if (i >= 2) {
+            if (!mbar_wait(bar_out_empty(ob), ((i >> 1) - 1) & 1)) {
+                if (lane == 0) atomicOr(&g_wait_status, kWaitOutEmpty);
+                return;
+            }
+        }
+
+#pragma unroll 4
+        for (int t = 0; t < steps; ++t) {
+            float xc[CPL], dr[CPL], zr[CPL];
+            if constexpr (CPL == 2) {
+                const float2 vx = ld_chan2<T>(sx + (t + 3) * 128), vd = ld_chan2<T>(sd + t * 128);
+                xc[0] = vx.x; xc[1] = vx.y; dr[0] = vd.x; dr[1] = vd.y;
+                if (has_z) {
+                    const float2 vz = ld_chan2<T>(sz + t * 128);
+                    zr[0] = vz.x; zr[1] = vz.y;
+                }
+            } else {
+                xc[0] = ld_chan1<T>(sx + (t + 3) * 128);
+                dr[0] = ld_chan1<T>(sd + t * 128);
+                if (has_z) zr[0] = ld_chan1<T>(sz + t * 128);
+            }
+            // B and C of this step, shared by the lane's channels
+            float4 Bv[4], Cv[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                Bv[k] = sBf[t * 4 + k];
+                Cv[k] = sCf[t * 4 + k];
+            }
+            float yout[CPL];
+#pragma unroll
+            for (int e = 0; e < CPL; ++e) {
+                // ---- point-wise
+                float u;
+                if (has_conv) {
+                    float c = cb_[e];
+                    c = fmaf(w_[e][0], xw[e][0], c);
+                    c = fmaf(w_[e][1], xw[e][1], c);
+                    c = fmaf(w_[e][2], xw[e][2], c);
+                    c = fmaf(w_[e][3], xc[e], c);
+                    u = silu_sel<FAST>(c);
+                } else {
+                    u = xc[e];
+                }
+                xw[e][0] = xw[e][1]; xw[e][1] = xw[e][2]; xw[e][2] = xc[e];
+                const float v = dr[e] + db_[e];
+                float dtv;
+                if (use_softplus) {
+                    if constexpr (FAST) {
+                        const float sp = kLn2 * lg2_approx(1.f + ex2_approx(v * kLog2e));
+                        dtv = v > 20.f ? v : sp;
+                    } else {
+                        dtv = softplus_acc(v);
+                    }
+                } else {
+                    dtv = v;
+                }
+                const float g = has_z ? silu_sel<FAST>(zr[e]) : 1.f;
+                const float xin = dtv * u;
+                // ---- decays
+                float2 a[8];
+                if constexpr (GEOM) {
+                    float r;
+                    if constexpr (FAST) r = ex2_approx(dtv * a0_[e]);
+                    else r = exp2f(dtv * a0_[e]);
+                    const float r2 = r * r;
+                    a[0] = make_float2(r, r2);
+                    a[1] = mul2(a[0], splat2(r2));
+                    const float r4 = a[1].y;
+                    a[2] = mul2(a[0], splat2(r4));
+                    a[3] = mul2(a[1], splat2(r4));
+                    const float r8 = a[3].y;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) a[4 + j] = mul2(a[j], splat2(r8));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if constexpr (FAST)
+                            a[j] = make_float2(ex2_approx(dtv * a2l[GEOM ? 0 : e][2 * j]), ex2_approx(dtv * a2l[GEOM ? 0 : e][2 * j + 1]));
+                        else
+                            a[j] = make_float2(exp2f(dtv * a2l[GEOM ? 0 : e][2 * j]), exp2f(dtv * a2l[GEOM ? 0 : e][2 * j + 1]));
+                    }
+                }
+                // ---- recurrence and output contraction, four independent accumulators
+                const float2 x2 = splat2(xin);
+                float2 acc[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    h[e][2 * k] = fma2(a[2 * k], h[e][2 * k], mul2(x2, make_float2(Bv[k].x, Bv[k].y)));
+                    h[e][2 * k + 1] = fma2(a[2 * k + 1], h[e][2 * k + 1], mul2(x2, make_float2(Bv[k].z, Bv[k].w)));
+                    acc[0] = fma2(make_float2(Cv[k].x, Cv[k].y), h[e][2 * k], acc[0]);
+                    acc[1] = fma2(make_float2(Cv[k].z, Cv[k].w), h[e][2 * k + 1], acc[1]);
+                }
+                const float2 ys = add2(acc[0], acc[1]);
+                yout[e] = (ys.x + ys.y + ds_[e] * u) * g;
+            }
+            if constexpr (CPL == 2) {
+                if constexpr (ES == 2) {
+                    const __nv_bfloat162 o = __floats2bfloat162_rn(yout[0], yout[1]);
+                    *reinterpret_cast<uint32_t *>(so + t * 128) = *reinterpret_cast<const uint32_t *>(&o);
+                } else {
+                    *reinterpret_cast<float2 *>(so + t * 128) = make_float2(yout[0], yout[1]);
+                }
+            } else {
+                st_f32(reinterpret_cast<T *>(so + t * 128), yout[0]);
+            }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(bar_empty(s));
+            mbar_arrive(bar_out_full(ob));
+        }
+    }
+
+    const bool last_seg = seg == p.n_segments - 1;
+#pragma unroll
+    for (int e = 0; e < CPL; ++e) {
+        if (dch + e >= p.D) continue;
+        float2 *dst = nullptr;
+        if (last_seg && p.h_last) dst = reinterpret_cast<float2 *>(p.h_last + ((int64_t)b * p.D + dch + e) * 16);
+        if (!last_seg) dst = reinterpret_cast<float2 *>(p.carry + (((int64_t)seg * p.B + b) * p.D + dch + e) * 16);
+        if (dst) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j] = h[e][j];
+        }
+    }
+    if (!last_seg) {
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+            const int fidx = ((seg * p.B + b) * gridDim.x + tile) * 8 + warp;
+            asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.flags + fidx), "r"(p.epoch) : "memory");
+        }
+    }
+}
+
+}  // namespace scan
+}  // namespace hx

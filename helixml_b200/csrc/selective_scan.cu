@@ -657,6 +657,14 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
     }
 }
 
+}  // namespace scan
+}  // namespace hx
+
+#include "scan_direct.cuh"
+
+namespace hx {
+namespace scan {
+
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
@@ -872,6 +880,109 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
     return HX_OK;
 }
 
+
+template <typename T, int CPL, bool GEOM, bool STD>
+static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *maps, dim3 grid, cudaStream_t st) {
+    using Cfg = DirectCfg<T, CPL, GEOM, STD>;
+    auto kern = scan_direct_kernel<T, Cfg>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    HX_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        HX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        attr_set[dev] = true;
+    }
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
+    return check_launch("scan_direct_kernel");
+}
+
+// channels per lane for the direct kernel: 2 when that still leaves about two warps per scheduler
+static int choose_cpl(const hx_scan_args *a) {
+    if (a->io_dtype != HX_BF16) return 1;
+    if (a->reserved == 1 || a->reserved == 2) return a->reserved;
+    const double chains = (double)a->batch * a->d_inner;
+    return chains / 64.0 >= 8.0 * sm_count() ? 2 : 1;
+}
+
+static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t st) {
+    HX_REQUIRE(a->d_state == 16, HX_ERR_UNSUPPORTED_OPERATION, "the direct scan needs d_state == 16 (got %d)", a->d_state);
+    const bool bf = a->io_dtype == HX_BF16;
+    const int ES = bf ? 2 : 4, BOXC = 128 / ES, TC = 16;
+    const int cpl = choose_cpl(a);
+    const int DT = bf ? (cpl == 2 ? 256 : 128) : 128;  // channels per CTA (4 consumer warps)
+    const int tiles = (a->d_inner + DT - 1) / DT;
+    int n_seg = 1, seg_len = (a->seq_len + TC - 1) / TC * TC;
+    if (split) seg_plan(a, bf ? kChunkBf16 : kChunkF32, &n_seg, &seg_len);
+
+    TiledParams p;
+    p.B = a->batch; p.L = a->seq_len; p.D = a->d_inner;
+    p.K = a->conv_w ? a->d_conv : 0;
+    p.has_z = a->z != nullptr;
+    p.dt_softplus = a->dt_softplus;
+    p.n_segments = n_seg; p.seg_len = seg_len;
+    p.A = a->A; p.Dskip = a->Dskip; p.conv_w = a->conv_w; p.conv_b = a->conv_b; p.dt_bias = a->dt_bias;
+    p.h_last = a->h_last;
+    p.carry = nullptr; p.flags = nullptr; p.epoch = 1;
+    if (n_seg > 1) {
+        const size_t need = workspace_bytes(a, n_seg);
+        HX_REQUIRE(a->workspace && a->workspace_bytes >= need, HX_ERR_INVALID_INPUT,
+                   "the sequence-split scan needs a workspace of %zu bytes (got %zu)", need, a->workspace_bytes);
+        char *ws = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(a->workspace) + 255) & ~uintptr_t(255));
+        const size_t carry = ((size_t)(n_seg - 1) * a->batch * a->d_inner * 16 * sizeof(float) + 255) / 256 * 256;
+        p.carry = reinterpret_cast<float *>(ws);
+        p.flags = reinterpret_cast<int *>(ws + carry);
+        HX_CUDA(cudaMemsetAsync(p.flags, 0, (size_t)(n_seg - 1) * a->batch * tiles_of(a) * 8 * sizeof(int), st));
+    }
+
+    CUtensorMap maps[6];
+    const uint64_t dims_d[3] = {(uint64_t)a->d_inner, (uint64_t)a->seq_len, (uint64_t)a->batch};
+    const uint64_t dims_n[3] = {16, (uint64_t)a->seq_len, (uint64_t)a->batch};
+    auto strides = [&](int64_t row, int64_t batch, uint64_t *out) {
+        out[0] = (uint64_t)row * ES;
+        out[1] = (uint64_t)batch * ES;
+    };
+    uint64_t sb[2];
+    const uint32_t box_x[3] = {(uint32_t)BOXC, (uint32_t)TC + 3, 1}, box_r[3] = {(uint32_t)BOXC, (uint32_t)TC, 1},
+                   box_n[3] = {16, (uint32_t)TC, 1};
+    hx_status s;
+    strides(a->x_row_stride, a->x_batch_stride, sb);
+    if ((s = encode_tensor_map(&maps[0], a->io_dtype, 3, a->x, dims_d, sb, box_x, false)) != HX_OK) return s;
+    strides(a->dt_row_stride, a->dt_batch_stride, sb);
+    if ((s = encode_tensor_map(&maps[1], a->io_dtype, 3, a->dt, dims_d, sb, box_r, false)) != HX_OK) return s;
+    if (a->z) {
+        strides(a->z_row_stride, a->z_batch_stride, sb);
+        if ((s = encode_tensor_map(&maps[2], a->io_dtype, 3, a->z, dims_d, sb, box_r, false)) != HX_OK) return s;
+    } else {
+        maps[2] = maps[1];
+    }
+    strides(a->B_row_stride, a->B_batch_stride, sb);
+    if ((s = encode_tensor_map(&maps[3], a->io_dtype, 3, a->Bm, dims_n, sb, box_n, false)) != HX_OK) return s;
+    strides(a->C_row_stride, a->C_batch_stride, sb);
+    if ((s = encode_tensor_map(&maps[4], a->io_dtype, 3, a->Cm, dims_n, sb, box_n, false)) != HX_OK) return s;
+    strides(a->y_row_stride, a->y_batch_stride, sb);
+    if ((s = encode_tensor_map(&maps[5], a->io_dtype, 3, a->y, dims_d, sb, box_r, false)) != HX_OK) return s;
+
+    HX_REQUIRE(a->batch <= 65535 && n_seg <= 65535, HX_ERR_INVALID_DIMENSION, "batch %d or segments %d exceed the grid limit",
+               a->batch, n_seg);
+    dim3 grid(tiles, a->batch, n_seg);
+    const bool geom = a->a_geometric != 0;
+    const bool stdp = a->conv_w != nullptr && a->z != nullptr && a->dt_softplus != 0;
+#define HX_DIRECT_CASE(T, CPL)                                                                     \
+    do {                                                                                           \
+        if (geom && stdp) return launch_direct_inst<T, CPL, true, true>(p, maps, grid, st);        \
+        if (geom) return launch_direct_inst<T, CPL, true, false>(p, maps, grid, st);               \
+        if (stdp) return launch_direct_inst<T, CPL, false, true>(p, maps, grid, st);               \
+        return launch_direct_inst<T, CPL, false, false>(p, maps, grid, st);                        \
+    } while (0)
+    if (bf) {
+        if (cpl == 2) HX_DIRECT_CASE(__nv_bfloat16, 2);
+        HX_DIRECT_CASE(__nv_bfloat16, 1);
+    }
+    HX_DIRECT_CASE(float, 1);
+#undef HX_DIRECT_CASE
+    return HX_OK;
+}
+
 }  // namespace scan
 
 hx_status read_status_scan(int *v, bool clear) {
@@ -892,13 +1003,18 @@ hx_status hx_selective_scan_fwd(const hx_scan_args *a, void *stream) {
     if (s != HX_OK) return s;
     if (a->batch == 0 || a->seq_len == 0 || a->d_inner == 0) return HX_OK;
     cudaStream_t st = (cudaStream_t)stream;
+    const bool split = a->seq_splits > 1;  // the tiled and direct kernels can both hand carries between segments
     switch (a->variant) {
         case HX_SCAN_SIMPLE: return hx::scan::launch_simple(a, st);
-        case HX_SCAN_TILED: return hx::scan::launch_tiled(a, false, st);
+        case HX_SCAN_TILED: return hx::scan::launch_tiled(a, split, st);
         case HX_SCAN_SEQSPLIT: return hx::scan::launch_tiled(a, true, st);
+        case HX_SCAN_DIRECT: return hx::scan::launch_direct(a, split, st);
         case HX_SCAN_AUTO: {
             if (a->d_state == 16) {
-                s = hx::scan::launch_tiled(a, false, st);
+                // enough independent chains for one lane per channel -> direct kernel, else split the states
+                const double chains = (double)a->batch * a->d_inner;
+                const bool direct = chains / 32.0 >= 8.0 * hx::sm_count();
+                s = direct ? hx::scan::launch_direct(a, split, st) : hx::scan::launch_tiled(a, split, st);
                 // an operand that does not meet the TMA alignment rules goes to the simple kernel
                 if (s != HX_ERR_UNSUPPORTED_OPERATION) return s;
             }
@@ -908,10 +1024,27 @@ hx_status hx_selective_scan_fwd(const hx_scan_args *a, void *stream) {
     }
 }
 
+int32_t hx_selective_scan_suggest_splits(const hx_scan_args *a) {
+    if (!a || a->d_state != 16 || a->batch <= 0 || a->seq_len <= 0 || a->d_inner <= 0) return 1;
+    // CTAs of the kernel AUTO would pick, against the CTA slots of the device (about 3 per SM)
+    const double chains = (double)a->batch * a->d_inner;
+    const bool direct = chains / 32.0 >= 8.0 * hx::sm_count();
+    const int tile = direct ? 128 : (a->io_dtype == HX_BF16 ? 64 : 32);
+    const double ctas = (double)a->batch * ((a->d_inner + tile - 1) / tile);
+    const double slots = 3.0 * hx::sm_count();
+    if (ctas >= 8.0 * slots) return 1;
+    int want = (int)(6.0 * slots / ctas + 0.999);
+    int splits = 1;
+    while (splits < want && splits < 16) splits *= 2;
+    while (splits > 1 && a->seq_len / splits < 128) splits /= 2;  // keep segments long enough to amortise the hand-over
+    return splits;
+}
+
 hx_status hx_selective_scan_workspace_bytes(const hx_scan_args *a, size_t *bytes) {
     HX_REQUIRE(a && bytes, HX_ERR_INVALID_INPUT, "hx_selective_scan_workspace_bytes: NULL argument");
     *bytes = 0;
-    if (a->variant != HX_SCAN_SEQSPLIT) return HX_OK;
+    if (a->variant != HX_SCAN_SEQSPLIT && a->seq_splits <= 1) return HX_OK;
+    if (a->variant == HX_SCAN_SIMPLE) return HX_OK;
     const int TC = a->io_dtype == HX_BF16 ? hx::scan::kChunkBf16 : hx::scan::kChunkF32;
     int n_seg, seg_len;
     hx::scan::seg_plan(a, TC, &n_seg, &seg_len);

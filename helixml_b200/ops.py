@@ -104,7 +104,7 @@ def selective_scan(x, dt, A, Bm, Cm, D=None, z=None, conv_w=None, conv_b=None, d
     a.lanes_per_channel = lanes_per_channel
     a.seq_splits = seq_splits
     a.reserved = tune
-    if variant == L.SCAN_SEQSPLIT:
+    if variant == L.SCAN_SEQSPLIT or seq_splits > 1:
         n = C.c_size_t(0)
         L.check(L.lib().hx_selective_scan_workspace_bytes(C.byref(a), C.byref(n)))
         if workspace is None:

@@ -61,8 +61,10 @@ typedef enum hx_scan_variant {
     HX_SCAN_AUTO = 0,     /* pick the fastest kernel that supports the arguments */
     HX_SCAN_SIMPLE = 1,   /* one thread per (batch, channel); any d_state <= 256; the parity baseline */
     HX_SCAN_TILED = 2,    /* state split over lanes, shared-memory staged tiles; d_state == 16 */
-    HX_SCAN_SEQSPLIT = 3  /* HX_SCAN_TILED with the sequence split over CTAs and carries passed
+    HX_SCAN_SEQSPLIT = 3, /* HX_SCAN_TILED with the sequence split over CTAs and carries passed
                              through `workspace` by a bounded look-back */
+    HX_SCAN_DIRECT = 4    /* one lane per channel (all 16 states in its registers), 1 or 2 channels per lane,
+                             no traffic between lanes; d_state == 16; best when batch * d_inner is large */
 } hx_scan_variant;
 
 HX_API const char *hx_version(void);
@@ -118,20 +120,26 @@ typedef struct hx_scan_args {
     const float *conv_b;      /* [d_inner] fp32 or NULL */
     const float *dt_bias;     /* [d_inner] fp32 or NULL */
     float *h_last;            /* [batch, d_inner, d_state] fp32 final state, or NULL */
-    void *workspace;          /* HX_SCAN_SEQSPLIT only: hx_selective_scan_workspace_bytes() bytes */
+    void *workspace;          /* split sequences only: hx_selective_scan_workspace_bytes() bytes */
     size_t workspace_bytes;
-    int32_t seq_splits;       /* HX_SCAN_SEQSPLIT: number of sequence segments (0 = choose) */
+    int32_t seq_splits;       /* > 1: cut the sequence into this many segments that run as separate CTAs in order,
+                                 each starting from its predecessor's final state (needs `workspace`); this
+                                 evens out the load when batch * d_inner / tile is not a multiple of the SM
+                                 slots.  HX_SCAN_SEQSPLIT: 0 = choose */
     int32_t a_geometric;      /* 1: the caller asserts A[d][n] == (n+1) * A[d][0] (checked once with
                                  hx_scan_check_geometric); then exp(dt*A[d][n]) is evaluated as a power of
                                  exp(dt*A[d][0]), one exp per point instead of d_state */
     int32_t lanes_per_channel;/* HX_SCAN_TILED / SEQSPLIT: lanes that share one channel's 16 states
                                  (1, 2 or 4; 0 = choose from the problem size) */
-    int32_t reserved;
+    int32_t reserved;         /* tuning selector, 0 = default.  HX_SCAN_DIRECT: channels per lane (1 or 2) */
 } hx_scan_args;
 
 HX_API hx_status hx_selective_scan_fwd(const hx_scan_args *args, void *stream);
 /* Bytes of `workspace` HX_SCAN_SEQSPLIT needs for these dimensions (0 for the other variants). */
 HX_API hx_status hx_selective_scan_workspace_bytes(const hx_scan_args *args, size_t *bytes);
+/* Number of sequence segments (a power of two, 1 = do not split) that evens out the load for these dimensions
+ * on the current device; pass it as args->seq_splits together with a workspace. */
+HX_API int32_t hx_selective_scan_suggest_splits(const hx_scan_args *args);
 /* The same operation on HOST activations: x, dt, z, Bm, Cm are read from (preferably pinned) host memory
  * with the strides given in args, staged into `dev_workspace` (caller-owned device memory of
  * hx_selective_scan_host_workspace_bytes() bytes), scanned, and y is copied back to the host pointer

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 
 def run_gpu(inp, dtype, *, variant, lpc=0, geom=None, gate=True, skip=True, conv=True, conv_b=None, dt_bias=None,
-            softplus=True, state=False, seq_splits=0):
+            softplus=True, state=False, seq_splits=0, tune=0):
     from helixml_b200 import ops
     cast = "bf16" if dtype == "bf16" else None
     out = ops.selective_scan(
@@ -21,7 +21,7 @@ def run_gpu(inp, dtype, *, variant, lpc=0, geom=None, gate=True, skip=True, conv
         D=to_dev(inp["D"]) if skip else None, z=to_dev(inp["z"], cast) if gate else None,
         conv_w=to_dev(inp["conv_w"]) if conv else None, conv_b=to_dev(conv_b), dt_bias=to_dev(dt_bias),
         dt_softplus=softplus, variant=variant, a_geometric=geom, lanes_per_channel=lpc, return_state=state,
-        seq_splits=seq_splits)
+        seq_splits=seq_splits, tune=tune)
     from helixml_b200 import _lib
     assert _lib.device_status() == 0, "a bounded device-side wait ran out"
     if state:
@@ -42,7 +42,7 @@ def check(got, ref, dtype):
         assert fp32_tol_err(got, ref) <= FP32_TOL
 
 
-SIMPLE, TILED, SEQSPLIT = 1, 2, 3
+SIMPLE, TILED, SEQSPLIT, DIRECT = 1, 2, 3, 4
 
 
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
@@ -72,6 +72,18 @@ def test_tiled_kernel(dtype, lpc, geom):
     assert fp32_tol_err(hg, hr) <= FP32_TOL if dtype == "f32" else rel_l2(hg, hr) <= BF16_TOL
 
 
+@pytest.mark.parametrize("dtype,cpl", [("f32", 1), ("bf16", 1), ("bf16", 2)])
+@pytest.mark.parametrize("geom", [True, False])
+@pytest.mark.parametrize("B,L,D", [(2, 150, 72), (1, 37, 296), (3, 16, 256)])
+def test_direct_kernel(dtype, cpl, geom, B, L, D):
+    # one lane per channel; L not a chunk multiple, D not a tile multiple (partly and fully empty boxes)
+    inp = synth.scan_inputs(43, B, L, D, 16, 4, bf16=dtype == "bf16")
+    got, hg = run_gpu(inp, dtype, variant=DIRECT, tune=cpl, geom=geom, state=True)
+    ref, hr = run_ref(inp, state=True)
+    check(got, ref, dtype)
+    assert fp32_tol_err(hg, hr) <= FP32_TOL if dtype == "f32" else rel_l2(hg, hr) <= BF16_TOL
+
+
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_tiled_general_decay(dtype):
     # an A that is not geometric: the caller's flag is 0 and every state takes its own exponential
@@ -94,7 +106,7 @@ def test_geometric_detection():
 def test_short_and_ragged_sequences(L):
     inp = synth.scan_inputs(35, 3, L, 16, 16, 4, bf16=False)
     ref = run_ref(inp)
-    for variant, lpc in ((SIMPLE, 0), (TILED, 4), (TILED, 1)):
+    for variant, lpc in ((SIMPLE, 0), (TILED, 4), (TILED, 1), (DIRECT, 0)):
         check(run_gpu(inp, "f32", variant=variant, lpc=lpc), ref, "f32")
 
 
@@ -106,6 +118,7 @@ def test_conv_taps_and_biases(K):
     ref = run_ref(inp, conv_b=cb, dt_bias=db)
     check(run_gpu(inp, "f32", variant=SIMPLE, conv_b=cb, dt_bias=db), ref, "f32")
     check(run_gpu(inp, "f32", variant=TILED, lpc=2, conv_b=cb, dt_bias=db), ref, "f32")
+    check(run_gpu(inp, "f32", variant=DIRECT, conv_b=cb, dt_bias=db), ref, "f32")
 
 
 @pytest.mark.parametrize("gate,skip,conv,softplus", [(False, True, True, True), (True, False, True, True),
@@ -116,7 +129,7 @@ def test_optional_terms(gate, skip, conv, softplus):
     if not softplus:
         inp["dt"] = np.abs(inp["dt"]) * 0.05  # dt is used as given: keep it a sane step size
     ref = run_ref(inp, gate=gate, skip=skip, conv=conv, softplus=softplus)
-    for variant, lpc in ((SIMPLE, 0), (TILED, 4), (TILED, 2), (TILED, 1)):
+    for variant, lpc in ((SIMPLE, 0), (TILED, 4), (TILED, 2), (TILED, 1), (DIRECT, 0)):
         check(run_gpu(inp, "f32", variant=variant, lpc=lpc, gate=gate, skip=skip, conv=conv, softplus=softplus), ref, "f32")
 
 
@@ -143,7 +156,7 @@ def test_strided_views(dtype):
     pad = torch.zeros((Bsz, L, R), dtype=xz.dtype, device="cuda")
     dbc = torch.cat([pad, to_dev(inp["B"], cast), to_dev(inp["C"], cast)], dim=2)
     ref = run_ref(inp)
-    for variant in (SIMPLE, TILED, 0):
+    for variant in (SIMPLE, TILED, DIRECT, 0):
         y = ops.selective_scan(xz[:, :, :D], to_dev(inp["dt"], cast), to_dev(inp["A"]), dbc[:, :, R:R + N],
                                dbc[:, :, R + N:], D=to_dev(inp["D"]), z=xz[:, :, D:], conv_w=to_dev(inp["conv_w"]),
                                variant=variant)
@@ -209,7 +222,7 @@ def test_golden_vectors(golden, name, dtype):
     cb = g["conv_b"] if g["conv_b"].size else None
     db = g["dt_bias"] if g["dt_bias"].size else None
     gate = bool(int(g["gate"]))
-    for variant, lpc in ((SIMPLE, 0), (TILED, 4), (TILED, 2), (TILED, 1)):
+    for variant, lpc in ((SIMPLE, 0), (TILED, 4), (TILED, 2), (TILED, 1), (DIRECT, 0)):
         got, hg = run_gpu(g, dtype, variant=variant, lpc=lpc, gate=gate, conv_b=cb, dt_bias=db, state=True)
         check(got, g["y"], dtype)
         check(hg, g["h_last"], dtype)
@@ -233,6 +246,8 @@ def test_full_size_config2_sampled_chains():
     outs = {}
     for lpc in (1, 2, 4):
         outs[lpc] = ops.selective_scan(x, dt, A, Bm, Cm, D=Dk, z=z, conv_w=cw, variant=TILED, lanes_per_channel=lpc)
+    for cpl in (1, 2):
+        outs[10 + cpl] = ops.selective_scan(x, dt, A, Bm, Cm, D=Dk, z=z, conv_w=cw, variant=DIRECT, tune=cpl)
     base = ops.selective_scan(x, dt, A, Bm, Cm, D=Dk, z=z, conv_w=cw, variant=SIMPLE)
     from helixml_b200 import _lib
     assert _lib.device_status() == 0
