@@ -13,15 +13,16 @@
 //     pair when CPL == 2; with geometric A the 16 decays are powers of one exponential;
 //   * no shuffles, no shared-memory traffic between lanes.
 // A warp therefore covers 32*CPL channels; a CTA has 4 such warps plus the producer warp, which issues the
-// TMA loads (unswizzled 128-byte-wide boxes: every warp-wide access is one contiguous row), widens B/C to
-// fp32 once per CTA and stores finished y tiles with TMA.  Barrier scheme, bounded waits, carry hand-over for
-// split sequences and the status word are those of scan_tiled_kernel.
+// TMA loads (unswizzled 128-byte-wide boxes: every warp-wide access is one contiguous row) and widens B/C to
+// fp32 once per CTA.  y needs no staging: each step a warp writes one contiguous run of 32*CPL channels
+// straight from registers.  Bounded waits, carry hand-over for split sequences and the status word are those
+// of scan_tiled_kernel.
 #pragma once
 
 namespace hx {
 namespace scan {
 
-template <typename T, int CPL_, bool GEOM_, bool STD_>
+template <typename T, int CPL_, bool GEOM_, bool STD_, int STAGES_>
 struct DirectCfg {
     static constexpr int CPL = CPL_;
     static constexpr bool GEOM = GEOM_;
@@ -29,7 +30,7 @@ struct DirectCfg {
     static constexpr bool FAST = sizeof(T) == 2;
     static constexpr int ES = sizeof(T);
     static constexpr int TC = 16;                      // time steps per chunk
-    static constexpr int STAGES = 3;
+    static constexpr int STAGES = STAGES_;
     static constexpr int NWARP = 4;                    // consumer warps
     static constexpr int BOXC = 128 / ES;              // channels per 128-byte box
     static constexpr int WC = 32 * CPL;                // channels per warp
@@ -43,10 +44,9 @@ struct DirectCfg {
     static constexpr int BC_BYTES = (TC * 16 * ES + 127) / 128 * 128;
     static constexpr int BCF_BYTES = TC * 16 * 4;
     static constexpr int STAGE_BYTES = NB * BOX_BYTES + 2 * BC_BYTES + 2 * BCF_BYTES;
-    static constexpr int OUT_BYTES = NB * ROW_BYTES;                // one out buffer (all boxes)
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * OUT_BYTES + 128 + 128;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 128 + 128;
     static_assert(WC * ES <= 128, "a warp's channels must fit one 128-byte box");
-    static_assert(3 * STAGES + 4 <= 16, "barrier area too small");
+    static_assert(3 * STAGES <= 16, "barrier area too small");
 };
 
 template <typename T> __device__ __forceinline__ float2 ld_chan2(const char *p);  // two adjacent channels
@@ -65,8 +65,8 @@ template <typename T, typename Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS)
 scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dt,
                    const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_B,
-                   const __grid_constant__ CUtensorMap tm_C, const __grid_constant__ CUtensorMap tm_y,
-                   const TiledParams p) {
+                   const __grid_constant__ CUtensorMap tm_C, const TiledParams p, T *__restrict__ yg, const int64_t y_bs,
+                   const int64_t y_rs) {
     constexpr int CPL = Cfg::CPL, TC = Cfg::TC, STAGES = Cfg::STAGES, NW = Cfg::NWARP, NB = Cfg::NB, ES = Cfg::ES;
     constexpr bool GEOM = Cfg::GEOM, FAST = Cfg::FAST, STD = Cfg::STD;
     const bool has_conv = STD || p.K > 0, has_z = STD || p.has_z, use_softplus = STD || p.dt_softplus;
@@ -74,14 +74,11 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     extern __shared__ __align__(16) char smem_raw[];
     char *smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);  // 128-byte alignment, shared space kept
     char *stage_base = smem;
-    char *out_base = stage_base + STAGES * Cfg::STAGE_BYTES;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(out_base + 2 * Cfg::OUT_BYTES);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(stage_base + STAGES * Cfg::STAGE_BYTES);
     const uint32_t bar0 = smem_u32(bars);
     auto bar_full = [&](int s) { return bar0 + 8u * s; };
     auto bar_ready = [&](int s) { return bar0 + 8u * (STAGES + s); };
     auto bar_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };
-    auto bar_out_full = [&](int b) { return bar0 + 8u * (3 * STAGES + b); };
-    auto bar_out_empty = [&](int b) { return bar0 + 8u * (3 * STAGES + 2 + b); };
     constexpr int OFF_BC = NB * Cfg::BOX_BYTES, OFF_C = OFF_BC + Cfg::BC_BYTES, OFF_BF = OFF_C + Cfg::BC_BYTES,
                   OFF_CF = OFF_BF + Cfg::BCF_BYTES;
 
@@ -100,10 +97,6 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             mbar_init(bar_ready(s), 1);
             mbar_init(bar_empty(s), NW);
         }
-        for (int k = 0; k < 2; ++k) {
-            mbar_init(bar_out_full(k), NW);
-            mbar_init(bar_out_empty(k), 1);
-        }
         mbar_fence_init();
     }
     __syncthreads();
@@ -115,7 +108,6 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             tma_prefetch_desc(&tm_dt);
             tma_prefetch_desc(&tm_B);
             tma_prefetch_desc(&tm_C);
-            tma_prefetch_desc(&tm_y);
             if (has_z) tma_prefetch_desc(&tm_z);
         }
         const uint32_t stage_tx = live_boxes * ((TC + 3) * 128 + TC * 128 * (has_z ? 2 : 1)) + 2 * TC * 16 * ES;
@@ -135,8 +127,8 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             tma_load_3d(sb + OFF_C, &tm_C, bar_full(s), 0, t0, b);
         };
         int issued = 0;
-        if (lane == 0)
-            for (; issued < STAGES && issued < nchunks; ++issued) issue(issued);
+        for (; issued < STAGES && issued < nchunks; ++issued)
+            if (lane == 0) issue(issued);
         int fail_code = 0;
         for (int i = 0; i <= nchunks; ++i) {
             if (i < nchunks) {
@@ -168,39 +160,26 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_ready(s));
             }
-            if (i >= 1) {
-                const int j = i - 1, ob = j & 1;
+            if (i >= 1 && issued < nchunks) {
+                // refill the stage chunk i-1 used once every consumer warp has released it
+                const int j = i - 1;
                 int fc = 0;
                 if (lane == 0) {
-                    if (!mbar_wait(bar_out_full(ob), (j >> 1) & 1)) {
-                        fc = kWaitOutFull;
+                    if (!mbar_wait(bar_empty(j % STAGES), (j / STAGES) & 1)) {
+                        fc = kWaitEmpty;
                     } else {
-                        for (int bx = 0; bx < live_boxes; ++bx)
-                            tma_store_3d(&tm_y, smem_u32(out_base + ob * Cfg::OUT_BYTES + bx * Cfg::ROW_BYTES),
-                                         d0 + bx * Cfg::BOXC, t_seg0 + j * TC, b);
-                        tma_store_commit();
-                        if (issued < nchunks) {
-                            if (!mbar_wait(bar_empty(j % STAGES), (j / STAGES) & 1)) {
-                                fc = kWaitEmpty;
-                            } else {
-                                issue(issued);
-                                ++issued;
-                            }
-                        }
-                        tma_store_wait_read<1>();
-                        if (j >= 1) mbar_arrive(bar_out_empty((j - 1) & 1));
+                        issue(issued);
                     }
                 }
                 fc = __shfl_sync(0xffffffffu, fc, 0);
                 if (fc) { fail_code = fc; break; }
+                ++issued;
             }
         }
-        if (lane == 0) {
-            tma_store_wait_all<0>();
-            if (fail_code) {
-                atomicOr(&g_wait_status, fail_code);
-                for (int i = 0; i < issued; ++i) mbar_wait(bar_full(i % STAGES), (i / STAGES) & 1);
-            }
+        if (lane == 0 && fail_code) {
+            atomicOr(&g_wait_status, fail_code);
+            // let loads already in flight land before the CTA's shared memory goes away
+            for (int i = 0; i < issued; ++i) mbar_wait(bar_full(i % STAGES), (i / STAGES) & 1);
         }
         return;
     }
@@ -231,6 +210,9 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         }
     }
 
+    // both channels in range and the pair 4-/8-byte aligned in y: one vector store per step
+    const bool pair_ok = CPL == 2 && dch + 1 < p.D && ((y_rs * ES) % (2 * ES) == 0) && ((y_bs * ES) % (2 * ES) == 0) &&
+                         ((reinterpret_cast<uintptr_t>(yg) % (2 * ES)) == 0);
     float2 h[CPL][8];
 #pragma unroll
     for (int e = 0; e < CPL; ++e)
@@ -260,7 +242,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     }
 
     for (int i = 0; i < nchunks; ++i) {
-        const int s = i % STAGES, ob = i & 1;
+        const int s = i % STAGES;
         if (!mbar_wait(bar_ready(s), (i / STAGES) & 1)) {
             if (lane == 0) atomicOr(&g_wait_status, kWaitFull);
             return;
@@ -269,8 +251,8 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const char *sd = sx + Cfg::X_BYTES, *sz = sd + Cfg::ROW_BYTES;
         const float4 *sBf = reinterpret_cast<const float4 *>(stage_base + s * Cfg::STAGE_BYTES + OFF_BF);
         const float4 *sCf = reinterpret_cast<const float4 *>(stage_base + s * Cfg::STAGE_BYTES + OFF_CF);
-        char *so = out_base + ob * Cfg::OUT_BYTES + box * Cfg::ROW_BYTES + lane_byte;
         const int steps = min(TC, t_seg1 - (t_seg0 + i * TC));
+        T *yrow = yg + (int64_t)b * y_bs + (int64_t)(t_seg0 + i * TC) * y_rs + dch;  // this lane's first output
 
         // conv window: the three steps before the chunk come from the halo rows
         float xw[CPL][3];
@@ -282,12 +264,6 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 xw[1][k] = v.y;
             } else {
                 xw[0][k] = ld_chan1<T>(sx + k * 128);
-            }
-        }
-        if (i >= 2) {
-            if (!mbar_wait(bar_out_empty(ob), ((i >> 1) - 1) & 1)) {
-                if (lane == 0) atomicOr(&g_wait_status, kWaitOutEmpty);
-                return;
             }
         }
 
@@ -380,23 +356,26 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 const float2 ys = add2(acc[0], acc[1]);
                 yout[e] = (ys.x + ys.y + ds_[e] * u) * g;
             }
+            // y goes straight from registers to HBM: the warp writes one contiguous run of 32*CPL channels
+            T *yp = yrow + (int64_t)t * y_rs;
             if constexpr (CPL == 2) {
-                if constexpr (ES == 2) {
-                    const __nv_bfloat162 o = __floats2bfloat162_rn(yout[0], yout[1]);
-                    *reinterpret_cast<uint32_t *>(so + t * 128) = *reinterpret_cast<const uint32_t *>(&o);
+                if (pair_ok) {
+                    if constexpr (ES == 2) {
+                        const __nv_bfloat162 o = __floats2bfloat162_rn(yout[0], yout[1]);
+                        *reinterpret_cast<uint32_t *>(yp) = *reinterpret_cast<const uint32_t *>(&o);
+                    } else {
+                        *reinterpret_cast<float2 *>(yp) = make_float2(yout[0], yout[1]);
+                    }
                 } else {
-                    *reinterpret_cast<float2 *>(so + t * 128) = make_float2(yout[0], yout[1]);
+                    if (dch < p.D) st_f32(yp, yout[0]);
+                    if (dch + 1 < p.D) st_f32(yp + 1, yout[1]);
                 }
             } else {
-                st_f32(reinterpret_cast<T *>(so + t * 128), yout[0]);
+                if (dch < p.D) st_f32(yp, yout[0]);
             }
         }
-        fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) {
-            mbar_arrive(bar_empty(s));
-            mbar_arrive(bar_out_full(ob));
-        }
+        if (lane == 0) mbar_arrive(bar_empty(s));
     }
 
     const bool last_seg = seg == p.n_segments - 1;

@@ -881,9 +881,10 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
 }
 
 
-template <typename T, int CPL, bool GEOM, bool STD>
-static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *maps, dim3 grid, cudaStream_t st) {
-    using Cfg = DirectCfg<T, CPL, GEOM, STD>;
+template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2>
+static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *maps, dim3 grid, cudaStream_t st, void *y,
+                                    int64_t y_bs, int64_t y_rs) {
+    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES>;
     auto kern = scan_direct_kernel<T, Cfg>;
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -892,14 +893,15 @@ static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *map
         HX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_set[dev] = true;
     }
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p, static_cast<T *>(y), y_bs,
+                                                      y_rs);
     return check_launch("scan_direct_kernel");
 }
 
 // channels per lane for the direct kernel: 2 when that still leaves about two warps per scheduler
 static int choose_cpl(const hx_scan_args *a) {
     if (a->io_dtype != HX_BF16) return 1;
-    if (a->reserved == 1 || a->reserved == 2) return a->reserved;
+    if (a->reserved % 10 == 1 || a->reserved % 10 == 2) return a->reserved % 10;
     const double chains = (double)a->batch * a->d_inner;
     return chains / 64.0 >= 8.0 * sm_count() ? 2 : 1;
 }
@@ -967,13 +969,20 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
     dim3 grid(tiles, a->batch, n_seg);
     const bool geom = a->a_geometric != 0;
     const bool stdp = a->conv_w != nullptr && a->z != nullptr && a->dt_softplus != 0;
-#define HX_DIRECT_CASE(T, CPL)                                                                     \
-    do {                                                                                           \
-        if (geom && stdp) return launch_direct_inst<T, CPL, true, true>(p, maps, grid, st);        \
-        if (geom) return launch_direct_inst<T, CPL, true, false>(p, maps, grid, st);               \
-        if (stdp) return launch_direct_inst<T, CPL, false, true>(p, maps, grid, st);               \
-        return launch_direct_inst<T, CPL, false, false>(p, maps, grid, st);                        \
+#define HX_DIRECT_CASE(T, CPL)                                                                                         \
+    do {                                                                                                               \
+        void *yv = a->y;                                                                                               \
+        const int64_t ybs = a->y_batch_stride, yrs = a->y_row_stride;                                                  \
+        if (geom && stdp) return launch_direct_inst<T, CPL, true, true>(p, maps, grid, st, yv, ybs, yrs);              \
+        if (geom) return launch_direct_inst<T, CPL, true, false>(p, maps, grid, st, yv, ybs, yrs);                     \
+        if (stdp) return launch_direct_inst<T, CPL, false, true>(p, maps, grid, st, yv, ybs, yrs);                     \
+        return launch_direct_inst<T, CPL, false, false>(p, maps, grid, st, yv, ybs, yrs);                              \
     } while (0)
+    if (bf && geom && stdp && a->reserved / 10 == 1) {  // tuning: three stages instead of two
+        if (cpl == 2)
+            return launch_direct_inst<__nv_bfloat16, 2, true, true, 3>(p, maps, grid, st, a->y, a->y_batch_stride, a->y_row_stride);
+        return launch_direct_inst<__nv_bfloat16, 1, true, true, 3>(p, maps, grid, st, a->y, a->y_batch_stride, a->y_row_stride);
+    }
     if (bf) {
         if (cpl == 2) HX_DIRECT_CASE(__nv_bfloat16, 2);
         HX_DIRECT_CASE(__nv_bfloat16, 1);
