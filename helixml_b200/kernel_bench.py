@@ -1,0 +1,69 @@
+"""Kernel-level timings with CUDA events, for the shapes of the byte-LM benchmark configuration.
+
+    python -m helixml_b200.kernel_bench gemm [in_proj out_proj x_proj dt_proj lm_head]
+    python -m helixml_b200.kernel_bench conv
+    python -m helixml_b200.kernel_bench norm
+
+Each case runs 3 warm-up calls, then 10 timed calls between two events on torch's current stream."""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from . import ops
+
+GEMM_SHAPES = {"in_proj": (65536, 3072, 768), "out_proj": (65536, 768, 1536), "x_proj": (65536, 80, 1536),
+               "dt_proj": (65536, 1536, 48), "lm_head": (65536, 256, 768)}
+
+
+def _time(fn, reps=10):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / reps
+
+
+def gemm(names):
+    for name in names or list(GEMM_SHAPES):
+        M, N, K = GEMM_SHAPES[name]
+        a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+        w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = _time(lambda: ops.gemm(a, w, out=c))
+        ref = a[:256].float() @ w.float().t()
+        err = (c[:256].float() - ref).abs().max().item()
+        print(f"gemm {name} M={M} N={N} K={K}: {ms * 1e3:.1f} us, {2 * M * N * K / ms / 1e9:.0f} TFLOP/s, "
+              f"max |err| on 256 rows {err:.3g}")
+
+
+def conv():
+    B, L, E = 32, 2048, 1536
+    xz = torch.randn(B, L, 2 * E, device="cuda").to(torch.bfloat16)
+    w = torch.rand(E, 4, device="cuda") - 0.5
+    b = torch.zeros(E, device="cuda")
+    u = torch.empty(B, L, E, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: ops.conv1d_silu(xz[:, :, :E], w, b, out=u))
+    byt = B * L * E * 2 * 2
+    print(f"conv_silu [{B},{L},{E}] bf16 (x read as a strided half of [B,L,2E]): {ms * 1e3:.1f} us, {byt / ms / 1e6:.0f} GB/s")
+
+
+def norm():
+    T, M = 65536, 768
+    x = torch.randn(T, M, device="cuda").to(torch.bfloat16)
+    r = torch.randn(T, M, device="cuda")
+    w = torch.ones(M, device="cuda")
+    ms = _time(lambda: ops.rmsnorm(x, w, 1e-5, residual=r, out_dtype=torch.bfloat16))
+    byt = T * M * (2 + 4 + 4 + 2)
+    print(f"rmsnorm + residual [{T},{M}]: {ms * 1e3:.1f} us, {byt / ms / 1e6:.0f} GB/s")
+
+
+if __name__ == "__main__":
+    what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    {"gemm": lambda: gemm(sys.argv[2:]), "conv": conv, "norm": norm}[what]()
