@@ -45,8 +45,8 @@ template <> struct Vec<__nv_bfloat16> {
 // FASTM (bf16 I/O): SiLU through ex2/rcp on the special-function unit; fp32 I/O keeps the accurate form.
 template <typename T, bool VEC, int TB, bool FASTM = (sizeof(T) == 2)>
 __global__ void __launch_bounds__(64)
-conv_silu_kernel(const T *x, int64_t xb, int64_t xr, const float *cw, const float *cb, T *u, int64_t ub, int64_t ur,
-                 int L, int D, int K) {
+conv_silu_kernel(const T *__restrict__ x, int64_t xb, int64_t xr, const float *__restrict__ cw, const float *__restrict__ cb,
+                 T *__restrict__ u, int64_t ub, int64_t ur, int L, int D, int K) {
     constexpr int VN = VEC ? Vec<T>::N : 1;
     const int g = blockIdx.x * blockDim.x + threadIdx.x;
     const int d = g * VN;
@@ -88,7 +88,7 @@ conv_silu_kernel(const T *x, int64_t xb, int64_t xr, const float *cw, const floa
             for (int e = 0; e < VN; ++e) win[j][e] = 0.f;
         }
     }
-#pragma unroll 8
+#pragma unroll 4
     for (int k = 0; k < TB; ++k) {
         const int t = t0 + k;
         if (t >= L) break;
@@ -120,6 +120,56 @@ conv_silu_kernel(const T *x, int64_t xb, int64_t xr, const float *cw, const floa
             v.store(up + t * ur);
         } else {
             st_f32(up + t * ur, out[0]);
+        }
+    }
+}
+
+// Lean bf16 variant: thread = one channel PAIR (a 4-byte load; a warp still reads 128 contiguous bytes per row),
+// so registers stay low and many more rows are in flight per SM than with 16-byte groups.
+template <int TB>
+__global__ void __launch_bounds__(128)
+conv_silu_pair_kernel(const __nv_bfloat16 *__restrict__ x, int64_t xb, int64_t xr, const float *__restrict__ cw,
+                      const float *__restrict__ cb, __nv_bfloat16 *__restrict__ u, int64_t ub, int64_t ur, int L, int D, int K) {
+    const int pr = blockIdx.x * blockDim.x + threadIdx.x;
+    const int d = pr * 2;
+    if (d >= D) return;
+    const int t0 = blockIdx.y * TB;
+    const int b = blockIdx.z;
+    float2 w[4], bias;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int src = j - (4 - K);
+        w[j] = src >= 0 ? make_float2(cw[(int64_t)d * K + src], cw[(int64_t)(d + 1) * K + src]) : make_float2(0.f, 0.f);
+    }
+    bias = cb ? make_float2(cb[d], cb[d + 1]) : make_float2(0.f, 0.f);
+    const __nv_bfloat16 *xp = x + b * xb + d;
+    __nv_bfloat16 *up = u + b * ub + d;
+    auto ldp = [&](int t) {
+        const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(xp + (int64_t)t * xr));
+        return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
+    };
+    float2 w0 = t0 >= 3 ? ldp(t0 - 3) : make_float2(0.f, 0.f);
+    float2 w1 = t0 >= 2 ? ldp(t0 - 2) : make_float2(0.f, 0.f);
+    float2 w2 = t0 >= 1 ? ldp(t0 - 1) : make_float2(0.f, 0.f);
+    const int n = min(TB, L - t0);
+    // rows are fetched eight at a time before any arithmetic, so eight loads per thread are in flight
+    for (int k0 = 0; k0 < n; k0 += 8) {
+        float2 rows[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) rows[e] = (k0 + e < n) ? ldp(t0 + k0 + e) : make_float2(0.f, 0.f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+        const int k = k0 + e;
+        if (k >= n) break;
+        const float2 cur = rows[e];
+        float2 c = bias;
+        c.x = fmaf(w[0].x, w0.x, c.x); c.y = fmaf(w[0].y, w0.y, c.y);
+        c.x = fmaf(w[1].x, w1.x, c.x); c.y = fmaf(w[1].y, w1.y, c.y);
+        c.x = fmaf(w[2].x, w2.x, c.x); c.y = fmaf(w[2].y, w2.y, c.y);
+        c.x = fmaf(w[3].x, cur.x, c.x); c.y = fmaf(w[3].y, cur.y, c.y);
+        const __nv_bfloat162 o = __floats2bfloat162_rn(silu_fast(c.x), silu_fast(c.y));
+        *reinterpret_cast<uint32_t *>(up + (int64_t)(t0 + k) * ur) = *reinterpret_cast<const uint32_t *>(&o);
+        w0 = w1; w1 = w2; w2 = cur;
         }
     }
 }
@@ -261,12 +311,20 @@ hx_status hx_conv1d_silu_fwd(const void *x, int64_t xb, int64_t xr, const float 
     HX_REQUIRE(xr >= d_inner && ur >= d_inner, HX_ERR_SHAPE_MISMATCH, "row stride smaller than d_inner");
     HX_REQUIRE(batch <= 65535, HX_ERR_INVALID_DIMENSION, "batch %d exceeds the grid limit", batch);
     cudaStream_t st = (cudaStream_t)stream;
-    constexpr int TB = 64;
+    constexpr int TB = 32;
     const int es = io_dtype == HX_BF16 ? 2 : 4, vn = 16 / es;
     const bool vec = d_inner % vn == 0 && xr % vn == 0 && ur % vn == 0 && xb % vn == 0 && ub % vn == 0 &&
                      (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(u) & 15) == 0;
     const int groups = vec ? d_inner / vn : d_inner;
     dim3 grid((groups + 63) / 64, (seq_len + TB - 1) / TB, batch), block(64);
+    if (io_dtype == HX_BF16 && d_inner % 2 == 0 && xr % 2 == 0 && ur % 2 == 0 && xb % 2 == 0 && ub % 2 == 0 &&
+        (reinterpret_cast<uintptr_t>(x) & 3) == 0 && (reinterpret_cast<uintptr_t>(u) & 3) == 0) {
+        constexpr int TBP = 64;
+        dim3 g2((d_inner / 2 + 127) / 128, (seq_len + TBP - 1) / TBP, batch);
+        conv_silu_pair_kernel<TBP><<<g2, 128, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), xb, xr, conv_w, conv_b,
+                                                      static_cast<__nv_bfloat16 *>(u), ub, ur, seq_len, d_inner, d_conv);
+        return hx::check_launch("conv_silu_pair_kernel");
+    }
     if (io_dtype == HX_BF16) {
         auto xp = static_cast<const __nv_bfloat16 *>(x);
         auto up = static_cast<__nv_bfloat16 *>(u);
