@@ -3,6 +3,7 @@
     python -m helixml_b200.kernel_bench gemm [in_proj out_proj x_proj dt_proj lm_head]
     python -m helixml_b200.kernel_bench conv
     python -m helixml_b200.kernel_bench norm
+    python -m helixml_b200.kernel_bench s4
 
 Each case runs 3 warm-up calls, then 10 timed calls between two events on torch's current stream."""
 from __future__ import annotations
@@ -64,6 +65,22 @@ def norm():
     print(f"rmsnorm + residual [{T},{M}]: {ms * 1e3:.1f} us, {byt / ms / 1e6:.0f} GB/s")
 
 
+def s4():
+    """Benchmark configuration 1: diagonal S4, f32, batch 8, L 2048, d_model 256, d_state 64."""
+    from . import synth
+    inp = synth.s4_inputs(1, 8, 2048, 256, 64)
+    dev = {k: torch.from_numpy(v).cuda() for k, v in inp.items()}
+    ms = _time(lambda: ops.s4_diag(dev["u"], dev["A"], dev["B"], dev["C"], dev["delta"], dev["D"]))
+    byt = 2 * 8 * 2048 * 256 * 4
+    upd = 8 * 2048 * 256 * 64
+    print(f"s4_diag [8,2048,256] N=64 f32: {ms * 1e3:.1f} us, {byt / ms / 1e6:.0f} GB/s, {upd / ms / 1e6:.1f} G state updates/s")
+    M, L, N = 256, 2048, 64
+    r = {"u": torch.randn(M, L, device="cuda"), "Ar": -torch.rand(N, device="cuda"), "Ai": torch.randn(N, device="cuda"),
+         "B": torch.randn(N, M, device="cuda") * 0.1, "C": torch.randn(M, N, device="cuda") * 0.1, "D": torch.randn(M, device="cuda")}
+    ms = _time(lambda: ops.s4_ref_forward_ssm(r["u"], r["Ar"], r["Ai"], r["B"], r["C"], r["D"]))
+    print(f"s4 reference-literal forward_ssm [256, 2048] N=64 f32: {ms * 1e3:.1f} us")
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": lambda: gemm(sys.argv[2:]), "conv": conv, "norm": norm}[what]()
+    {"gemm": lambda: gemm(sys.argv[2:]), "conv": conv, "norm": norm, "s4": s4}[what]()
