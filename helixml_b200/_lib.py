@@ -43,6 +43,8 @@ class ScanArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("seq_splits", C.c_int32), ("a_geometric", C.c_int32), ("lanes_per_channel", C.c_int32),
         ("reserved", C.c_int32),
+        ("dt_low", C.c_void_p), ("W_dt", C.c_void_p), ("dt_low_batch_stride", C.c_int64), ("dt_low_row_stride", C.c_int64),
+        ("dt_rank", C.c_int32), ("reserved2", C.c_int32),
     ]
 
 

@@ -203,17 +203,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     if (nb >= N) break;  // warp-uniform
                     char *buf = my_stage + (sc & 1) * Cfg::OUT_STAGE_BYTES;
                     ++sc;
+                    // both halves of the block are fetched from tensor memory before anything waits
+                    constexpr int HALVES = CPB / 32;
+                    uint32_t r[HALVES][32];
+#pragma unroll
+                    for (int half = 0; half < HALVES; ++half)
+                        tmem_ld32(tmem_base + acc * BN + cb * CPB + half * 32 + ((uint32_t)(wq * 32) << 16), r[half]);
                     if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer is done
+                    tmem_ld_wait();
                     __syncwarp();
 #pragma unroll
-                    for (int half = 0; half < CPB / 32; ++half) {
-                        uint32_t r[32];
-                        tmem_ld32(tmem_base + acc * BN + cb * CPB + half * 32 + ((uint32_t)(wq * 32) << 16), r);
-                        tmem_ld_wait();
+                    for (int half = 0; half < HALVES; ++half) {
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
-                            float x = __uint_as_float(r[j]);
+                            float x = __uint_as_float(r[half][j]);
                             const int n = nb + half * 32 + j;
                             if (bias) x += (n < N) ? __ldg(bias + n) : 0.f;
                             v[j] = apply_epilogue<EPI>(x);

@@ -116,7 +116,13 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     if ((s = gemm(u, E, a->W_x, E, dbc, W, (int)T, W, E)) != HX_OK) return s;
     mark(3);
     // 4. dt_lin = dt_low W_dt^T                          [T, E]   (bias and softplus happen inside the scan)
-    if ((s = gemm(dbc, W, a->W_dt, R, dtl, E, (int)T, E, R)) != HX_OK) return s;
+    // With bf16 operands and enough chains for the one-lane-per-channel scan, the projection is done inside the
+    // scan kernel (its producer warp, tensor cores) and this GEMM, its 2*T*E-byte write and read disappear.
+    const double chains = (double)a->batch * E;
+    const bool fuse_dt = bf && N == 16 && R >= 8 && R <= 64 && R % 8 == 0 && W % 8 == 0 &&
+                         (a->scan_variant == HX_SCAN_DIRECT ||
+                          (a->scan_variant == HX_SCAN_AUTO && chains / 32.0 >= 8.0 * hx::sm_count()));
+    if (!fuse_dt && (s = gemm(dbc, W, a->W_dt, R, dtl, E, (int)T, E, R)) != HX_OK) return s;
     mark(4);
     // 5. fused scan on strided views
     hx_scan_args sa;
@@ -125,6 +131,11 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     sa.io_dtype = a->io_dtype; sa.dt_softplus = 1; sa.variant = a->scan_variant;
     sa.x = u; sa.x_batch_stride = (int64_t)a->seq_len * E; sa.x_row_stride = E;
     sa.dt = dtl; sa.dt_batch_stride = (int64_t)a->seq_len * E; sa.dt_row_stride = E;
+    if (fuse_dt) {
+        sa.dt = nullptr;
+        sa.dt_low = dbc; sa.dt_low_batch_stride = (int64_t)a->seq_len * W; sa.dt_low_row_stride = W;
+        sa.W_dt = a->W_dt; sa.dt_rank = R;
+    }
     sa.z = static_cast<char *>(xz) + (size_t)E * es; sa.z_batch_stride = (int64_t)a->seq_len * 2 * E; sa.z_row_stride = 2 * E;
     sa.Bm = static_cast<char *>(dbc) + (size_t)R * es; sa.B_batch_stride = (int64_t)a->seq_len * W; sa.B_row_stride = W;
     sa.Cm = static_cast<char *>(dbc) + (size_t)(R + N) * es; sa.C_batch_stride = (int64_t)a->seq_len * W; sa.C_row_stride = W;

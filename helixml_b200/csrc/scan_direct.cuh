@@ -22,8 +22,10 @@
 namespace hx {
 namespace scan {
 
-template <typename T, int CPL_, bool GEOM_, bool STD_, int STAGES_>
+template <typename T, int CPL_, bool GEOM_, bool STD_, int STAGES_, bool FUSEDT_ = false>
 struct DirectCfg {
+    static constexpr bool FUSEDT = FUSEDT_;            // dt = dt_low . W_dt^T computed by the producer warp (bf16 only)
+    static constexpr int RP = 64;                      // columns of the dt_low / W_dt tiles (dt_rank <= 64, zero filled)
     static constexpr int CPL = CPL_;
     static constexpr bool GEOM = GEOM_;
     static constexpr bool STD = STD_;
@@ -40,13 +42,20 @@ struct DirectCfg {
     static constexpr int THREADS = (NWARP + 1) * 32;
     static constexpr int X_BYTES = (TC + 3) * 128;
     static constexpr int ROW_BYTES = TC * 128;
-    static constexpr int BOX_BYTES = X_BYTES + 2 * ROW_BYTES;       // x, dt, z of one box
+    static constexpr int DTROW = FUSEDT ? BOXC * 4 + 32 : 128;            // bytes per dt row (fp32 + pad when produced here:
+                                                                          // the pad spreads the producer's stores over banks)
+    static constexpr int DTT_BYTES = TC * DTROW;
+    static constexpr int BOX_BYTES = X_BYTES + ROW_BYTES + DTT_BYTES;     // x, z, dt of one box
     static constexpr int BC_BYTES = (TC * 16 * ES + 127) / 128 * 128;
     static constexpr int BCF_BYTES = TC * 16 * 4;
-    static constexpr int STAGE_BYTES = NB * BOX_BYTES + 2 * BC_BYTES + 2 * BCF_BYTES;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 128 + 128;
+    static constexpr int DTLOW_BYTES = FUSEDT ? TC * RP * 2 : 0;          // [TC][RP] bf16
+    static constexpr int WDT_BYTES = FUSEDT ? DT * RP * 2 : 0;            // [DT][RP] bf16, once per CTA
+    static constexpr int STAGE_RAW = NB * BOX_BYTES + 2 * BC_BYTES + 2 * BCF_BYTES + DTLOW_BYTES;
+    static constexpr int STAGE_BYTES = FUSEDT ? (STAGE_RAW + 1023) / 1024 * 1024 : STAGE_RAW;  // swizzled tile first
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + WDT_BYTES + 128 + (FUSEDT ? 1024 : 128);
     static_assert(WC * ES <= 128, "a warp's channels must fit one 128-byte box");
-    static_assert(3 * STAGES <= 16, "barrier area too small");
+    static_assert(3 * STAGES + 1 <= 16, "barrier area too small");
+    static_assert(!FUSEDT || sizeof(T) == 2, "the fused dt projection takes bf16 operands");
 };
 
 template <typename T> __device__ __forceinline__ float2 ld_chan2(const char *p);  // two adjacent channels
@@ -65,22 +74,31 @@ template <typename T, typename Cfg>
 __global__ void __launch_bounds__(Cfg::THREADS)
 scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dt,
                    const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_B,
-                   const __grid_constant__ CUtensorMap tm_C, const TiledParams p, T *__restrict__ yg, const int64_t y_bs,
+                   const __grid_constant__ CUtensorMap tm_C, const __grid_constant__ CUtensorMap tm_dtlow,
+                   const __grid_constant__ CUtensorMap tm_wdt, const TiledParams p, T *__restrict__ yg, const int64_t y_bs,
                    const int64_t y_rs) {
     constexpr int CPL = Cfg::CPL, TC = Cfg::TC, STAGES = Cfg::STAGES, NW = Cfg::NWARP, NB = Cfg::NB, ES = Cfg::ES;
-    constexpr bool GEOM = Cfg::GEOM, FAST = Cfg::FAST, STD = Cfg::STD;
+    constexpr bool GEOM = Cfg::GEOM, FAST = Cfg::FAST, STD = Cfg::STD, FUSEDT = Cfg::FUSEDT;
     const bool has_conv = STD || p.K > 0, has_z = STD || p.has_z, use_softplus = STD || p.dt_softplus;
 
     extern __shared__ __align__(16) char smem_raw[];
-    char *smem = smem_raw + ((128u - (smem_u32(smem_raw) & 127u)) & 127u);  // 128-byte alignment, shared space kept
-    char *stage_base = smem;
+    // aligned by pointer arithmetic (keeps the shared address space): 1024 bytes when the swizzled W_dt tile is
+    // present, 128 otherwise
+    constexpr uint32_t ALIGN = FUSEDT ? 1024u : 128u;
+    char *smem = smem_raw + ((ALIGN - (smem_u32(smem_raw) & (ALIGN - 1))) & (ALIGN - 1));
+    char *wdt_tile = smem;  // [DT][64] bf16, 128-byte swizzle (row r: 16-byte chunk c sits at c ^ (r & 7))
+    char *stage_base = smem + Cfg::WDT_BYTES;
     uint64_t *bars = reinterpret_cast<uint64_t *>(stage_base + STAGES * Cfg::STAGE_BYTES);
     const uint32_t bar0 = smem_u32(bars);
     auto bar_full = [&](int s) { return bar0 + 8u * s; };
     auto bar_ready = [&](int s) { return bar0 + 8u * (STAGES + s); };
     auto bar_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };
-    constexpr int OFF_BC = NB * Cfg::BOX_BYTES, OFF_C = OFF_BC + Cfg::BC_BYTES, OFF_BF = OFF_C + Cfg::BC_BYTES,
+    const uint32_t bar_w = bar0 + 8u * (3 * STAGES);  // W_dt tile landed
+    // stage layout: [dt_low tile (fused dt only, 1024-aligned for its swizzle)] [boxes] [B, C raw] [B, C fp32]
+    constexpr int OFF_DTLOW = 0, OFF_BOX0 = Cfg::DTLOW_BYTES;
+    constexpr int OFF_BC = OFF_BOX0 + NB * Cfg::BOX_BYTES, OFF_C = OFF_BC + Cfg::BC_BYTES, OFF_BF = OFF_C + Cfg::BC_BYTES,
                   OFF_CF = OFF_BF + Cfg::BCF_BYTES;
+    constexpr int OFF_Z = Cfg::X_BYTES, OFF_DTT = Cfg::X_BYTES + Cfg::ROW_BYTES;  // inside a box: x, z, dt
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, b = blockIdx.y, seg = blockIdx.z;
@@ -97,6 +115,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             mbar_init(bar_ready(s), 1);
             mbar_init(bar_empty(s), NW);
         }
+        mbar_init(bar_w, 1);
         mbar_fence_init();
     }
     __syncthreads();
@@ -110,19 +129,29 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             tma_prefetch_desc(&tm_C);
             if (has_z) tma_prefetch_desc(&tm_z);
         }
-        const uint32_t stage_tx = live_boxes * ((TC + 3) * 128 + TC * 128 * (has_z ? 2 : 1)) + 2 * TC * 16 * ES;
+        const uint32_t stage_tx = live_boxes * ((TC + 3) * 128 + TC * 128 * ((has_z ? 1 : 0) + (FUSEDT ? 0 : 1))) +
+                                  2 * TC * 16 * ES + Cfg::DTLOW_BYTES;
+        if constexpr (FUSEDT) {
+            if (lane == 0) {
+                tma_prefetch_desc(&tm_dtlow);
+                tma_prefetch_desc(&tm_wdt);
+                mbar_expect_tx(bar_w, Cfg::WDT_BYTES);
+                tma_load_2d(smem_u32(wdt_tile), &tm_wdt, bar_w, 0, d0);  // rows past d_inner arrive as zeros
+            }
+        }
         auto issue = [&](int i) {
             const int s = i % STAGES;
             const int t0 = t_seg0 + i * TC;
             const uint32_t sb = smem_u32(stage_base + s * Cfg::STAGE_BYTES);
             mbar_expect_tx(bar_full(s), stage_tx);
             for (int bx = 0; bx < live_boxes; ++bx) {
-                const uint32_t bb = sb + bx * Cfg::BOX_BYTES;
+                const uint32_t bb = sb + OFF_BOX0 + bx * Cfg::BOX_BYTES;
                 const int dc = d0 + bx * Cfg::BOXC;
                 tma_load_3d(bb, &tm_x, bar_full(s), dc, t0 - 3, b);
-                tma_load_3d(bb + Cfg::X_BYTES, &tm_dt, bar_full(s), dc, t0, b);
-                if (has_z) tma_load_3d(bb + Cfg::X_BYTES + Cfg::ROW_BYTES, &tm_z, bar_full(s), dc, t0, b);
+                if (has_z) tma_load_3d(bb + OFF_Z, &tm_z, bar_full(s), dc, t0, b);
+                if constexpr (!FUSEDT) tma_load_3d(bb + OFF_DTT, &tm_dt, bar_full(s), dc, t0, b);
             }
+            if constexpr (FUSEDT) tma_load_3d(sb + OFF_DTLOW, &tm_dtlow, bar_full(s), 0, t0, b);
             tma_load_3d(sb + OFF_BC, &tm_B, bar_full(s), 0, t0, b);
             tma_load_3d(sb + OFF_C, &tm_C, bar_full(s), 0, t0, b);
         };
@@ -130,12 +159,56 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         for (; issued < STAGES && issued < nchunks; ++issued)
             if (lane == 0) issue(issued);
         int fail_code = 0;
-        for (int i = 0; i <= nchunks; ++i) {
+        if constexpr (FUSEDT) {
+            const bool okw = mbar_wait(bar_w, 0);
+            if (!__all_sync(0xffffffffu, okw)) fail_code = kWaitFull;
+        }
+        for (int i = 0; i <= nchunks && !fail_code; ++i) {
             if (i < nchunks) {
                 const int s = i % STAGES;
                 const bool ok = mbar_wait(bar_full(s), (i / STAGES) & 1);
                 if (!__all_sync(0xffffffffu, ok)) { fail_code = kWaitFull; break; }
                 char *st = stage_base + s * Cfg::STAGE_BYTES;
+                if constexpr (FUSEDT) {
+                    // dt[16 steps][DT channels] = dt_low[16][RP] . W_dt[DT][RP]^T on the tensor cores
+                    // (mma.sync m16n8k16, bf16 in, fp32 out), written as the fp32 dt tile of every box
+                    constexpr int RPB = Cfg::RP * 2;  // row bytes of both operand tiles
+                    const int g = lane >> 2, tid = lane & 3;
+                    const int ksteps = (p.dt_rank + 15) >> 4;
+                    const char *dl = st + OFF_DTLOW + 2 * tid * 2;  // swizzled like the W_dt tile
+                    uint32_t af[4][4];
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) {
+                        const int c0 = ((2 * kk) ^ g) << 4, c1 = ((2 * kk + 1) ^ g) << 4;  // (g + 8) & 7 == g
+                        af[kk][0] = *reinterpret_cast<const uint32_t *>(dl + g * RPB + c0);
+                        af[kk][1] = *reinterpret_cast<const uint32_t *>(dl + (g + 8) * RPB + c0);
+                        af[kk][2] = *reinterpret_cast<const uint32_t *>(dl + g * RPB + c1);
+                        af[kk][3] = *reinterpret_cast<const uint32_t *>(dl + (g + 8) * RPB + c1);
+                    }
+#pragma unroll 2
+                    for (int nt = 0; nt < Cfg::DT / 8; ++nt) {
+                        float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;
+                        // row nt*8+g of the swizzled tile: (row & 7) == g, so the eight rows a load touches
+                        // land in eight different 16-byte chunks (no bank conflict)
+                        const char *wr = wdt_tile + (nt * 8 + g) * RPB + 2 * tid * 2;
+#pragma unroll
+                        for (int kk = 0; kk < 4; ++kk) {
+                            if (kk < ksteps) {
+                                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(wr + (((2 * kk) ^ g) << 4));
+                                const uint32_t b1 = *reinterpret_cast<const uint32_t *>(wr + (((2 * kk + 1) ^ g) << 4));
+                                asm volatile(
+                                    "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+                                    "{%8, %9}, {%0, %1, %2, %3};"
+                                    : "+f"(c0), "+f"(c1), "+f"(c2), "+f"(c3)
+                                    : "r"(af[kk][0]), "r"(af[kk][1]), "r"(af[kk][2]), "r"(af[kk][3]), "r"(b0), "r"(b1));
+                            }
+                        }
+                        const int bx = (nt * 8) / Cfg::BOXC, col = (nt * 8) % Cfg::BOXC + 2 * tid;
+                        char *dtt = st + OFF_BOX0 + bx * Cfg::BOX_BYTES + OFF_DTT + col * 4;
+                        *reinterpret_cast<float2 *>(dtt + g * Cfg::DTROW) = make_float2(c0, c1);
+                        *reinterpret_cast<float2 *>(dtt + (g + 8) * Cfg::DTROW) = make_float2(c2, c3);
+                    }
+                }
                 // widen B and C of this chunk to fp32: TC*16 values per array, 8 per lane per round
                 constexpr int ROUNDS = TC * 16 * 2 / (32 * 8);
 #pragma unroll
@@ -247,8 +320,12 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             if (lane == 0) atomicOr(&g_wait_status, kWaitFull);
             return;
         }
-        const char *sx = stage_base + s * Cfg::STAGE_BYTES + box * Cfg::BOX_BYTES + lane_byte;  // row 0 = 3 steps back
-        const char *sd = sx + Cfg::X_BYTES, *sz = sd + Cfg::ROW_BYTES;
+        const char *sbox = stage_base + s * Cfg::STAGE_BYTES + OFF_BOX0 + box * Cfg::BOX_BYTES;
+        const char *sx = sbox + lane_byte;  // row 0 = 3 steps back
+        const char *sz = sbox + OFF_Z + lane_byte;
+        // dt: the caller's tile (io dtype) or the fp32 tile the producer computed
+        const char *sd = sbox + OFF_DTT + (FUSEDT ? (lane_byte / ES) * 4 : lane_byte);
+        constexpr int DROW = Cfg::DTROW;  // bytes per dt row
         const float4 *sBf = reinterpret_cast<const float4 *>(stage_base + s * Cfg::STAGE_BYTES + OFF_BF);
         const float4 *sCf = reinterpret_cast<const float4 *>(stage_base + s * Cfg::STAGE_BYTES + OFF_CF);
         const int steps = min(TC, t_seg1 - (t_seg0 + i * TC));
@@ -271,7 +348,10 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         for (int t = 0; t < steps; ++t) {
             float xc[CPL], dr[CPL], zr[CPL];
             if constexpr (CPL == 2) {
-                const float2 vx = ld_chan2<T>(sx + (t + 3) * 128), vd = ld_chan2<T>(sd + t * 128);
+                const float2 vx = ld_chan2<T>(sx + (t + 3) * 128);
+                float2 vd;
+                if constexpr (FUSEDT) vd = *reinterpret_cast<const float2 *>(sd + t * DROW);
+                else vd = ld_chan2<T>(sd + t * DROW);
                 xc[0] = vx.x; xc[1] = vx.y; dr[0] = vd.x; dr[1] = vd.y;
                 if (has_z) {
                     const float2 vz = ld_chan2<T>(sz + t * 128);
@@ -279,7 +359,8 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 }
             } else {
                 xc[0] = ld_chan1<T>(sx + (t + 3) * 128);
-                dr[0] = ld_chan1<T>(sd + t * 128);
+                if constexpr (FUSEDT) dr[0] = *reinterpret_cast<const float *>(sd + t * DROW);
+                else dr[0] = ld_chan1<T>(sd + t * DROW);
                 if (has_z) zr[0] = ld_chan1<T>(sz + t * 128);
             }
             // B and C of this step, shared by the lane's channels

@@ -124,6 +124,7 @@ struct TiledParams {
     float *carry;     // [n_segments-1, B, D, 16] states handed from segment s to s+1
     int *flags;       // [n_segments-1, B, tiles, 8] one per consumer warp, set to `epoch` once its carry is written
     int epoch;
+    int dt_rank;      // > 0: dt is produced in the kernel from dt_low and W_dt (direct kernel only)
 };
 
 template <typename T, int LPC_, bool GEOM_, int TC_, int STAGES_, bool STD_>
@@ -683,13 +684,20 @@ static hx_status validate(const hx_scan_args *a) {
     hx_status s = validate_dims(a);
     if (s != HX_OK) return s;
     if (a->batch == 0 || a->seq_len == 0 || a->d_inner == 0) return HX_OK;
-    HX_REQUIRE(a->x && a->dt && a->Bm && a->Cm && a->y && a->A, HX_ERR_INVALID_INPUT,
-               "x, dt, Bm, Cm, y and A must not be NULL");
+    HX_REQUIRE(a->x && (a->dt || a->W_dt) && a->Bm && a->Cm && a->y && a->A, HX_ERR_INVALID_INPUT,
+               "x, dt (or W_dt), Bm, Cm, y and A must not be NULL");
+    if (a->W_dt) {
+        HX_REQUIRE(a->dt_low != nullptr, HX_ERR_INVALID_INPUT, "W_dt given without dt_low");
+        HX_REQUIRE(a->dt_rank >= 8 && a->dt_rank <= 64 && a->dt_rank % 8 == 0, HX_ERR_INVALID_DIMENSION,
+                   "fused dt projection needs dt_rank in [8, 64] and a multiple of 8 (got %d)", a->dt_rank);
+        HX_REQUIRE(a->io_dtype == HX_BF16, HX_ERR_UNSUPPORTED_OPERATION, "the fused dt projection takes bf16 operands");
+        HX_REQUIRE(a->dt_low_row_stride >= a->dt_rank, HX_ERR_SHAPE_MISMATCH, "dt_low row stride smaller than dt_rank");
+    }
     if (a->conv_w)
         HX_REQUIRE(a->d_conv >= 1 && a->d_conv <= 4, HX_ERR_INVALID_DIMENSION, "d_conv %d outside [1, 4]", a->d_conv);
     HX_REQUIRE(a->conv_w || !a->conv_b, HX_ERR_INVALID_INPUT, "conv_b given without conv_w");
     const int64_t D = a->d_inner, N = a->d_state;
-    HX_REQUIRE(a->x_row_stride >= D && a->dt_row_stride >= D && a->y_row_stride >= D && (!a->z || a->z_row_stride >= D),
+    HX_REQUIRE(a->x_row_stride >= D && (a->W_dt || a->dt_row_stride >= D) && a->y_row_stride >= D && (!a->z || a->z_row_stride >= D),
                HX_ERR_SHAPE_MISMATCH, "a row stride is smaller than d_inner %d", a->d_inner);
     HX_REQUIRE(a->B_row_stride >= N && a->C_row_stride >= N, HX_ERR_SHAPE_MISMATCH,
                "B/C row stride is smaller than d_state %d", a->d_state);
@@ -697,6 +705,7 @@ static hx_status validate(const hx_scan_args *a) {
 }
 
 static hx_status launch_simple(const hx_scan_args *a, cudaStream_t st) {
+    HX_REQUIRE(a->W_dt == nullptr, HX_ERR_UNSUPPORTED_OPERATION, "the simple scan kernel has no fused dt projection");
     SimpleParams p;
     p.B = a->batch; p.L = a->seq_len; p.D = a->d_inner; p.N = a->d_state; p.K = a->conv_w ? a->d_conv : 0;
     p.dt_softplus = a->dt_softplus;
@@ -773,6 +782,7 @@ static int choose_lpc(const hx_scan_args *a) {
 }
 
 static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st) {
+    HX_REQUIRE(a->W_dt == nullptr, HX_ERR_UNSUPPORTED_OPERATION, "the lane-split scan kernel has no fused dt projection");
     HX_REQUIRE(a->d_state == 16, HX_ERR_UNSUPPORTED_OPERATION, "the tiled scan needs d_state == 16 (got %d)", a->d_state);
     const bool bf = a->io_dtype == HX_BF16;
     // `reserved` picks another (chunk, stages) pair for the bf16 / geometric / standard path (tuning knob)
@@ -791,7 +801,7 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
     p.n_segments = n_seg; p.seg_len = seg_len;
     p.A = a->A; p.Dskip = a->Dskip; p.conv_w = a->conv_w; p.conv_b = a->conv_b; p.dt_bias = a->dt_bias;
     p.h_last = a->h_last;
-    p.carry = nullptr; p.flags = nullptr; p.epoch = 1;
+    p.carry = nullptr; p.flags = nullptr; p.epoch = 1; p.dt_rank = 0;
     if (n_seg > 1) {
         const size_t need = workspace_bytes(a, n_seg);
         HX_REQUIRE(a->workspace && a->workspace_bytes >= need, HX_ERR_INVALID_INPUT,
@@ -881,10 +891,10 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
 }
 
 
-template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2>
+template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2, bool FUSEDT = false>
 static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *maps, dim3 grid, cudaStream_t st, void *y,
                                     int64_t y_bs, int64_t y_rs) {
-    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES>;
+    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES, FUSEDT>;
     auto kern = scan_direct_kernel<T, Cfg>;
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -893,8 +903,8 @@ static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *map
         HX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_set[dev] = true;
     }
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], p, static_cast<T *>(y), y_bs,
-                                                      y_rs);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[6], maps[7], p,
+                                                      static_cast<T *>(y), y_bs, y_rs);
     return check_launch("scan_direct_kernel");
 }
 
@@ -925,6 +935,7 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
     p.A = a->A; p.Dskip = a->Dskip; p.conv_w = a->conv_w; p.conv_b = a->conv_b; p.dt_bias = a->dt_bias;
     p.h_last = a->h_last;
     p.carry = nullptr; p.flags = nullptr; p.epoch = 1;
+    p.dt_rank = a->W_dt ? a->dt_rank : 0;
     if (n_seg > 1) {
         const size_t need = workspace_bytes(a, n_seg);
         HX_REQUIRE(a->workspace && a->workspace_bytes >= need, HX_ERR_INVALID_INPUT,
@@ -936,7 +947,7 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
         HX_CUDA(cudaMemsetAsync(p.flags, 0, (size_t)(n_seg - 1) * a->batch * tiles_of(a) * 8 * sizeof(int), st));
     }
 
-    CUtensorMap maps[6];
+    CUtensorMap maps[8];
     const uint64_t dims_d[3] = {(uint64_t)a->d_inner, (uint64_t)a->seq_len, (uint64_t)a->batch};
     const uint64_t dims_n[3] = {16, (uint64_t)a->seq_len, (uint64_t)a->batch};
     auto strides = [&](int64_t row, int64_t batch, uint64_t *out) {
@@ -949,8 +960,25 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
     hx_status s;
     strides(a->x_row_stride, a->x_batch_stride, sb);
     if ((s = encode_tensor_map(&maps[0], a->io_dtype, 3, a->x, dims_d, sb, box_x, false)) != HX_OK) return s;
-    strides(a->dt_row_stride, a->dt_batch_stride, sb);
-    if ((s = encode_tensor_map(&maps[1], a->io_dtype, 3, a->dt, dims_d, sb, box_r, false)) != HX_OK) return s;
+    const bool fused_dt = a->W_dt != nullptr;
+    if (fused_dt) {
+        // dt_low [B, L, R] -> boxes of [16 steps x 64 columns] (columns past R are zero-filled);
+        // W_dt [D, R] -> one [DT channels x 64] tile per CTA
+        const uint64_t dims_l[3] = {(uint64_t)a->dt_rank, (uint64_t)a->seq_len, (uint64_t)a->batch};
+        const uint32_t box_l[3] = {64, (uint32_t)TC, 1};
+        strides(a->dt_low_row_stride, a->dt_low_batch_stride, sb);
+        if ((s = encode_tensor_map(&maps[6], HX_BF16, 3, a->dt_low, dims_l, sb, box_l, true)) != HX_OK) return s;
+        const uint64_t dims_w[2] = {(uint64_t)a->dt_rank, (uint64_t)a->d_inner};
+        const uint64_t str_w[1] = {(uint64_t)a->dt_rank * 2};
+        const uint32_t box_w[2] = {64, (uint32_t)DT};
+        if ((s = encode_tensor_map(&maps[7], HX_BF16, 2, a->W_dt, dims_w, str_w, box_w, true)) != HX_OK) return s;
+        maps[1] = maps[0];
+    } else {
+        strides(a->dt_row_stride, a->dt_batch_stride, sb);
+        if ((s = encode_tensor_map(&maps[1], a->io_dtype, 3, a->dt, dims_d, sb, box_r, false)) != HX_OK) return s;
+        maps[6] = maps[0];
+        maps[7] = maps[0];
+    }
     if (a->z) {
         strides(a->z_row_stride, a->z_batch_stride, sb);
         if ((s = encode_tensor_map(&maps[2], a->io_dtype, 3, a->z, dims_d, sb, box_r, false)) != HX_OK) return s;
@@ -978,6 +1006,19 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
         if (stdp) return launch_direct_inst<T, CPL, false, true>(p, maps, grid, st, yv, ybs, yrs);                     \
         return launch_direct_inst<T, CPL, false, false>(p, maps, grid, st, yv, ybs, yrs);                              \
     } while (0)
+    if (fused_dt) {
+        HX_REQUIRE(stdp || (a->z != nullptr && a->dt_softplus != 0), HX_ERR_UNSUPPORTED_OPERATION,
+                   "the fused dt projection is built for the block's configuration (gate and softplus present)");
+        void *yv = a->y;
+        const int64_t ybs = a->y_batch_stride, yrs = a->y_row_stride;
+        // the block hands u (already convolved): conv flags are read at run time, so STD is false here
+        if (cpl == 2) {
+            if (geom) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
+            return launch_direct_inst<__nv_bfloat16, 2, false, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
+        }
+        if (geom) return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
+        return launch_direct_inst<__nv_bfloat16, 1, false, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
+    }
     if (bf && geom && stdp && a->reserved / 10 == 1) {  // tuning: three stages instead of two
         if (cpl == 2)
             return launch_direct_inst<__nv_bfloat16, 2, true, true, 3>(p, maps, grid, st, a->y, a->y_batch_stride, a->y_row_stride);
@@ -1022,7 +1063,7 @@ hx_status hx_selective_scan_fwd(const hx_scan_args *a, void *stream) {
             if (a->d_state == 16) {
                 // enough independent chains for one lane per channel -> direct kernel, else split the states
                 const double chains = (double)a->batch * a->d_inner;
-                const bool direct = chains / 32.0 >= 8.0 * hx::sm_count();
+                const bool direct = a->W_dt != nullptr || chains / 32.0 >= 8.0 * hx::sm_count();
                 s = direct ? hx::scan::launch_direct(a, split, st) : hx::scan::launch_tiled(a, split, st);
                 // an operand that does not meet the TMA alignment rules goes to the simple kernel
                 if (s != HX_ERR_UNSUPPORTED_OPERATION) return s;

@@ -60,7 +60,7 @@ def scan_workspace_bytes(batch, seq_len, d_inner, dtype, seq_splits=0) -> int:
 
 def selective_scan(x, dt, A, Bm, Cm, D=None, z=None, conv_w=None, conv_b=None, dt_bias=None, dt_softplus=True,
                    variant=L.SCAN_AUTO, a_geometric=None, lanes_per_channel=0, return_state=False, out=None,
-                   workspace=None, seq_splits=0, tune=0):
+                   workspace=None, seq_splits=0, tune=0, dt_low=None, W_dt=None):
     """Fused selective scan (hx_selective_scan_fwd).  x, dt, z, y: [B, L, D]; Bm, Cm: [B, L, N]."""
     Bsz, Lq, Dm = x.shape
     N = A.shape[1]
@@ -72,6 +72,11 @@ def selective_scan(x, dt, A, Bm, Cm, D=None, z=None, conv_w=None, conv_b=None, d
     a.io_dtype = _dt(x)
     a.dt_softplus = 1 if dt_softplus else 0
     a.variant = variant
+    if W_dt is not None:
+        # fused dt projection: dt = dt_low @ W_dt.T inside the kernel
+        a.dt_low, a.W_dt = dt_low.data_ptr(), W_dt.contiguous().data_ptr()
+        a.dt_low_batch_stride, a.dt_low_row_stride = _view3(dt_low)
+        a.dt_rank = W_dt.shape[1]
     for name, t in (("x", x), ("dt", dt), ("z", z), ("y", y)):
         if t is None:
             continue

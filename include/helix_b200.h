@@ -132,6 +132,17 @@ typedef struct hx_scan_args {
     int32_t lanes_per_channel;/* HX_SCAN_TILED / SEQSPLIT: lanes that share one channel's 16 states
                                  (1, 2 or 4; 0 = choose from the problem size) */
     int32_t reserved;         /* tuning selector, 0 = default.  HX_SCAN_DIRECT: channels per lane (1 or 2) */
+    /* Optional fused dt projection (bf16 I/O, HX_SCAN_DIRECT or HX_SCAN_AUTO when it picks that kernel):
+     * when W_dt != NULL the raw step sizes are computed inside the kernel as
+     *   dt_raw[b,t,d] = sum_r dt_low[b,t,r] * W_dt[d,r]      (fp32 accumulation on the tensor cores)
+     * and `dt` is ignored.  dt_low is [batch, seq_len, dt_rank] with its own strides (a column slice of the
+     * x_proj output), W_dt is [d_inner, dt_rank] row-major like nn::Linear; dt_rank <= 64 and a multiple of 8.
+     * Other kernels report HX_ERR_UNSUPPORTED_OPERATION for it. */
+    const void *dt_low;
+    const void *W_dt;
+    int64_t dt_low_batch_stride, dt_low_row_stride;
+    int32_t dt_rank;
+    int32_t reserved2;
 } hx_scan_args;
 
 HX_API hx_status hx_selective_scan_fwd(const hx_scan_args *args, void *stream);

@@ -177,6 +177,23 @@ def test_mamba_block_bf16(B, L, M):
     assert rel_l2(to_np(got), ref) <= BF16_TOL
 
 
+def test_mamba_block_bf16_direct_scan_with_fused_dt():
+    """The block with the one-lane-per-channel scan forced: the dt projection then runs inside the scan kernel."""
+    from helixml_b200 import _lib, ops
+    B, L, M = 2, 200, 768
+    w = synth.mamba_block_weights(5, M, 16, 4, 2, init="0.02")
+    big = ("W_in", "W_x", "W_dt", "W_out")
+    wq = {k: (synth.round_bf16(v) if k in big else v) for k, v in w.items()}
+    x = synth.round_bf16(synth.normal(5, "x", (B, L, M)))
+    dev = {k: to_dev(v, "bf16" if k in big else None) for k, v in wq.items()}
+    ref = cbind.mamba_block(x, wq, 16, 4)
+    outs = [to_np(ops.mamba_block(to_dev(x, "bf16"), dev, 16, 4, scan_variant=v)) for v in (_lib.SCAN_DIRECT, _lib.SCAN_TILED)]
+    _status_ok()
+    for got in outs:
+        assert rel_l2(got, ref) <= BF16_TOL
+    assert rel_l2(outs[0], outs[1]) <= 1e-2  # fused and unfused dt projection agree
+
+
 def test_exported_reference_block(golden):
     """The exported nn::MambaBlock::forward (crates/nn/src/lib.rs:888-906) is out_proj(silu(gate(x))):
     two Linear calls and a SiLU, reproduced with the GEMM's bias and SiLU epilogue."""

@@ -84,6 +84,40 @@ def test_direct_kernel(dtype, cpl, geom, B, L, D):
     assert fp32_tol_err(hg, hr) <= FP32_TOL if dtype == "f32" else rel_l2(hg, hr) <= BF16_TOL
 
 
+@pytest.mark.parametrize("cpl", [1, 2])
+@pytest.mark.parametrize("geom,conv", [(True, False), (True, True), (False, False)])
+@pytest.mark.parametrize("B,L,D,R", [(2, 150, 200, 48), (1, 33, 512, 16), (3, 64, 136, 64)])
+def test_direct_fused_dt_projection(cpl, geom, conv, B, L, D, R):
+    """dt = dt_low . W_dt^T computed inside the scan kernel (producer warp, tensor cores), with dt_low a column
+    slice of a wider row as in the Mamba block.  The oracle gets the same product computed in fp32."""
+    import torch
+    from helixml_b200 import _lib, ops
+    inp = synth.scan_inputs(44, B, L, D, 16, 4, bf16=True)
+    if not geom:
+        inp["A"] = -np.exp(synth.uniform(44, "Alog", (D, 16), -1.0, 2.0)).astype(np.float32)
+    dt_low = synth.round_bf16(synth.normal(44, "dt_low", (B, L, R)))
+    W_dt = synth.round_bf16(synth.normal(44, "W_dt", (D, R), 0.0, 0.4 / np.sqrt(R)))
+    bias = synth.uniform(44, "bias", (D,), -3.0, -1.5)
+    dt = (dt_low.reshape(-1, R).astype(np.float64) @ W_dt.astype(np.float64).T).reshape(B, L, D).astype(np.float32)
+    ref = cbind.selective_scan(inp["x"], dt, inp["A"], inp["B"], inp["C"], D=inp["D"], z=inp["z"],
+                               conv_w=inp["conv_w"] if conv else None, dt_bias=bias)
+    wide = torch.zeros((B, L, R + 32), dtype=torch.bfloat16, device="cuda")
+    wide[:, :, :R] = to_dev(dt_low, "bf16")
+    wide[:, :, R:R + 16] = to_dev(inp["B"], "bf16")
+    wide[:, :, R + 16:] = to_dev(inp["C"], "bf16")
+    y = ops.selective_scan(to_dev(inp["x"], "bf16"), None, to_dev(inp["A"]), wide[:, :, R:R + 16], wide[:, :, R + 16:],
+                           D=to_dev(inp["D"]), z=to_dev(inp["z"], "bf16"), conv_w=to_dev(inp["conv_w"]) if conv else None,
+                           dt_bias=to_dev(bias), variant=DIRECT, tune=cpl, a_geometric=geom, dt_low=wide[:, :, :R],
+                           W_dt=to_dev(W_dt, "bf16"))
+    assert _lib.device_status() == 0
+    assert rel_l2(to_np(y), ref) <= BF16_TOL
+    # kernels without the fusion say so instead of ignoring W_dt
+    with pytest.raises(_lib.HxError) as e:
+        ops.selective_scan(to_dev(inp["x"], "bf16"), None, to_dev(inp["A"]), wide[:, :, R:R + 16], wide[:, :, R + 16:],
+                           variant=TILED, dt_low=wide[:, :, :R], W_dt=to_dev(W_dt, "bf16"))
+    assert e.value.variant == "UnsupportedOperation"
+
+
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_tiled_general_decay(dtype):
     # an A that is not geometric: the caller's flag is 0 and every state takes its own exponential
