@@ -58,6 +58,34 @@ def scan_algorithmic_bytes(batch, seq_len, d_inner, d_state, d_conv, es=2):
     return pts * 4 * es + 2 * batch * seq_len * d_state * es + d_inner * (d_state + d_conv + 1) * 4
 
 
+def pipe_rates():
+    """fp32 FMA and special-function (ex2) results per second of this GPU, measured with the library's probes."""
+    from helixml_b200 import ops
+    return {"fma_per_s": ops.probe_pipe("fma"), "fma2_lanes_per_s": ops.probe_pipe("fma2"), "ex2_per_s": ops.probe_pipe("ex2")}
+
+
+def scan_compute_roof(points, d_state, d_conv, alg_bytes, hbm_gbs, rates, launch_ms):
+    """The scan against the slowest of its three ceilings: bytes at the measured copy bandwidth, exponentials
+    at the measured ex2 rate, fp32 operations at the measured FMA rate.
+
+    `spec`: the operation as it is defined, one exponential per state for the decays plus softplus and the two
+    SiLUs (N + 3 per point) and 3N + k + 8 fp32 operations per point.
+    `kernel`: what the direct kernel issues when A[d][n] = (n+1) A[d][0]: one exponential gives all N decays
+    as powers, so 7 special-function results per point (4 ex2, 2 rcp, 1 lg2) and about 86 fp32 pipe
+    operations (15 for the powers, 48 for the recurrence and the C contraction, 23 point-wise)."""
+    t_hbm = alg_bytes / (hbm_gbs * 1e9) * 1e6
+    out = {"rates": {k: round(v / 1e12, 3) for k, v in rates.items()}, "rates_unit": "1e12 results/s", "t_hbm_us": t_hbm}
+    conv = 1 if d_conv > 0 else 0  # without the conv (it ran in its own kernel) its taps and its SiLU are not this kernel's
+    for name, sfu, fp in (("spec", d_state + 2 + conv, 3 * d_state + d_conv + 8), ("kernel", 5 + 2 * conv, 79 + 7 * conv)):
+        t_sfu = points * sfu / rates["ex2_per_s"] * 1e6
+        t_fma = points * fp / rates["fma_per_s"] * 1e6
+        t_roof = max(t_hbm, t_sfu, t_fma)
+        out[name] = {"sfu_per_point": sfu, "fp32_per_point": fp, "t_sfu_us": t_sfu, "t_fma_us": t_fma, "t_roof_us": t_roof,
+                     "bound": "hbm" if t_roof == t_hbm else ("sfu" if t_roof == t_sfu else "fma"),
+                     "frac_of_t_roof": t_roof / (launch_ms * 1e3)}
+    return out
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -295,6 +323,8 @@ def run_scan(args, cfg, name):
             "roofline": {"bound": "hbm", "kernel": "scan_tiled_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "algorithmic_bytes_per_launch": alg, "traffic": None},
+            "compute_roof": scan_compute_roof(cfg["batch"] * cfg["seq_len"] * cfg["d_inner"], cfg["d_state"], cfg["d_conv"], alg,
+                                              peaks["hbm_gbs"], pipe_rates(), ms_step),
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks, "device_status": status,
         }
         print(json.dumps(line))
@@ -459,7 +489,9 @@ def run_lm(args, cfg, name):
                        "l2": "per-layer activations (0.2-0.4 GB each) exceed the 126 MB L2, no flush"},
             "roofline": roof,
             "stages_ms": stage_ms,
-            "scan": {"gbs": scan_gbs, "frac_of_hbm_peak": scan_gbs / peaks["hbm_gbs"], "ms_per_launch": scan_ms},
+            "scan": {"gbs": scan_gbs, "frac_of_hbm_peak": scan_gbs / peaks["hbm_gbs"], "ms_per_launch": scan_ms,
+                     "compute_roof": scan_compute_roof(B * L * E, N, 0, scan_bytes, peaks["hbm_gbs"], pipe_rates(),
+                                                       scan_ms)},
             "gemm": {"tflops": gemm_tflops, "frac_of_sustained_peak": gemm_tflops / peaks["bf16_tflops_sustained"], "ms_total": gemm_ms},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps * lm.launches_per_forward, "clocks": clocks,
             "device_status": status,

@@ -81,6 +81,7 @@ _PROTOS = {
     "hx_selective_scan_fwd_noalloc": (C.c_int, [C.POINTER(ScanArgs), C.c_void_p]),
     "hx_scan_check_geometric": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int32)]),
     "hx_device_status": (C.c_int, [C.POINTER(C.c_int32), C.c_int32]),
+    "hx_probe_pipe": (C.c_int, [C.c_int32, C.c_void_p, C.c_size_t, C.POINTER(C.c_double), C.c_void_p]),
     "hx_conv1d_silu_fwd": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                      C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "hx_s4_diag_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -99,6 +100,7 @@ _PROTOS = {
                                    C.c_void_p]),
     "hx_silu_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "hx_mamba_block_fwd": (C.c_int, [C.POINTER(MambaBlockArgs), C.c_void_p]),
+    "hx_mamba_block_kernel_launches": (C.c_int, [C.POINTER(MambaBlockArgs), C.POINTER(C.c_int32)]),
     "hx_mamba_block_workspace_bytes": (C.c_int, [C.POINTER(MambaBlockArgs), C.POINTER(C.c_size_t)]),
     # ---- module-level API
     "hx_manual_seed": (None, [C.c_uint64]),

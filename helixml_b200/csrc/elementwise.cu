@@ -124,54 +124,80 @@ conv_silu_kernel(const T *__restrict__ x, int64_t xb, int64_t xr, const float *_
     }
 }
 
-// Lean bf16 variant: thread = one channel PAIR (a 4-byte load; a warp still reads 128 contiguous bytes per row),
-// so registers stay low and many more rows are in flight per SM than with 16-byte groups.
-template <int TB>
+// Lean bf16 variant: a thread owns CH (2 or 4) adjacent channels and a strip of TB time steps; a warp reads
+// 32*CH contiguous channels per row.  Rows are fetched eight at a time before any arithmetic, so every thread
+// keeps eight loads in flight, and the strips are short enough (TB = 32) that the grid has several thousand
+// CTAs to spread over the SMs.  The window of the three previous rows lives in registers.
+template <int CH> struct PackBf16;
+template <> struct PackBf16<2> { using T = uint32_t; };
+template <> struct PackBf16<4> { using T = uint2; };
+
+template <int CH>
+__device__ __forceinline__ void unpack_bf16(const typename PackBf16<CH>::T &v, float *f) {
+    const uint32_t *p = reinterpret_cast<const uint32_t *>(&v);
+#pragma unroll
+    for (int i = 0; i < CH / 2; ++i) {
+        f[2 * i] = __uint_as_float(p[i] << 16);
+        f[2 * i + 1] = __uint_as_float(p[i] & 0xffff0000u);
+    }
+}
+
+template <int CH, int TB>
 __global__ void __launch_bounds__(128)
-conv_silu_pair_kernel(const __nv_bfloat16 *__restrict__ x, int64_t xb, int64_t xr, const float *__restrict__ cw,
-                      const float *__restrict__ cb, __nv_bfloat16 *__restrict__ u, int64_t ub, int64_t ur, int L, int D, int K) {
-    const int pr = blockIdx.x * blockDim.x + threadIdx.x;
-    const int d = pr * 2;
+conv_silu_strip_kernel(const __nv_bfloat16 *__restrict__ x, int64_t xb, int64_t xr, const float *__restrict__ cw,
+                       const float *__restrict__ cb, __nv_bfloat16 *__restrict__ u, int64_t ub, int64_t ur, int L, int D, int K) {
+    using V = typename PackBf16<CH>::T;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * CH;
     if (d >= D) return;
     const int t0 = blockIdx.y * TB;
     const int b = blockIdx.z;
-    float2 w[4], bias;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const int src = j - (4 - K);
-        w[j] = src >= 0 ? make_float2(cw[(int64_t)d * K + src], cw[(int64_t)(d + 1) * K + src]) : make_float2(0.f, 0.f);
-    }
-    bias = cb ? make_float2(cb[d], cb[d + 1]) : make_float2(0.f, 0.f);
-    const __nv_bfloat16 *xp = x + b * xb + d;
-    __nv_bfloat16 *up = u + b * ub + d;
-    auto ldp = [&](int t) {
-        const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(xp + (int64_t)t * xr));
-        return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xffff0000u));
-    };
-    float2 w0 = t0 >= 3 ? ldp(t0 - 3) : make_float2(0.f, 0.f);
-    float2 w1 = t0 >= 2 ? ldp(t0 - 2) : make_float2(0.f, 0.f);
-    float2 w2 = t0 >= 1 ? ldp(t0 - 1) : make_float2(0.f, 0.f);
     const int n = min(TB, L - t0);
-    // rows are fetched eight at a time before any arithmetic, so eight loads per thread are in flight
-    for (int k0 = 0; k0 < n; k0 += 8) {
-        float2 rows[8];
+    float w[4][CH], bias[CH];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) rows[e] = (k0 + e < n) ? ldp(t0 + k0 + e) : make_float2(0.f, 0.f);
+    for (int e = 0; e < CH; ++e) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-        const int k = k0 + e;
-        if (k >= n) break;
-        const float2 cur = rows[e];
-        float2 c = bias;
-        c.x = fmaf(w[0].x, w0.x, c.x); c.y = fmaf(w[0].y, w0.y, c.y);
-        c.x = fmaf(w[1].x, w1.x, c.x); c.y = fmaf(w[1].y, w1.y, c.y);
-        c.x = fmaf(w[2].x, w2.x, c.x); c.y = fmaf(w[2].y, w2.y, c.y);
-        c.x = fmaf(w[3].x, cur.x, c.x); c.y = fmaf(w[3].y, cur.y, c.y);
-        const __nv_bfloat162 o = __floats2bfloat162_rn(silu_fast(c.x), silu_fast(c.y));
-        *reinterpret_cast<uint32_t *>(up + (int64_t)(t0 + k) * ur) = *reinterpret_cast<const uint32_t *>(&o);
-        w0 = w1; w1 = w2; w2 = cur;
+        for (int j = 0; j < 4; ++j) {  // tap j of the 4-wide window is tap j-(4-K) of the K given ones
+            const int src = j - (4 - K);
+            w[j][e] = src >= 0 ? cw[(int64_t)(d + e) * K + src] : 0.f;
         }
+        bias[e] = cb ? cb[d + e] : 0.f;
     }
+    const __nv_bfloat16 *xp = x + b * xb + d + (int64_t)t0 * xr;
+    __nv_bfloat16 *up = u + b * ub + d + (int64_t)t0 * ur;
+    auto ld = [&](int k) { return __ldg(reinterpret_cast<const V *>(xp + (int64_t)k * xr)); };
+    float w0[CH], w1[CH], w2[CH];  // x[t-3], x[t-2], x[t-1]
+#pragma unroll
+    for (int e = 0; e < CH; ++e) w0[e] = w1[e] = w2[e] = 0.f;
+    if (t0 >= 3) unpack_bf16<CH>(ld(-3), w0);
+    if (t0 >= 2) unpack_bf16<CH>(ld(-2), w1);
+    if (t0 >= 1) unpack_bf16<CH>(ld(-1), w2);
+    auto step = [&](const V &v, int k) {
+        float cur[CH];
+        unpack_bf16<CH>(v, cur);
+        V o;
+        uint32_t *op = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+        for (int e = 0; e < CH; e += 2) {
+            float c0 = fmaf(w[0][e], w0[e], bias[e]), c1 = fmaf(w[0][e + 1], w0[e + 1], bias[e + 1]);
+            c0 = fmaf(w[1][e], w1[e], c0); c1 = fmaf(w[1][e + 1], w1[e + 1], c1);
+            c0 = fmaf(w[2][e], w2[e], c0); c1 = fmaf(w[2][e + 1], w2[e + 1], c1);
+            c0 = fmaf(w[3][e], cur[e], c0); c1 = fmaf(w[3][e + 1], cur[e + 1], c1);
+            const __nv_bfloat162 ob = __floats2bfloat162_rn(silu_fast(c0), silu_fast(c1));
+            op[e / 2] = *reinterpret_cast<const uint32_t *>(&ob);
+        }
+        *reinterpret_cast<V *>(up + (int64_t)k * ur) = o;
+#pragma unroll
+        for (int e = 0; e < CH; ++e) { w0[e] = w1[e]; w1[e] = w2[e]; w2[e] = cur[e]; }
+    };
+    int k0 = 0;
+    for (; k0 + 8 <= n; k0 += 8) {
+        V v[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[e] = ld(k0 + e);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) step(v[e], k0 + e);
+    }
+    for (; k0 < n; ++k0) step(ld(k0), k0);
 }
 
 // ---------------------------------------------------------------- RMSNorm (+ residual add)
@@ -317,13 +343,24 @@ hx_status hx_conv1d_silu_fwd(const void *x, int64_t xb, int64_t xr, const float 
                      (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(u) & 15) == 0;
     const int groups = vec ? d_inner / vn : d_inner;
     dim3 grid((groups + 63) / 64, (seq_len + TB - 1) / TB, batch), block(64);
-    if (io_dtype == HX_BF16 && d_inner % 2 == 0 && xr % 2 == 0 && ur % 2 == 0 && xb % 2 == 0 && ub % 2 == 0 &&
-        (reinterpret_cast<uintptr_t>(x) & 3) == 0 && (reinterpret_cast<uintptr_t>(u) & 3) == 0) {
-        constexpr int TBP = 64;
-        dim3 g2((d_inner / 2 + 127) / 128, (seq_len + TBP - 1) / TBP, batch);
-        conv_silu_pair_kernel<TBP><<<g2, 128, 0, st>>>(static_cast<const __nv_bfloat16 *>(x), xb, xr, conv_w, conv_b,
-                                                      static_cast<__nv_bfloat16 *>(u), ub, ur, seq_len, d_inner, d_conv);
-        return hx::check_launch("conv_silu_pair_kernel");
+    if (io_dtype == HX_BF16) {
+        auto fits = [&](int ch) {
+            return d_inner % ch == 0 && xr % ch == 0 && ur % ch == 0 && xb % ch == 0 && ub % ch == 0 &&
+                   (reinterpret_cast<uintptr_t>(x) % (2 * ch)) == 0 && (reinterpret_cast<uintptr_t>(u) % (2 * ch)) == 0;
+        };
+        constexpr int TBS = 32;
+        auto xp = static_cast<const __nv_bfloat16 *>(x);
+        auto up = static_cast<__nv_bfloat16 *>(u);
+        if (fits(4)) {
+            dim3 g2((d_inner / 4 + 127) / 128, (seq_len + TBS - 1) / TBS, batch);
+            conv_silu_strip_kernel<4, TBS><<<g2, 128, 0, st>>>(xp, xb, xr, conv_w, conv_b, up, ub, ur, seq_len, d_inner, d_conv);
+            return hx::check_launch("conv_silu_strip_kernel");
+        }
+        if (fits(2)) {
+            dim3 g2((d_inner / 2 + 127) / 128, (seq_len + TBS - 1) / TBS, batch);
+            conv_silu_strip_kernel<2, TBS><<<g2, 128, 0, st>>>(xp, xb, xr, conv_w, conv_b, up, ub, ur, seq_len, d_inner, d_conv);
+            return hx::check_launch("conv_silu_strip_kernel");
+        }
     }
     if (io_dtype == HX_BF16) {
         auto xp = static_cast<const __nv_bfloat16 *>(x);

@@ -569,8 +569,13 @@ Result<Unit> ByteLM::ensure_buffers(int64_t batch, int64_t seq_len) {
 }
 
 int64_t ByteLM::launches_per_forward() const {
-    // embedding + per layer (norm, 4 GEMMs, conv, scan) + final norm + logits GEMM
-    return 1 + (int64_t)blocks.size() * 7 + 2;
+    // embedding + per layer (norm + the block's 5 or 6 kernels) + final norm + logits GEMM
+    int32_t per_block = 6;
+    if (buf_ && buf_->batch > 0 && !blocks.empty()) {
+        hx_mamba_block_args a = block_args(*blocks[0], buf_->batch, buf_->seq_len);
+        hx_mamba_block_kernel_launches(&a, &per_block);
+    }
+    return 1 + (int64_t)blocks.size() * (1 + per_block) + 2;
 }
 
 Result<Unit> ByteLM::forward_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream) {

@@ -60,6 +60,15 @@ static hx_status validate(const hx_mamba_block_args *a) {
     return HX_OK;
 }
 
+// True when the dt projection runs inside the scan kernel instead of as a GEMM of its own.
+static bool fuses_dt(const hx_mamba_block_args *a, int W) {
+    const int R = a->dt_rank;
+    const double chains = (double)a->batch * a->d_inner;
+    return a->io_dtype == HX_BF16 && a->d_state == 16 && R >= 8 && R <= 64 && R % 8 == 0 && W % 8 == 0 &&
+           (a->scan_variant == HX_SCAN_DIRECT ||
+            (a->scan_variant == HX_SCAN_AUTO && chains / 32.0 >= 8.0 * hx::sm_count()));
+}
+
 }  // namespace block
 }  // namespace hx
 
@@ -70,6 +79,15 @@ hx_status hx_mamba_block_workspace_bytes(const hx_mamba_block_args *a, size_t *b
     hx_status s = hx::block::validate(a);
     if (s != HX_OK) return s;
     *bytes = hx::block::plan(a).total;
+    return HX_OK;
+}
+
+hx_status hx_mamba_block_kernel_launches(const hx_mamba_block_args *a, int32_t *launches) {
+    HX_REQUIRE(launches != nullptr, HX_ERR_INVALID_INPUT, "launches is NULL");
+    hx_status s = hx::block::validate(a);
+    if (s != HX_OK) return s;
+    // in_proj, conv, x_proj, dt_proj (unless fused into the scan), scan, out_proj
+    *launches = (a->batch == 0 || a->seq_len == 0) ? 0 : (hx::block::fuses_dt(a, (int)hx::block::plan(a).W) ? 5 : 6);
     return HX_OK;
 }
 
@@ -118,10 +136,7 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     // 4. dt_lin = dt_low W_dt^T                          [T, E]   (bias and softplus happen inside the scan)
     // With bf16 operands and enough chains for the one-lane-per-channel scan, the projection is done inside the
     // scan kernel (its producer warp, tensor cores) and this GEMM, its 2*T*E-byte write and read disappear.
-    const double chains = (double)a->batch * E;
-    const bool fuse_dt = bf && N == 16 && R >= 8 && R <= 64 && R % 8 == 0 && W % 8 == 0 &&
-                         (a->scan_variant == HX_SCAN_DIRECT ||
-                          (a->scan_variant == HX_SCAN_AUTO && chains / 32.0 >= 8.0 * hx::sm_count()));
+    const bool fuse_dt = fuses_dt(a, W);
     if (!fuse_dt && (s = gemm(dbc, W, a->W_dt, R, dtl, E, (int)T, E, R)) != HX_OK) return s;
     mark(4);
     // 5. fused scan on strided views

@@ -47,6 +47,17 @@ def check_geometric(A: torch.Tensor) -> bool:
     return bool(flag.value)
 
 
+def probe_pipe(kind: str) -> float:
+    """Results per second of one arithmetic pipe on the current GPU: 'fma' (scalar fp32 fused multiply-adds),
+    'fma2' (the packed two-wide form, counted per lane) or 'ex2' (special-function exponentials)."""
+    code = {"fma": 0, "fma2": 1, "ex2": 2}[kind]
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    scratch = torch.empty(sms * 8 * 256, device="cuda", dtype=torch.float32)
+    out = C.c_double(0.0)
+    L.check(L.lib().hx_probe_pipe(code, _p(scratch), scratch.numel() * 4, C.byref(out), _stream()))
+    return out.value
+
+
 def scan_workspace_bytes(batch, seq_len, d_inner, dtype, seq_splits=0) -> int:
     a = L.ScanArgs()
     a.batch, a.seq_len, a.d_inner, a.d_state = batch, seq_len, d_inner, 16

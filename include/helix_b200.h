@@ -190,6 +190,15 @@ HX_API hx_status hx_scan_check_geometric(const float *A, int32_t d_inner, int32_
  * clear are not valid; map it to TensorError::BackendError. */
 HX_API hx_status hx_device_status(int32_t *status, int32_t clear);
 
+/* Measures, on the current device, how many results per second one arithmetic pipe retires: fp32
+ * fused multiply-adds (scalar, or the packed two-wide form, counted per lane) or special-function
+ * ex2.approx results.  The scan is bound by these pipes rather than by HBM, so the benchmark reports it
+ * against max(bytes / bandwidth, exps / ex2 rate, fp32 operations / fma rate) with the rates measured here.
+ * Synchronous; `scratch` is device memory of at least 8 * 256 * 4 bytes per SM (results nobody reads).
+ * No counterpart in the reference. */
+typedef enum hx_probe_kind { HX_PROBE_FMA = 0, HX_PROBE_FMA2 = 1, HX_PROBE_EX2 = 2 } hx_probe_kind;
+HX_API hx_status hx_probe_pipe(int32_t kind, void *scratch, size_t scratch_bytes, double *per_second, void *stream);
+
 /* ---- causal depthwise conv + SiLU alone: u = silu(conv(x)).  In the full block the x_proj GEMM
  *      consumes u before the scan can run.  Stands in for nn::ssm::MambaBlock::conv1d
  *      (crates/nn/src/ssm.rs:467-471, `input.clone()` in the reference). */
@@ -280,6 +289,10 @@ typedef struct hx_mamba_block_args {
 
 HX_API hx_status hx_mamba_block_fwd(const hx_mamba_block_args *args, void *stream);
 HX_API hx_status hx_mamba_block_workspace_bytes(const hx_mamba_block_args *args, size_t *bytes);
+/* Kernel launches one hx_mamba_block_fwd call with these arguments makes: 6 (in_proj, conv, x_proj, dt_proj,
+ * scan, out_proj), or 5 when the dt projection is computed inside the scan kernel (bf16, d_state 16,
+ * dt_rank a multiple of 8 up to 64, and enough batch * d_inner chains for the one-lane-per-channel scan). */
+HX_API hx_status hx_mamba_block_kernel_launches(const hx_mamba_block_args *args, int32_t *launches);
 
 /* =============================================================================================
  * Module-level API: opaque handles over the C++ host layer (helixml_b200/csrc/helix_host.hpp), which
@@ -333,6 +346,8 @@ HX_API hx_status hx_byte_lm_forward_host(hx_module *m, const uint8_t *tokens_hos
                                   int64_t seq_len, void *stream);
 HX_API hx_status hx_byte_lm_forward_device(hx_module *m, const uint8_t *tokens_dev, void *logits_dev, int64_t batch,
                                     int64_t seq_len, void *stream);
+/* Kernel launches of one forward at the shape of the most recent serving call (before any call: of a
+ * forward whose blocks do not fuse the dt projection). */
 HX_API int64_t hx_byte_lm_launches_per_forward(const hx_module *m);
 /* Per-stage timing of the byte LM with CUDA events on the launching stream.  enable = 1 makes the following
  * forward calls record events around every stage; hx_byte_lm_profile_read synchronises, adds the elapsed
