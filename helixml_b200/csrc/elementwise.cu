@@ -152,25 +152,42 @@ conv_silu_strip_kernel(const __nv_bfloat16 *__restrict__ x, int64_t xb, int64_t 
     const int t0 = blockIdx.y * TB;
     const int b = blockIdx.z;
     const int n = min(TB, L - t0);
+    // the strips are short, so the per-thread set-up counts: with four taps a channel's weights are one 16-byte load
     float w[4][CH], bias[CH];
 #pragma unroll
     for (int e = 0; e < CH; ++e) {
+        if (K == 4) {
+            const float4 q = __ldg(reinterpret_cast<const float4 *>(cw) + d + e);
+            w[0][e] = q.x; w[1][e] = q.y; w[2][e] = q.z; w[3][e] = q.w;
+        } else {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {  // tap j of the 4-wide window is tap j-(4-K) of the K given ones
-            const int src = j - (4 - K);
-            w[j][e] = src >= 0 ? cw[(int64_t)(d + e) * K + src] : 0.f;
+            for (int j = 0; j < 4; ++j) {  // tap j of the 4-wide window is tap j-(4-K) of the K given ones
+                const int src = j - (4 - K);
+                w[j][e] = src >= 0 ? cw[(int64_t)(d + e) * K + src] : 0.f;
+            }
         }
-        bias[e] = cb ? cb[d + e] : 0.f;
+    }
+    // no branch around a load here: a conditional load would have to land before the row loads below could be
+    // issued, and with strips this short one more round trip to memory costs a quarter of the kernel's time
+    const float *cbp = cb ? cb : cw;
+#pragma unroll
+    for (int e = 0; e < CH; ++e) {
+        const float v = cbp[d + e];
+        bias[e] = cb ? v : 0.f;
     }
     const __nv_bfloat16 *xp = x + b * xb + d + (int64_t)t0 * xr;
     __nv_bfloat16 *up = u + b * ub + d + (int64_t)t0 * ur;
-    auto ld = [&](int k) { return __ldg(reinterpret_cast<const V *>(xp + (int64_t)k * xr)); };
-    float w0[CH], w1[CH], w2[CH];  // x[t-3], x[t-2], x[t-1]
+    auto ld = [&](int k) { return *reinterpret_cast<const V *>(xp + (int64_t)k * xr); };
+    float w0[CH], w1[CH], w2[CH];  // x[t-3], x[t-2], x[t-1]; rows before the sequence start read row t0 and are zeroed
+    unpack_bf16<CH>(ld(t0 >= 3 ? -3 : 0), w0);
+    unpack_bf16<CH>(ld(t0 >= 2 ? -2 : 0), w1);
+    unpack_bf16<CH>(ld(t0 >= 1 ? -1 : 0), w2);
 #pragma unroll
-    for (int e = 0; e < CH; ++e) w0[e] = w1[e] = w2[e] = 0.f;
-    if (t0 >= 3) unpack_bf16<CH>(ld(-3), w0);
-    if (t0 >= 2) unpack_bf16<CH>(ld(-2), w1);
-    if (t0 >= 1) unpack_bf16<CH>(ld(-1), w2);
+    for (int e = 0; e < CH; ++e) {
+        w0[e] = t0 >= 3 ? w0[e] : 0.f;
+        w1[e] = t0 >= 2 ? w1[e] : 0.f;
+        w2[e] = t0 >= 1 ? w2[e] : 0.f;
+    }
     auto step = [&](const V &v, int k) {
         float cur[CH];
         unpack_bf16<CH>(v, cur);
