@@ -56,6 +56,18 @@ class MambaBlockArgs(C.Structure):
         ("W_out", C.c_void_p), ("conv_w", C.c_void_p), ("conv_b", C.c_void_p), ("b_dt", C.c_void_p),
         ("A", C.c_void_p), ("Dskip", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("scan_variant", C.c_int32), ("a_geometric", C.c_int32), ("stage_events", C.c_void_p),
+        ("h_last", C.c_void_p), ("conv_state", C.c_void_p),
+    ]
+
+
+class MambaStepArgs(C.Structure):
+    _fields_ = [
+        ("batch", C.c_int32), ("d_model", C.c_int32), ("d_inner", C.c_int32), ("d_state", C.c_int32),
+        ("d_conv", C.c_int32), ("dt_rank", C.c_int32), ("io_dtype", C.c_int32), ("reserved", C.c_int32),
+        ("x", C.c_void_p), ("out", C.c_void_p), ("W_in", C.c_void_p), ("W_x", C.c_void_p), ("W_dt", C.c_void_p),
+        ("W_out", C.c_void_p), ("conv_w", C.c_void_p), ("conv_b", C.c_void_p), ("b_dt", C.c_void_p),
+        ("A", C.c_void_p), ("Dskip", C.c_void_p), ("h", C.c_void_p), ("conv_state", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
 
@@ -101,6 +113,10 @@ _PROTOS = {
     "hx_silu_fwd": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     "hx_mamba_block_fwd": (C.c_int, [C.POINTER(MambaBlockArgs), C.c_void_p]),
     "hx_mamba_block_kernel_launches": (C.c_int, [C.POINTER(MambaBlockArgs), C.POINTER(C.c_int32)]),
+    "hx_mamba_block_step": (C.c_int, [C.POINTER(MambaStepArgs), C.c_void_p]),
+    "hx_mamba_step_workspace_bytes": (C.c_int, [C.POINTER(MambaStepArgs), C.POINTER(C.c_size_t)]),
+    "hx_conv_state_from_prefill": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
+                                             C.c_int32, C.c_void_p]),
     "hx_mamba_block_workspace_bytes": (C.c_int, [C.POINTER(MambaBlockArgs), C.POINTER(C.c_size_t)]),
     # ---- module-level API
     "hx_manual_seed": (None, [C.c_uint64]),
@@ -123,6 +139,10 @@ _PROTOS = {
     "hx_byte_lm_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "hx_byte_lm_forward_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "hx_byte_lm_launches_per_forward": (C.c_int64, [C.c_void_p]),
+    "hx_byte_lm_prefill_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
+    "hx_byte_lm_decode_step_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
+    "hx_byte_lm_decode_graph": (C.c_int, [C.c_void_p, C.c_int32]),
+    "hx_byte_lm_launches_per_decode_step": (C.c_int64, [C.c_void_p]),
     "hx_byte_lm_profile": (C.c_int, [C.c_void_p, C.c_int32]),
     "hx_byte_lm_profile_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int32)]),
     "hx_module_num_parameters": (C.c_int32, [C.c_void_p]),

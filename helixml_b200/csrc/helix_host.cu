@@ -433,11 +433,45 @@ size_t MambaBlock::workspace_bytes(int64_t batch, int64_t seq_len) const {
 }
 
 Result<Unit> MambaBlock::forward_into(const void *x, void *out, int64_t batch, int64_t seq_len, void *workspace,
-                                      size_t ws_bytes, void *stream, void **stage_events) const {
+                                      size_t ws_bytes, void *stream, void **stage_events, float *h_last,
+                                      void *conv_state) const {
     hx_mamba_block_args a = block_args(*this, batch, seq_len);
     a.x = x; a.out = out; a.workspace = workspace; a.workspace_bytes = ws_bytes;
     a.stage_events = stage_events;
+    a.h_last = h_last; a.conv_state = conv_state;
     HELIX_TRY_ABI(hx_mamba_block_fwd(&a, stream));
+    return Unit{};
+}
+
+static hx_mamba_step_args step_args(const MambaBlock &m, int64_t batch) {
+    hx_mamba_step_args a;
+    std::memset(&a, 0, sizeof(a));
+    a.batch = (int)batch;
+    a.d_model = (int)m.d_model; a.d_inner = (int)m.d_inner; a.d_state = (int)m.d_state; a.d_conv = (int)m.d_conv;
+    a.dt_rank = (int)m.dt_rank;
+    a.io_dtype = (int)m.dtype;
+    a.W_in = m.W_in.data(); a.W_x = m.W_x.data(); a.W_dt = m.W_dt.data(); a.W_out = m.W_out.data();
+    a.conv_w = static_cast<const float *>(m.conv_w.data());
+    a.conv_b = static_cast<const float *>(m.conv_b.data());
+    a.b_dt = static_cast<const float *>(m.b_dt.data());
+    a.A = static_cast<const float *>(m.A.data());
+    a.Dskip = static_cast<const float *>(m.D.data());
+    return a;
+}
+
+size_t MambaBlock::step_workspace_bytes(int64_t batch) const {
+    hx_mamba_step_args a = step_args(*this, batch);
+    size_t n = 0;
+    hx_mamba_step_workspace_bytes(&a, &n);
+    return n;
+}
+
+Result<Unit> MambaBlock::step_into(const void *x, void *out, int64_t batch, float *h, void *conv_state, void *workspace,
+                                   size_t ws_bytes, void *stream) const {
+    hx_mamba_step_args a = step_args(*this, batch);
+    a.x = x; a.out = out; a.h = h; a.conv_state = conv_state;
+    a.workspace = workspace; a.workspace_bytes = ws_bytes;
+    HELIX_TRY_ABI(hx_mamba_block_step(&a, stream));
     return Unit{};
 }
 
@@ -470,6 +504,21 @@ struct ByteLM::Buffers {
     DeviceTensor tokens, resid, normed, block_out, logits, workspace;
 };
 
+// Decode state of one batch: per layer the scan state and the conv window, the step's own buffers, and the
+// captured graph of one step over those buffers.
+struct ByteLM::Decode {
+    int64_t batch = 0;
+    std::vector<DeviceTensor> h, conv;  // per layer: [B, E, N] fp32, [B, 3, E] model dtype
+    DeviceTensor tokens, resid, normed, block_out, logits, workspace;
+    cudaStream_t capture_stream = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int64_t steps = 0;
+    ~Decode() {
+        if (exec) cudaGraphExecDestroy(exec);
+        if (capture_stream) cudaStreamDestroy(capture_stream);
+    }
+};
+
 // Event-based stage timing: per forward, events[0] before the embedding, then per layer one event before the
 // norm and the block's seven, then events before the final norm, before the head and after it.
 struct ByteLM::Profile {
@@ -494,6 +543,7 @@ struct ByteLM::Profile {
 ByteLM::~ByteLM() {
     delete buf_;
     delete prof_;
+    delete dec_;
 }
 
 Result<Unit> ByteLM::set_profile(bool enable) {
@@ -579,9 +629,110 @@ int64_t ByteLM::launches_per_forward() const {
 }
 
 Result<Unit> ByteLM::forward_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream) {
+    return run_layers(tokens_dev, logits_dev, batch, seq_len, stream, false);
+}
+
+Result<Unit> ByteLM::prefill_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream) {
+    return run_layers(tokens_dev, logits_dev, batch, seq_len, stream, true);
+}
+
+Result<Unit> ByteLM::ensure_decode(int64_t batch) {
+    if (dec_ && dec_->batch == batch) return Unit{};
+    delete dec_;
+    dec_ = new Decode();
+    const MambaBlock &b0 = *blocks[0];
+    for (size_t l = 0; l < blocks.size(); ++l) {
+        DeviceTensor h, c;
+        HELIX_ASSIGN(h, DeviceTensor::zeros(Shape({batch, b0.d_inner, b0.d_state}), DType::F32, device_));
+        HELIX_ASSIGN(c, DeviceTensor::zeros(Shape({batch, 3, b0.d_inner}), dtype, device_));
+        dec_->h.push_back(std::move(h));
+        dec_->conv.push_back(std::move(c));
+    }
+    HELIX_ASSIGN(dec_->tokens, DeviceTensor::empty(Shape({batch}), DType::U8, device_));
+    HELIX_ASSIGN(dec_->resid, DeviceTensor::empty(Shape({batch, d_model}), DType::F32, device_));
+    HELIX_ASSIGN(dec_->normed, DeviceTensor::empty(Shape({batch, d_model}), dtype, device_));
+    HELIX_ASSIGN(dec_->block_out, DeviceTensor::empty(Shape({batch, d_model}), dtype, device_));
+    HELIX_ASSIGN(dec_->logits, DeviceTensor::empty(Shape({batch, 256}), dtype, device_));
+    HELIX_ASSIGN(dec_->workspace, DeviceTensor::empty(Shape({(int64_t)b0.step_workspace_bytes(batch)}), DType::U8, device_));
+    dec_->batch = batch;
+    return Unit{};
+}
+
+// One step over the module's own buffers (dec_->tokens in, dec_->logits out): what the graph captures.
+Result<Unit> ByteLM::enqueue_step(void *stream) {
+    const int64_t B = dec_->batch;
+    float *resid = static_cast<float *>(dec_->resid.data());
+    HELIX_TRY_ABI(hx_embedding_fwd(static_cast<const uint8_t *>(dec_->tokens.data()), embedding.data(), (int)dtype, resid, HX_F32,
+                                   B, (int)d_model, stream));
+    for (size_t l = 0; l < blocks.size(); ++l) {
+        const void *delta = l == 0 ? nullptr : dec_->block_out.data();
+        HELIX_TRY_ABI(hx_rmsnorm_fwd(delta, (int)dtype, resid, static_cast<const float *>(norms[l]->weight.data()),
+                                     dec_->normed.data(), (int)dtype, B, (int)d_model, eps, stream));
+        HELIX_TRY(blocks[l]->step_into(dec_->normed.data(), dec_->block_out.data(), B, static_cast<float *>(dec_->h[l].data()),
+                                       dec_->conv[l].data(), dec_->workspace.data(), (size_t)dec_->workspace.numel(), stream));
+    }
+    HELIX_TRY_ABI(hx_rmsnorm_fwd(dec_->block_out.data(), (int)dtype, resid, static_cast<const float *>(norm_f.data()),
+                                 dec_->normed.data(), (int)dtype, B, (int)d_model, eps, stream));
+    if (dtype == DType::BF16 && d_model % 8 == 0)
+        HELIX_TRY_ABI(hx_gemm_bf16(dec_->normed.data(), d_model, embedding.data(), d_model, nullptr, dec_->logits.data(), 256,
+                                   HX_BF16, (int)B, 256, (int)d_model, 0, stream));
+    else
+        HELIX_TRY_ABI(hx_gemm_simt(dec_->normed.data(), d_model, embedding.data(), d_model, nullptr, dec_->logits.data(), 256,
+                                   (int)dtype, (int)dtype, (int)B, 256, (int)d_model, 0, stream));
+    return Unit{};
+}
+
+Result<Unit> ByteLM::decode_step_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, void *stream) {
+    if (!tokens_dev || !logits_dev) return err(HX_ERR_INVALID_INPUT, "ByteLM::decode_step_device: NULL buffer");
+    if (!dec_ || dec_->batch != batch)
+        return err(HX_ERR_INVALID_INPUT, "ByteLM::decode_step_device: no prefill state for batch " + std::to_string(batch));
+    HELIX_TRY(use_device(device_));
+    cudaStream_t st = (cudaStream_t)stream;
+    if (cudaMemcpyAsync(dec_->tokens.data(), tokens_dev, (size_t)batch, cudaMemcpyDeviceToDevice, st) != cudaSuccess)
+        return err(HX_ERR_BACKEND, "ByteLM::decode_step_device: token copy failed");
+    // The first step runs as plain launches (it also sets the kernels' attributes); the second one is captured
+    // on a private stream (capture is not allowed on the legacy default stream) and every later step replays it.
+    if (decode_graph_ && dec_->steps >= 1 && !dec_->exec) {
+        if (!dec_->capture_stream && cudaStreamCreateWithFlags(&dec_->capture_stream, cudaStreamNonBlocking) != cudaSuccess)
+            return err(HX_ERR_BACKEND, "ByteLM::decode_step_device: cannot create the capture stream");
+        if (cudaStreamBeginCapture(dec_->capture_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess)
+            return err(HX_ERR_BACKEND, "ByteLM::decode_step_device: cudaStreamBeginCapture failed");
+        auto r = enqueue_step(dec_->capture_stream);
+        cudaGraph_t graph = nullptr;
+        const cudaError_t ce = cudaStreamEndCapture(dec_->capture_stream, &graph);
+        if (!r.ok()) {
+            if (graph) cudaGraphDestroy(graph);
+            return r.error();
+        }
+        if (ce != cudaSuccess || !graph) return err(HX_ERR_BACKEND, "ByteLM::decode_step_device: stream capture failed");
+        const cudaError_t ie = cudaGraphInstantiate(&dec_->exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ie != cudaSuccess) {
+            dec_->exec = nullptr;
+            return err(HX_ERR_BACKEND, "ByteLM::decode_step_device: cudaGraphInstantiate failed");
+        }
+    }
+    if (decode_graph_ && dec_->exec) {
+        if (cudaGraphLaunch(dec_->exec, st) != cudaSuccess) return err(HX_ERR_BACKEND, "ByteLM::decode_step_device: graph launch failed");
+    } else {
+        HELIX_TRY(enqueue_step(stream));
+    }
+    dec_->steps += 1;
+    if (cudaMemcpyAsync(logits_dev, dec_->logits.data(), (size_t)batch * 256 * dtype_size(dtype), cudaMemcpyDeviceToDevice, st) !=
+        cudaSuccess)
+        return err(HX_ERR_BACKEND, "ByteLM::decode_step_device: logits copy failed");
+    return Unit{};
+}
+
+Result<Unit> ByteLM::run_layers(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream,
+                                bool keep_state) {
     if (batch <= 0 || seq_len <= 0) return err(HX_ERR_INVALID_DIMENSION, "ByteLM: batch and seq_len must be positive");
     HELIX_TRY(use_device(device_));
     HELIX_TRY(ensure_buffers(batch, seq_len));
+    if (keep_state) {
+        HELIX_TRY(ensure_decode(batch));
+        dec_->steps = 0;
+    }
     const int64_t T = batch * seq_len;
     float *resid = static_cast<float *>(buf_->resid.data());
     auto mark = [&](int cls) {
@@ -612,7 +763,9 @@ Result<Unit> ByteLM::forward_device(const uint8_t *tokens_dev, void *logits_dev,
             sevp = sev;
         }
         HELIX_TRY(blocks[l]->forward_into(buf_->normed.data(), buf_->block_out.data(), batch, seq_len, buf_->workspace.data(),
-                                          (size_t)buf_->workspace.numel(), stream, sevp));
+                                          (size_t)buf_->workspace.numel(), stream, sevp,
+                                          keep_state ? static_cast<float *>(dec_->h[l].data()) : nullptr,
+                                          keep_state ? dec_->conv[l].data() : nullptr));
     }
     mark(1);
     HELIX_TRY_ABI(hx_rmsnorm_fwd(buf_->block_out.data(), (int)dtype, resid, static_cast<const float *>(norm_f.data()),
@@ -820,6 +973,38 @@ hx_status hx_byte_lm_forward_device(hx_module *m, const uint8_t *tokens_dev, voi
     auto r = lm->forward_device(tokens_dev, logits_dev, batch, seq_len, stream);
     HX_RETURN_IF_ERR(r);
     return HX_OK;
+}
+
+hx_status hx_byte_lm_prefill_device(hx_module *m, const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len,
+                                    void *stream) {
+    HX_REQUIRE(m && tokens_dev && logits_dev, HX_ERR_INVALID_INPUT, "hx_byte_lm_prefill_device: NULL argument");
+    auto *lm = dynamic_cast<helix::ByteLM *>(m->m.get());
+    HX_REQUIRE(lm != nullptr, HX_ERR_UNSUPPORTED_OPERATION, "prefill on a module that is not a ByteLM");
+    auto r = lm->prefill_device(tokens_dev, logits_dev, batch, seq_len, stream);
+    HX_RETURN_IF_ERR(r);
+    return HX_OK;
+}
+
+hx_status hx_byte_lm_decode_step_device(hx_module *m, const uint8_t *tokens_dev, void *logits_dev, int64_t batch, void *stream) {
+    HX_REQUIRE(m != nullptr, HX_ERR_INVALID_INPUT, "hx_byte_lm_decode_step_device: module is NULL");
+    auto *lm = dynamic_cast<helix::ByteLM *>(m->m.get());
+    HX_REQUIRE(lm != nullptr, HX_ERR_UNSUPPORTED_OPERATION, "decode step on a module that is not a ByteLM");
+    auto r = lm->decode_step_device(tokens_dev, logits_dev, batch, stream);
+    HX_RETURN_IF_ERR(r);
+    return HX_OK;
+}
+
+hx_status hx_byte_lm_decode_graph(hx_module *m, int32_t enable) {
+    HX_REQUIRE(m != nullptr, HX_ERR_INVALID_INPUT, "hx_byte_lm_decode_graph: module is NULL");
+    auto *lm = dynamic_cast<helix::ByteLM *>(m->m.get());
+    HX_REQUIRE(lm != nullptr, HX_ERR_UNSUPPORTED_OPERATION, "decode graph on a module that is not a ByteLM");
+    lm->set_decode_graph(enable != 0);
+    return HX_OK;
+}
+
+int64_t hx_byte_lm_launches_per_decode_step(const hx_module *m) {
+    auto *lm = m ? dynamic_cast<const helix::ByteLM *>(m->m.get()) : nullptr;
+    return lm ? lm->launches_per_decode_step() : 0;
 }
 
 hx_status hx_byte_lm_profile(hx_module *m, int32_t enable) {

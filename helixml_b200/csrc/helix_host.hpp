@@ -194,9 +194,16 @@ class MambaBlock : public Module {
                                                       DType dtype, const Device &device);
     Result<DeviceTensor> forward(const DeviceTensor &input) const override;
     // forward into caller-provided buffers (no allocation): x and out are [batch*seq_len, d_model]
+    // h_last [batch, d_inner, d_state] fp32 and conv_state [batch, 3, d_inner] (model dtype), when given, receive
+    // the state a decode step continues from.
     Result<Unit> forward_into(const void *x, void *out, int64_t batch, int64_t seq_len, void *workspace,
-                              size_t workspace_bytes, void *stream, void **stage_events = nullptr) const;
+                              size_t workspace_bytes, void *stream, void **stage_events = nullptr, float *h_last = nullptr,
+                              void *conv_state = nullptr) const;
     size_t workspace_bytes(int64_t batch, int64_t seq_len) const;
+    // one decode step: x, out [batch, d_model]; h and conv_state are updated in place
+    Result<Unit> step_into(const void *x, void *out, int64_t batch, float *h, void *conv_state, void *workspace,
+                           size_t workspace_bytes, void *stream) const;
+    size_t step_workspace_bytes(int64_t batch) const;
     std::vector<const DeviceTensor *> parameters() const override;
     std::vector<DeviceTensor *> parameters_mut() override;
     Result<Unit> parameters_updated() override;
@@ -225,6 +232,15 @@ class ByteLM : public Module {
     // Same on device buffers: tokens_dev [B*L] u8, logits_dev [B*L, 256] model dtype.
     Result<Unit> forward_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream);
     int64_t launches_per_forward() const;
+    // Serving: prefill_device is forward_device that also keeps, per layer, the scan state and the conv window;
+    // decode_step_device then advances every sequence by one token (tokens_dev [batch] u8, logits_dev
+    // [batch, 256] model dtype).  From its second call on, a step is one replay of a CUDA graph captured over the
+    // module's own step buffers (set_decode_graph(false) keeps plain launches).  One decode stream per module:
+    // the state lives in the module.
+    Result<Unit> prefill_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream);
+    Result<Unit> decode_step_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, void *stream);
+    void set_decode_graph(bool enable) { decode_graph_ = enable; }
+    int64_t launches_per_decode_step() const { return 1 + (int64_t)blocks.size() * 6 + 2; }
     // per-stage CUDA-event timing (see hx_byte_lm_profile in the C header)
     Result<Unit> set_profile(bool enable);
     Result<Unit> read_profile(float *ms9, int *forwards);
@@ -242,9 +258,16 @@ class ByteLM : public Module {
 
   private:
     Result<Unit> ensure_buffers(int64_t batch, int64_t seq_len);
+    Result<Unit> ensure_decode(int64_t batch);
+    Result<Unit> enqueue_step(void *stream);
+    Result<Unit> run_layers(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream,
+                            bool keep_state);
     Device device_;
     struct Buffers;
     Buffers *buf_ = nullptr;
+    struct Decode;
+    Decode *dec_ = nullptr;
+    bool decode_graph_ = true;
     struct Profile;
     Profile *prof_ = nullptr;
 };

@@ -124,6 +124,10 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     mark(0);
     // 1. xz = x W_in^T                                  [T, 2E]
     if ((s = gemm(a->x, M, a->W_in, M, xz, 2 * E, (int)T, 2 * E, M)) != HX_OK) return s;
+    if (a->conv_state &&
+        (s = hx_conv_state_from_prefill(xz, (int64_t)a->seq_len * 2 * E, 2 * E, a->conv_state, a->batch, a->seq_len, E,
+                                        a->io_dtype, stream)) != HX_OK)
+        return s;
     mark(1);
     // 2. u = silu(conv(xs)), xs = xz[:, :E]            [T, E]
     if ((s = hx_conv1d_silu_fwd(xz, (int64_t)a->seq_len * 2 * E, 2 * E, a->conv_w, a->conv_b, u, (int64_t)a->seq_len * E,
@@ -156,6 +160,7 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     sa.Cm = static_cast<char *>(dbc) + (size_t)(R + N) * es; sa.C_batch_stride = (int64_t)a->seq_len * W; sa.C_row_stride = W;
     sa.y = y; sa.y_batch_stride = (int64_t)a->seq_len * E; sa.y_row_stride = E;
     sa.A = a->A; sa.Dskip = a->Dskip; sa.dt_bias = a->b_dt;
+    sa.h_last = a->h_last;
     sa.conv_w = nullptr; sa.conv_b = nullptr;  // u is already activated
     sa.a_geometric = a->a_geometric;
     if (l.splits > 1) {

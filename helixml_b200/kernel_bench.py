@@ -4,6 +4,7 @@
     python -m helixml_b200.kernel_bench conv
     python -m helixml_b200.kernel_bench norm
     python -m helixml_b200.kernel_bench s4
+    python -m helixml_b200.kernel_bench decode
 
 Each case runs 3 warm-up calls, then 10 timed calls between two events on torch's current stream."""
 from __future__ import annotations
@@ -81,6 +82,34 @@ def s4():
     print(f"s4 reference-literal forward_ssm [256, 2048] N=64 f32: {ms * 1e3:.1f} us")
 
 
+def decode():
+    """Byte LM of benchmark configuration 3 (24 blocks, d_model 768, bf16): prefill 32 x 2048, then single-token
+    steps for the whole batch, as plain launches and as replays of the captured CUDA graph."""
+    from . import nn
+    B, L0, steps = 32, 2048, 64
+    nn.manual_seed(3)
+    lm = nn.ByteLM(24, 768, dtype=nn.BF16)
+    tok = torch.randint(0, 256, (B, L0), device="cuda", dtype=torch.uint8)
+    pre = torch.empty(B, L0, 256, device="cuda", dtype=torch.bfloat16)
+    nxt = torch.randint(0, 256, (B,), device="cuda", dtype=torch.uint8)
+    lg = torch.empty(B, 256, device="cuda", dtype=torch.bfloat16)
+    for graph in (False, True):
+        lm.decode_graph(graph)
+        lm.prefill_device(tok.data_ptr(), pre.data_ptr(), B, L0)
+        for _ in range(4):  # the first step is plain, the second captures
+            lm.decode_step_device(nxt.data_ptr(), lg.data_ptr(), B)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            lm.decode_step_device(nxt.data_ptr(), lg.data_ptr(), B)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        print(f"decode step, batch {B}, 24 blocks, d_model 768, {'CUDA graph' if graph else 'plain launches'} "
+              f"({lm.launches_per_decode_step} kernels): {ms * 1e3:.0f} us/step, {B / ms * 1e3:.0f} tokens/s")
+
+
 if __name__ == "__main__":
     what = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": lambda: gemm(sys.argv[2:]), "conv": conv, "norm": norm, "s4": s4}[what]()
+    {"gemm": lambda: gemm(sys.argv[2:]), "conv": conv, "norm": norm, "s4": s4, "decode": decode}[what]()

@@ -200,6 +200,23 @@ class ByteLM(Module):
         L.check(L.lib().hx_byte_lm_forward_device(self._h, C.c_void_p(tokens_ptr), C.c_void_p(logits_ptr), batch, seq_len,
                                                   C.c_void_p(stream)))
 
+    def prefill_device(self, tokens_ptr: int, logits_ptr: int, batch: int, seq_len: int, stream: int = 0) -> None:
+        """forward_device that also keeps the per-layer state decode_step_device continues from."""
+        L.check(L.lib().hx_byte_lm_prefill_device(self._h, C.c_void_p(tokens_ptr), C.c_void_p(logits_ptr), batch, seq_len,
+                                                  C.c_void_p(stream)))
+
+    def decode_step_device(self, tokens_ptr: int, logits_ptr: int, batch: int, stream: int = 0) -> None:
+        """One token per sequence: tokens [batch] u8 in, logits [batch, 256] out (device pointers)."""
+        L.check(L.lib().hx_byte_lm_decode_step_device(self._h, C.c_void_p(tokens_ptr), C.c_void_p(logits_ptr), batch,
+                                                      C.c_void_p(stream)))
+
+    def decode_graph(self, enable: bool) -> None:
+        L.check(L.lib().hx_byte_lm_decode_graph(self._h, 1 if enable else 0))
+
+    @property
+    def launches_per_decode_step(self) -> int:
+        return int(L.lib().hx_byte_lm_launches_per_decode_step(self._h))
+
     @property
     def launches_per_forward(self) -> int:
         return int(L.lib().hx_byte_lm_launches_per_forward(self._h))

@@ -226,9 +226,10 @@ def mamba_block_workspace_bytes(batch, seq_len, d_model, d_inner, d_state, d_con
 
 
 def mamba_block(x, w: dict, d_state: int, d_conv: int, workspace=None, scan_variant=L.SCAN_AUTO, a_geometric=None,
-                out=None):
+                out=None, h_last=None, conv_state=None):
     """One Mamba block forward (hx_mamba_block_fwd).  x [B, L, M]; w: device tensors W_in, W_x, W_dt,
-    W_out in x.dtype and conv_w, conv_b, b_dt, A, D in fp32."""
+    W_out in x.dtype and conv_w, conv_b, b_dt, A, D in fp32.  h_last [B, E, N] fp32 and conv_state [B, 3, E]
+    (x.dtype), when given, receive the state a decode step continues from."""
     Bsz, Lq, M = x.shape
     x = x.contiguous()
     E = w["W_in"].shape[0] // 2
@@ -258,7 +259,45 @@ def mamba_block(x, w: dict, d_state: int, d_conv: int, workspace=None, scan_vari
     if a_geometric is None:
         a_geometric = check_geometric(w["A"])
     a.a_geometric = 1 if a_geometric else 0
+    if h_last is not None:
+        a.h_last = h_last.data_ptr()
+    if conv_state is not None:
+        a.conv_state = conv_state.data_ptr()
     L.check(L.lib().hx_mamba_block_fwd(C.byref(a), _stream()))
+    return y
+
+
+def mamba_block_step(x, w: dict, d_state: int, d_conv: int, h, conv_state, workspace=None, out=None):
+    """One decode step of the block (hx_mamba_block_step): x [B, M]; h [B, E, N] fp32 and conv_state [B, 3, E]
+    (x.dtype) are updated in place."""
+    Bsz, M = x.shape
+    x = x.contiguous()
+    E = w["W_in"].shape[0] // 2
+    R = w["W_dt"].shape[1]
+    y = out if out is not None else torch.empty_like(x)
+    a = L.MambaStepArgs()
+    a.batch, a.d_model, a.d_inner, a.d_state, a.d_conv, a.dt_rank = Bsz, M, E, d_state, d_conv, R
+    a.io_dtype = _dt(x)
+    a.x, a.out = x.data_ptr(), y.data_ptr()
+    for k in ("W_in", "W_x", "W_dt", "W_out"):
+        if w[k].dtype != x.dtype:
+            raise L.HxError(4, f"{k} has dtype {w[k].dtype}, expected {x.dtype}")
+        setattr(a, k, w[k].contiguous().data_ptr())
+    a.conv_w = _f32(w["conv_w"]).data_ptr()
+    if w.get("conv_b") is not None:
+        a.conv_b = _f32(w["conv_b"]).data_ptr()
+    a.b_dt = _f32(w["b_dt"]).data_ptr()
+    a.A = _f32(w["A"]).data_ptr()
+    a.Dskip = _f32(w["D"]).data_ptr()
+    if h.dtype != torch.float32 or conv_state.dtype != x.dtype:
+        raise L.HxError(4, "h must be fp32 and conv_state must have the dtype of x")
+    a.h, a.conv_state = h.data_ptr(), conv_state.data_ptr()
+    n = C.c_size_t(0)
+    L.check(L.lib().hx_mamba_step_workspace_bytes(C.byref(a), C.byref(n)))
+    if workspace is None:
+        workspace = torch.empty(n.value, dtype=torch.uint8, device=x.device)
+    a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
+    L.check(L.lib().hx_mamba_block_step(C.byref(a), _stream()))
     return y
 
 

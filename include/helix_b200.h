@@ -285,6 +285,10 @@ typedef struct hx_mamba_block_args {
     int32_t a_geometric;      /* as hx_scan_args.a_geometric */
     void **stage_events;      /* NULL, or 7 cudaEvent_t: recorded on `stream` before each of the six stages
                                  (in_proj, conv, x_proj, dt_proj, scan, out_proj) and after the last one */
+    float *h_last;            /* NULL, or [batch, d_inner, d_state] fp32: the scan's state after the last step */
+    void *conv_state;         /* NULL, or [batch, 3, d_inner] io dtype: the conv inputs of the last three steps
+                                 (oldest first, zeros where seq_len < 3); with h_last, what hx_mamba_block_step
+                                 continues from */
 } hx_mamba_block_args;
 
 HX_API hx_status hx_mamba_block_fwd(const hx_mamba_block_args *args, void *stream);
@@ -293,6 +297,31 @@ HX_API hx_status hx_mamba_block_workspace_bytes(const hx_mamba_block_args *args,
  * scan, out_proj), or 5 when the dt projection is computed inside the scan kernel (bf16, d_state 16,
  * dt_rank a multiple of 8 up to 64, and enough batch * d_inner chains for the one-lane-per-channel scan). */
 HX_API hx_status hx_mamba_block_kernel_launches(const hx_mamba_block_args *args, int32_t *launches);
+
+/* ---- single-token decode step of the block: the recurrent form of hx_mamba_block_fwd, continuing from
+ *      the state a prefill (or an earlier step) left.  x and out are [batch, d_model]; `h` and `conv_state`
+ *      are updated in place.  Five launches: in_proj, conv step, x_proj, state step (dt projection, softplus,
+ *      h <- exp(dt A) h + dt B u, y = C.h + D u, gate), out_proj.  The reference has no decode path
+ *      (its MambaBlock::forward always takes a whole sequence, crates/nn/src/lib.rs:888-906); this is the
+ *      step that follows prefill in serving. */
+typedef struct hx_mamba_step_args {
+    int32_t batch, d_model, d_inner, d_state, d_conv, dt_rank;
+    int32_t io_dtype, reserved;
+    const void *x;            /* [batch, d_model] */
+    void *out;                /* [batch, d_model] */
+    const void *W_in, *W_x, *W_dt, *W_out;   /* as hx_mamba_block_args */
+    const float *conv_w, *conv_b, *b_dt, *A, *Dskip;
+    float *h;                 /* [batch, d_inner, d_state] fp32, in/out */
+    void *conv_state;         /* [batch, 3, d_inner] io dtype, in/out */
+    void *workspace;          /* hx_mamba_step_workspace_bytes() bytes */
+    size_t workspace_bytes;
+} hx_mamba_step_args;
+HX_API hx_status hx_mamba_block_step(const hx_mamba_step_args *args, void *stream);
+HX_API hx_status hx_mamba_step_workspace_bytes(const hx_mamba_step_args *args, size_t *bytes);
+/* The conv window a decode step starts from, taken from the conv input x [batch, seq_len, d_inner]
+ * (element strides) of a prefill: conv_state[b][j] = x[b][seq_len-3+j], zeros for negative steps. */
+HX_API hx_status hx_conv_state_from_prefill(const void *x, int64_t x_batch_stride, int64_t x_row_stride, void *conv_state,
+                                     int32_t batch, int32_t seq_len, int32_t d_inner, int32_t io_dtype, void *stream);
 
 /* =============================================================================================
  * Module-level API: opaque handles over the C++ host layer (helixml_b200/csrc/helix_host.hpp), which
@@ -346,6 +375,19 @@ HX_API hx_status hx_byte_lm_forward_host(hx_module *m, const uint8_t *tokens_hos
                                   int64_t seq_len, void *stream);
 HX_API hx_status hx_byte_lm_forward_device(hx_module *m, const uint8_t *tokens_dev, void *logits_dev, int64_t batch,
                                     int64_t seq_len, void *stream);
+/* Serving with state: hx_byte_lm_prefill_device is hx_byte_lm_forward_device that also keeps, per layer, the
+ * scan's final state and the conv window; hx_byte_lm_decode_step_device then advances every sequence of that
+ * batch by one token: tokens_dev [batch] u8 in, logits_dev [batch, 256] (model dtype) out, state updated in the
+ * module.  The first step after a prefill runs as plain launches, the second is captured into a CUDA graph over
+ * the module's own step buffers and every later step replays it (1 + 6 per layer + 2 kernels in one launch);
+ * hx_byte_lm_decode_graph(m, 0) keeps plain launches.  The state belongs to the module: one decoding stream per
+ * module.  The reference's example has no decode loop (examples/ssm_byte_lm/src/main.rs:423-444 are placeholders). */
+HX_API hx_status hx_byte_lm_prefill_device(hx_module *m, const uint8_t *tokens_dev, void *logits_dev, int64_t batch,
+                                    int64_t seq_len, void *stream);
+HX_API hx_status hx_byte_lm_decode_step_device(hx_module *m, const uint8_t *tokens_dev, void *logits_dev, int64_t batch,
+                                        void *stream);
+HX_API hx_status hx_byte_lm_decode_graph(hx_module *m, int32_t enable);
+HX_API int64_t hx_byte_lm_launches_per_decode_step(const hx_module *m);
 /* Kernel launches of one forward at the shape of the most recent serving call (before any call: of a
  * forward whose blocks do not fuse the dt projection). */
 HX_API int64_t hx_byte_lm_launches_per_forward(const hx_module *m);

@@ -35,8 +35,9 @@ def test_struct_layout_matches_c():
 #include <stddef.h>
 #include "helix_b200.h"
 int main(void) {
-  printf("%zu %zu %zu %zu %zu %zu\n", sizeof(hx_scan_args), offsetof(hx_scan_args, x), offsetof(hx_scan_args, A),
-         offsetof(hx_scan_args, seq_splits), sizeof(hx_mamba_block_args), offsetof(hx_mamba_block_args, workspace));
+  printf("%zu %zu %zu %zu %zu %zu %zu %zu\n", sizeof(hx_scan_args), offsetof(hx_scan_args, x), offsetof(hx_scan_args, A),
+         offsetof(hx_scan_args, seq_splits), sizeof(hx_mamba_block_args), offsetof(hx_mamba_block_args, workspace),
+         sizeof(hx_mamba_step_args), offsetof(hx_mamba_step_args, h));
   return 0;
 }'''
     with tempfile.TemporaryDirectory() as d:
@@ -47,7 +48,7 @@ int main(void) {
         out = subprocess.run([exe], check=True, capture_output=True, text=True).stdout.split()
     got = [int(v) for v in out]
     want = [C.sizeof(L.ScanArgs), L.ScanArgs.x.offset, L.ScanArgs.A.offset, L.ScanArgs.seq_splits.offset,
-            C.sizeof(L.MambaBlockArgs), L.MambaBlockArgs.workspace.offset]
+            C.sizeof(L.MambaBlockArgs), L.MambaBlockArgs.workspace.offset, C.sizeof(L.MambaStepArgs), L.MambaStepArgs.h.offset]
     assert got == want
 
 

@@ -194,6 +194,63 @@ def test_mamba_block_bf16_direct_scan_with_fused_dt():
     assert rel_l2(outs[0], outs[1]) <= 1e-2  # fused and unfused dt projection agree
 
 
+@pytest.mark.parametrize("dtype,L0,steps", [("f32", 37, 5), ("f32", 2, 4), ("bf16", 150, 6)])
+def test_mamba_block_decode_steps_continue_prefill(dtype, L0, steps):
+    """Prefill L0 tokens keeping (h, conv window), then `steps` single-token steps: every step's output must be
+    the oracle's full-sequence output at that position (the oracle has no step function: it re-runs the block
+    over the longer sequence)."""
+    import torch
+    from helixml_b200 import ops
+    B, M, N, K = 2, 64, 16, 4
+    E = 2 * M
+    w = synth.mamba_block_weights(7, M, N, K, 2)
+    big = ("W_in", "W_x", "W_dt", "W_out")
+    bf = dtype == "bf16"
+    wq = {k: (synth.round_bf16(v) if (bf and k in big) else v) for k, v in w.items()}
+    x = synth.uniform(7, "x", (B, L0 + steps, M), -1, 1)
+    if bf:
+        x = synth.round_bf16(x)
+    dev = {k: to_dev(v, "bf16" if (bf and k in big) else None) for k, v in wq.items()}
+    td = torch.bfloat16 if bf else torch.float32
+    xd = to_dev(x, "bf16" if bf else None)
+    h = torch.zeros(B, E, N, device="cuda", dtype=torch.float32)
+    cs = torch.zeros(B, 3, E, device="cuda", dtype=td)
+    ops.mamba_block(xd[:, :L0].contiguous(), dev, N, K, h_last=h, conv_state=cs)
+    ref = cbind.mamba_block(x, wq, N, K)  # [B, L0 + steps, M]
+    outs = []
+    for s in range(steps):
+        outs.append(to_np(ops.mamba_block_step(xd[:, L0 + s].contiguous(), dev, N, K, h, cs)))
+    _status_ok()
+    got = np.stack(outs, axis=1)
+    if bf:
+        assert rel_l2(got, ref[:, L0:]) <= BF16_TOL
+    else:
+        assert fp32_tol_err(got, ref[:, L0:]) <= FP32_TOL
+    # the conv window now holds the last three conv inputs: a second prefill over everything gives the same state
+    h2 = torch.zeros_like(h)
+    cs2 = torch.zeros_like(cs)
+    ops.mamba_block(xd, dev, N, K, h_last=h2, conv_state=cs2)
+    tol = 2e-2 if bf else 1e-4
+    assert torch.allclose(cs.float(), cs2.float(), atol=tol, rtol=tol)
+    assert (h - h2).abs().max().item() <= tol * (1 + h2.abs().max().item())
+
+
+def test_mamba_block_step_rejects_bad_arguments():
+    import torch
+    from helixml_b200 import _lib, ops
+    w = synth.mamba_block_weights(7, 64, 16, 4, 2)
+    dev = {k: to_dev(v) for k, v in w.items()}
+    x = torch.zeros(2, 64, device="cuda")
+    h = torch.zeros(2, 128, 16, device="cuda")
+    cs = torch.zeros(2, 3, 128, device="cuda")
+    with pytest.raises(_lib.HxError) as e:
+        ops.mamba_block_step(x, dev, 16, 4, h, cs, workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+    assert e.value.status == 10  # InvalidInput: workspace too small
+    with pytest.raises(_lib.HxError) as e:
+        ops.mamba_block_step(x, dev, 16, 5, h, cs)
+    assert e.value.status == 2   # InvalidDimension: d_conv outside [1, 4]
+
+
 def test_exported_reference_block(golden):
     """The exported nn::MambaBlock::forward (crates/nn/src/lib.rs:888-906) is out_proj(silu(gate(x))):
     two Linear calls and a SiLU, reproduced with the GEMM's bias and SiLU epilogue."""

@@ -146,3 +146,59 @@ def test_byte_lm_bf16_matches_oracle_and_host_call():
     assert np.array_equal(lh.float().numpy(), got)
     assert _lib.device_status() == 0
     assert lm.launches_per_forward == 1 + nl * 7 + 2
+
+
+@pytest.mark.parametrize("dtype_name", ["f32", "bf16"])
+def test_byte_lm_prefill_then_decode_steps(dtype_name):
+    """Prefill L0 bytes keeping the per-layer state, then decode token by token: the logits of every step must be
+    the oracle's logits for that position of the longer sequence.  Steps 3+ replay the captured CUDA graph; a run
+    with plain launches must give the same bits."""
+    import torch
+    from helixml_b200 import _lib, nn
+    bf = dtype_name == "bf16"
+    M, nl, B, L0, steps = 64, 3, 2, 41, 6
+    emb, layers, normf = _lm_weights(9, nl, M)
+    big = ("W_in", "W_x", "W_dt", "W_out")
+    if bf:
+        layers = [{k: (synth.round_bf16(v) if k in big else v) for k, v in l.items()} for l in layers]
+        emb = synth.round_bf16(emb)
+    tok = synth.random_bytes(9, "tok", (B, L0 + steps))
+    ref = cbind.byte_lm(tok, emb, layers, normf, 16, 4)  # [B, L0 + steps, 256]
+    td = torch.bfloat16 if bf else torch.float32
+    tok_d = torch.from_numpy(tok).cuda()
+    runs = []
+    for graph in (True, False):
+        lm = nn.ByteLM(nl, M, dtype=nn.BF16 if bf else nn.F32)
+        lm.load_weights(emb, layers, normf)
+        lm.decode_graph(graph)
+        pre = torch.empty(B, L0, 256, device="cuda", dtype=td)
+        lm.prefill_device(tok_d[:, :L0].contiguous().data_ptr(), pre.data_ptr(), B, L0)
+        outs = []
+        for s in range(steps):
+            t1 = tok_d[:, L0 + s].contiguous()
+            lg = torch.empty(B, 256, device="cuda", dtype=td)
+            lm.decode_step_device(t1.data_ptr(), lg.data_ptr(), B)
+            outs.append(lg.float().cpu().numpy())
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        got = np.stack(outs, axis=1)
+        if bf:
+            assert rel_l2(pre.float().cpu().numpy(), ref[:, :L0]) <= BF16_TOL
+            assert rel_l2(got, ref[:, L0:]) <= BF16_TOL
+        else:
+            assert fp32_tol_err(pre.cpu().numpy(), ref[:, :L0]) <= FP32_TOL
+            assert fp32_tol_err(got, ref[:, L0:]) <= FP32_TOL
+        assert lm.launches_per_decode_step == 1 + nl * 6 + 2
+        runs.append(got)
+    assert np.array_equal(runs[0], runs[1])  # graph replay and plain launches agree bit for bit
+
+
+def test_byte_lm_decode_without_prefill_is_an_error():
+    import torch
+    from helixml_b200 import _lib, nn
+    lm = nn.ByteLM(1, 64, dtype=nn.F32)
+    t = torch.zeros(2, dtype=torch.uint8, device="cuda")
+    lg = torch.empty(2, 256, device="cuda")
+    with pytest.raises(_lib.HxError) as e:
+        lm.decode_step_device(t.data_ptr(), lg.data_ptr(), 2)
+    assert e.value.status == 10
