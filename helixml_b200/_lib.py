@@ -60,6 +60,11 @@ class MambaBlockArgs(C.Structure):
     ]
 
 
+class CheckpointMeta(C.Structure):
+    _fields_ = [("epoch", C.c_uint64), ("step", C.c_uint64), ("training_loss", C.c_double), ("validation_loss", C.c_double),
+                ("learning_rate", C.c_double), ("timestamp_secs", C.c_uint64)]
+
+
 class MambaStepArgs(C.Structure):
     _fields_ = [
         ("batch", C.c_int32), ("d_model", C.c_int32), ("d_inner", C.c_int32), ("d_state", C.c_int32),
@@ -139,6 +144,15 @@ _PROTOS = {
     "hx_byte_lm_forward_host": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "hx_byte_lm_forward_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "hx_byte_lm_launches_per_forward": (C.c_int64, [C.c_void_p]),
+    "hx_module_save_checkpoint": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(CheckpointMeta)]),
+    "hx_module_load_checkpoint": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(CheckpointMeta)]),
+    "hx_checkpoint_write": (C.c_int, [C.c_char_p, C.POINTER(CheckpointMeta), C.c_int32, C.POINTER(C.c_void_p),
+                                      C.POINTER(C.c_void_p), C.POINTER(C.c_int32)]),
+    "hx_checkpoint_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "hx_checkpoint_num_tensors": (C.c_int32, [C.c_void_p]),
+    "hx_checkpoint_meta_get": (C.c_int, [C.c_void_p, C.POINTER(CheckpointMeta)]),
+    "hx_checkpoint_tensor": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int32)]),
+    "hx_checkpoint_close": (None, [C.c_void_p]),
     "hx_byte_lm_prefill_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "hx_byte_lm_decode_step_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "hx_byte_lm_decode_graph": (C.c_int, [C.c_void_p, C.c_int32]),

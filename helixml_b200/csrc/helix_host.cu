@@ -829,8 +829,6 @@ std::vector<DeviceTensor *> ByteLM::parameters_mut() {
 }  // namespace helix
 
 // ============================================================================================ C handles
-struct hx_tensor { helix::DeviceTensor t; };
-struct hx_module { std::unique_ptr<helix::Module> m; };
 
 namespace {
 hx_status fail_from(const helix::TensorError &e) { return hx::fail(e.code, "%s", e.message.c_str()); }

@@ -277,3 +277,7 @@ class ByteLM : public Module {
 void manual_seed(uint64_t seed);
 
 }  // namespace helix
+
+// The opaque handles of the C ABI (include/helix_b200.h) wrap these.
+struct hx_tensor { helix::DeviceTensor t; };
+struct hx_module { std::unique_ptr<helix::Module> m; };

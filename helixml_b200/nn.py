@@ -114,6 +114,21 @@ class Module:
             p.copy_from(a)
         L.check(L.lib().hx_module_parameters_updated(self._h))
 
+    def save_checkpoint(self, path: str, epoch=0, step=0, training_loss=0.0, validation_loss=0.0, learning_rate=0.0,
+                        timestamp_secs=0) -> None:
+        """CheckpointableModule::checkpoint + CheckpointManager's file layout (crates/nn/src/lib.rs:50-52,
+        crates/training/src/checkpoint.rs:136-170): parameters() as f32 CpuTensors."""
+        m = L.CheckpointMeta()
+        m.epoch, m.step, m.timestamp_secs = epoch, step, timestamp_secs
+        m.training_loss, m.validation_loss, m.learning_rate = training_loss, validation_loss, learning_rate
+        L.check(L.lib().hx_module_save_checkpoint(self._h, path.encode(), C.byref(m)))
+
+    def load_checkpoint(self, path: str) -> dict:
+        """CheckpointableModule::restore from a file in the reference's layout; returns the metadata."""
+        m = L.CheckpointMeta()
+        L.check(L.lib().hx_module_load_checkpoint(self._h, path.encode(), C.byref(m)))
+        return {k: getattr(m, k) for k, _ in L.CheckpointMeta._fields_}
+
     @property
     def name(self) -> str:
         return L.lib().hx_module_name(self._h).decode()

@@ -406,6 +406,32 @@ HX_API hx_status hx_module_parameters_updated(hx_module *m);
 HX_API const char *hx_module_name(const hx_module *m);
 HX_API void hx_module_free(hx_module *m);
 
+/* ---- checkpoints in the reference's on-disk layout (crates/training/src/checkpoint.rs:136-197): a u32
+ *      big-endian length, the CheckpointData JSON, then bincode of Vec<CpuTensor> (f32 storage, row-major).
+ *      hx_module_save_checkpoint is CheckpointableModule::checkpoint + save_checkpoint_to_file (parameters in
+ *      parameters() order, bf16 widened to f32); hx_module_load_checkpoint is load_checkpoint_from_file +
+ *      CheckpointableModule::restore (crates/nn/src/lib.rs:42-56): a different parameter count gives
+ *      HX_ERR_INVALID_CHECKPOINT, a different shape HX_ERR_SHAPE_MISMATCH, a malformed file
+ *      HX_ERR_SERIALIZATION, and the module is unchanged.  The hx_checkpoint_* calls work on host arrays only
+ *      (no GPU needed): the same file format for callers that hold their tensors on the host. */
+typedef struct hx_checkpoint_meta {
+    uint64_t epoch, step;
+    double training_loss, validation_loss, learning_rate;
+    uint64_t timestamp_secs;  /* seconds since the Unix epoch */
+} hx_checkpoint_meta;
+typedef struct hx_checkpoint hx_checkpoint;
+HX_API hx_status hx_module_save_checkpoint(const hx_module *m, const char *path, const hx_checkpoint_meta *meta);
+HX_API hx_status hx_module_load_checkpoint(hx_module *m, const char *path, hx_checkpoint_meta *meta_out);
+HX_API hx_status hx_checkpoint_write(const char *path, const hx_checkpoint_meta *meta, int32_t n_tensors,
+                              const float *const *data, const int64_t *const *dims, const int32_t *ndims);
+HX_API hx_status hx_checkpoint_open(const char *path, hx_checkpoint **out);
+HX_API int32_t hx_checkpoint_num_tensors(const hx_checkpoint *ck);
+HX_API hx_status hx_checkpoint_meta_get(const hx_checkpoint *ck, hx_checkpoint_meta *meta);
+/* data and dims point into the checkpoint object and stay valid until hx_checkpoint_close */
+HX_API hx_status hx_checkpoint_tensor(const hx_checkpoint *ck, int32_t index, const float **data, const int64_t **dims,
+                               int32_t *ndim);
+HX_API void hx_checkpoint_close(hx_checkpoint *ck);
+
 #ifdef __cplusplus
 }
 #endif

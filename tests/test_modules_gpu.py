@@ -202,3 +202,35 @@ def test_byte_lm_decode_without_prefill_is_an_error():
     with pytest.raises(_lib.HxError) as e:
         lm.decode_step_device(t.data_ptr(), lg.data_ptr(), 2)
     assert e.value.status == 10
+
+
+def test_module_checkpoint_round_trip(tmp_path):
+    """Save a block's parameters in the reference's checkpoint layout, restore them into a freshly initialised
+    block: same parameters, same forward; a checkpoint of another architecture is refused and changes nothing."""
+    from helixml_b200 import _lib, checkpoint, nn
+    nn.manual_seed(11)
+    a = nn.MambaBlock(64, 16, 4, 2, dtype=nn.BF16)
+    nn.manual_seed(12)
+    b = nn.MambaBlock(64, 16, 4, 2, dtype=nn.BF16)
+    x = nn.Tensor.from_numpy(synth.round_bf16(synth.normal(11, "x", (2, 40, 64))), dtype=nn.BF16)
+    ya = a(x).numpy()
+    assert not np.array_equal(ya, b(x).numpy())
+    p = str(tmp_path / "checkpoint_epoch_4.pt")
+    a.save_checkpoint(p, epoch=4, step=77, training_loss=1.25, learning_rate=3e-4, timestamp_secs=1700000000)
+    meta, arrays = checkpoint.read(p)  # the host-side reader sees the same file
+    assert meta["epoch"] == 4 and meta["step"] == 77 and len(arrays) == len(a.parameters())
+    for t, arr in zip(a.parameters(), arrays):
+        assert tuple(arr.shape) == tuple(t.shape) and np.array_equal(t.numpy(), arr)
+    got = b.load_checkpoint(p)
+    assert got["epoch"] == 4 and got["training_loss"] == 1.25
+    assert np.array_equal(b(x).numpy(), ya)
+    other = nn.MambaBlock(32, 16, 4, 2, dtype=nn.BF16)
+    before = [t.numpy() for t in other.parameters()]
+    with pytest.raises(_lib.HxError) as e:
+        other.load_checkpoint(p)
+    assert e.value.variant == "ShapeMismatch"
+    lin = nn.Linear(8, 8)
+    with pytest.raises(_lib.HxError) as e:
+        lin.load_checkpoint(p)
+    assert e.value.variant == "InvalidCheckpoint"
+    assert all(np.array_equal(t.numpy(), v) for t, v in zip(other.parameters(), before))
