@@ -331,6 +331,33 @@ embedding_kernel(const uint8_t *tok, const TE *emb, TO *out, int64_t n, int d) {
     st_f32(out + i, ld_f32(emb + (int64_t)tok[r] * d + j));
 }
 
+// bf16 table, rows of a multiple of 8 elements: a thread moves 8 elements (one 16-byte load of the table row,
+// 16 or 32 bytes stored) and reads its token once
+template <typename TO>
+__global__ void __launch_bounds__(256)
+embedding_vec_kernel(const uint8_t *__restrict__ tok, const __nv_bfloat16 *__restrict__ emb, TO *__restrict__ out, int64_t n, int d) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // group of 8 elements
+    const int gpr = d >> 3;
+    if (i >= n * gpr) return;
+    const int64_t r = i / gpr;
+    const int j = (int)(i - r * gpr) << 3;
+    const uint4 v = *reinterpret_cast<const uint4 *>(emb + (int64_t)tok[r] * d + j);
+    TO *o = out + r * d + j;
+    if constexpr (sizeof(TO) == 2) {
+        *reinterpret_cast<uint4 *>(o) = v;
+    } else {
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        float f[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            f[2 * e] = __uint_as_float(w[e] << 16);
+            f[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+        }
+        *reinterpret_cast<float4 *>(o) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4 *>(o + 4) = make_float4(f[4], f[5], f[6], f[7]);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) silu_kernel(const T *x, T *y, int64_t n) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -437,6 +464,13 @@ hx_status hx_embedding_fwd(const uint8_t *tokens, const void *emb, int32_t emb_d
     const int64_t total = n_tokens * d_model;
     dim3 grid((unsigned)((total + 255) / 256)), block(256);
     const bool eb = emb_dtype == HX_BF16, ob = out_dtype == HX_BF16;
+    if (eb && d_model % 8 == 0 && (reinterpret_cast<uintptr_t>(emb) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        const int64_t groups = n_tokens * (d_model / 8);
+        dim3 g8((unsigned)((groups + 255) / 256));
+        if (ob) embedding_vec_kernel<<<g8, block, 0, st>>>(tokens, static_cast<const __nv_bfloat16 *>(emb), static_cast<__nv_bfloat16 *>(out), n_tokens, d_model);
+        else embedding_vec_kernel<<<g8, block, 0, st>>>(tokens, static_cast<const __nv_bfloat16 *>(emb), static_cast<float *>(out), n_tokens, d_model);
+        return hx::check_launch("embedding_vec_kernel");
+    }
     if (eb && ob) embedding_kernel<<<grid, block, 0, st>>>(tokens, static_cast<const __nv_bfloat16 *>(emb), static_cast<__nv_bfloat16 *>(out), n_tokens, d_model);
     else if (eb) embedding_kernel<<<grid, block, 0, st>>>(tokens, static_cast<const __nv_bfloat16 *>(emb), static_cast<float *>(out), n_tokens, d_model);
     else if (ob) embedding_kernel<<<grid, block, 0, st>>>(tokens, static_cast<const float *>(emb), static_cast<__nv_bfloat16 *>(out), n_tokens, d_model);

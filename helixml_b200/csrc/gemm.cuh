@@ -14,6 +14,11 @@ template <int EPI> __device__ __forceinline__ float apply_epilogue(float v) {
     else return v;
 }
 
+// The few-rows kernel (gemm_skinny.cu): M <= 64, K a multiple of 32, operands 16-byte aligned with row strides
+// that are multiples of 8 elements.
+hx_status launch_skinny(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias, void *C, int64_t ldc,
+                        int c_dtype, int M, int N, int K, int epi, cudaStream_t st);
+
 hx_status validate_gemm(const void *A, int64_t lda, const void *W, int64_t ldw, void *C, int64_t ldc, int M, int N, int K);
 
 }  // namespace gemm

@@ -343,6 +343,9 @@ extern "C" hx_status hx_gemm_bf16(const void *A, int64_t lda, const void *W, int
                "hx_gemm_bf16 needs K, lda and ldw to be multiples of 8 (got %d, %lld, %lld)", K, (long long)lda,
                (long long)ldw);
     cudaStream_t st = (cudaStream_t)stream;
+    // a handful of rows (a decode step): stream the weights through many small CTAs instead of one 128-row tile
+    if (M <= 64 && K % 32 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0)
+        return launch_skinny(A, lda, W, ldw, bias, C, ldc, c_dtype, M, N, K, epilogue, st);
     const int BN = N > 128 ? 256 : 128;
     CUtensorMap ma, mw;
     const uint64_t dims_a[2] = {(uint64_t)K, (uint64_t)M}, dims_w[2] = {(uint64_t)K, (uint64_t)N};

@@ -61,10 +61,16 @@ s4_diag_kernel(const T *u, const float *A, const float *Bp, const float *Cp, con
     float2 h[kNSL / 2];
 #pragma unroll
     for (int j = 0; j < kNSL / 2; ++j) h[j] = make_float2(0.f, 0.f);
-    for (int t = t0; t < t1; t += TU) {
-        float ub[TU];
+    // the loads of the next TU steps are issued before the arithmetic of the current ones: all warps of a CTA walk
+    // in step, so without this every batch would wait out a full memory round trip
+    auto fetch = [&](int t, float *dst) {
 #pragma unroll
-        for (int e = 0; e < TU; ++e) ub[e] = (t + e < t1 && chan_ok) ? ld_f32(up + (int64_t)(t + e) * D) : 0.f;
+        for (int e = 0; e < TU; ++e) dst[e] = (t + e < t1 && chan_ok) ? ld_f32(up + (int64_t)(t + e) * D) : 0.f;
+    };
+    float ub[TU], un[TU];
+    fetch(t0, ub);
+    for (int t = t0; t < t1; t += TU) {
+        fetch(t + TU, un);
 #pragma unroll
         for (int e = 0; e < TU; ++e) {
             if (t + e < t1) {
@@ -73,6 +79,8 @@ s4_diag_kernel(const T *u, const float *A, const float *Bp, const float *Cp, con
                 for (int j = 0; j < kNSL / 2; ++j) h[j] = fma2(a[j], h[j], u2);
             }
         }
+#pragma unroll
+        for (int e = 0; e < TU; ++e) ub[e] = un[e];
     }
 #pragma unroll
     for (int j = 0; j < kNSL / 2; ++j) {
@@ -89,10 +97,9 @@ s4_diag_kernel(const T *u, const float *A, const float *Bp, const float *Cp, con
             h[j] = fma2(aT[j], h[j], make_float2(ends[gp][lane][2 * j], ends[gp][lane][2 * j + 1]));
     }
     // ---- pass 2: the real run
+    fetch(t0, ub);
     for (int t = t0; t < t1; t += TU) {
-        float ub[TU];
-#pragma unroll
-        for (int e = 0; e < TU; ++e) ub[e] = (t + e < t1 && chan_ok) ? ld_f32(up + (int64_t)(t + e) * D) : 0.f;
+        fetch(t + TU, un);
 #pragma unroll
         for (int e = 0; e < TU; ++e) {
             if (t + e < t1) {  // warp-uniform
@@ -109,6 +116,8 @@ s4_diag_kernel(const T *u, const float *A, const float *Bp, const float *Cp, con
                 if (chan_ok && q == (e % LPC)) st_f32(yp + (int64_t)(t + e) * D, s + dsk * ub[e]);
             }
         }
+#pragma unroll
+        for (int e = 0; e < TU; ++e) ub[e] = un[e];
     }
 }
 

@@ -6,7 +6,8 @@
     python -m helixml_b200.kernel_bench s4
     python -m helixml_b200.kernel_bench decode
 
-Each case runs 3 warm-up calls, then 10 timed calls between two events on torch's current stream."""
+Each case runs 3 warm-up calls, then 10 timed calls between two events on torch's current stream, queued behind a
+2 ms spin kernel so that the host's call rate does not limit the figure."""
 from __future__ import annotations
 
 import sys
@@ -24,6 +25,9 @@ def _time(fn, reps=10):
         fn()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # keep the GPU busy for ~2 ms while the host queues the timed launches, so that a kernel of a few tens of
+    # microseconds is timed back to back and not at the rate the host can issue calls
+    torch.cuda._sleep(4_000_000)
     e0.record()
     for _ in range(reps):
         fn()

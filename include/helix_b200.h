@@ -234,7 +234,10 @@ HX_API size_t hx_s4_ref_workspace_bytes(int32_t seq_len, int32_t d_state);
  *      (crates/nn/src/lib.rs:120-134) and the orphan cuBLAS sgemm call
  *      (crates/backend-cuda/src/ops_impl.rs:222-236).
  *      lda / ldw / ldc are row strides in elements; K, lda, ldw must be multiples of 8 and the
- *      base pointers 16-byte aligned (TMA rules).  epilogue: 0 none, 1 SiLU, 2 softplus. */
+ *      base pointers 16-byte aligned (TMA rules).  epilogue: 0 none, 1 SiLU, 2 softplus.
+ *      With M <= 64 and K a multiple of 32 (a decode step) the work goes to a kernel that streams W through
+ *      N/8 CTAs (16 warps each, K split between them) with warp-level tensor-core instructions instead of one
+ *      128-row tcgen05 tile. */
 HX_API hx_status hx_gemm_bf16(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias,
                        void *C, int64_t ldc, int32_t c_dtype, int32_t M, int32_t N, int32_t K,
                        int32_t epilogue, void *stream);

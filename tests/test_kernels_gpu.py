@@ -101,6 +101,12 @@ def test_embedding_and_silu():
     tok = synth.random_bytes(53, "tok", (3, 21))
     out = ops.embedding(to_dev(tok), to_dev(emb))
     assert np.array_equal(to_np(out), emb[tok])
+    # bf16 table: the 8-elements-per-thread path (fp32 and bf16 out) and the scalar one (row length not a multiple of 8)
+    for d in (48, 44):
+        embq = synth.round_bf16(synth.normal(53, "embq", (256, d), 0, 0.02))
+        for od in (torch.float32, torch.bfloat16):
+            got = ops.embedding(to_dev(tok), to_dev(embq, "bf16"), out_dtype=od)
+            assert np.array_equal(to_np(got), embq[tok])
     x = synth.normal(53, "x", (1000,))
     assert fp32_tol_err(to_np(ops.silu(to_dev(x))), cbind.silu(x)) <= FP32_TOL
 
@@ -148,6 +154,28 @@ def test_gemm_tcgen05_bias_epilogue_and_strides():
     with pytest.raises(_lib.HxError) as e:
         ops.gemm(to_dev(wide, "bf16")[:, :44], to_dev(w, "bf16")[:, :44].contiguous())
     assert e.value.variant == "UnsupportedOperation"
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8, 32), (16, 3072, 768), (17, 80, 1536), (32, 768, 1536), (33, 50, 64), (64, 256, 768),
+                                   (7, 7, 96), (32, 3072, 768)])
+def test_gemm_few_rows_bf16(M, N, K):
+    """M <= 64 and K a multiple of 32 go to the weight-streaming kernel (the decode-step shapes)."""
+    import torch
+    from helixml_b200 import _lib, ops
+    a = synth.round_bf16(synth.normal(64, "a", (M, K)))
+    w = synth.round_bf16(synth.normal(64, "w", (N, K), 0, 0.05))
+    b = synth.normal(64, "b", (N,))
+    ref = a.astype(np.float64) @ w.astype(np.float64).T
+    got32 = ops.gemm(to_dev(a, "bf16"), to_dev(w, "bf16"), out_dtype=torch.float32)
+    assert fp32_tol_err(to_np(got32), ref) <= FP32_TOL
+    got16 = ops.gemm(to_dev(a, "bf16"), to_dev(w, "bf16"))
+    assert rel_l2(to_np(got16), ref) <= 5e-3
+    # bias + SiLU epilogue, A as a column slice of a wider matrix (lda > K)
+    wide = synth.round_bf16(synth.normal(64, "wide", (M, K + 40)))
+    lin = wide[:, :K].astype(np.float64) @ w.astype(np.float64).T + b
+    got = ops.gemm(to_dev(wide, "bf16")[:, :K], to_dev(w, "bf16"), to_dev(b), out_dtype=torch.float32, epilogue=_lib.EPI_SILU)
+    assert fp32_tol_err(to_np(got), lin / (1 + np.exp(-lin))) <= FP32_TOL
+    _status_ok()
 
 
 # ------------------------------------------------------------------ the whole block
