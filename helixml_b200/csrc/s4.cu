@@ -67,20 +67,29 @@ s4_diag_kernel(const T *u, const float *A, const float *Bp, const float *Cp, con
 #pragma unroll
         for (int e = 0; e < TU; ++e) dst[e] = (t + e < t1 && chan_ok) ? ld_f32(up + (int64_t)(t + e) * D) : 0.f;
     };
+    // Full batches of TU steps run without a per-step guard (a branch per step would keep the compiler from
+    // overlapping the dependent chains of neighbouring steps); the ragged end of the segment runs guarded.
     float ub[TU], un[TU];
     fetch(t0, ub);
-    for (int t = t0; t < t1; t += TU) {
+    int t = t0;
+    for (; t + TU <= t1; t += TU) {
         fetch(t + TU, un);
 #pragma unroll
         for (int e = 0; e < TU; ++e) {
-            if (t + e < t1) {
-                const float2 u2 = splat2(ub[e]);
+            const float2 u2 = splat2(ub[e]);
 #pragma unroll
-                for (int j = 0; j < kNSL / 2; ++j) h[j] = fma2(a[j], h[j], u2);
-            }
+            for (int j = 0; j < kNSL / 2; ++j) h[j] = fma2(a[j], h[j], u2);
         }
 #pragma unroll
         for (int e = 0; e < TU; ++e) ub[e] = un[e];
+    }
+#pragma unroll
+    for (int e = 0; e < TU; ++e) {
+        if (t + e < t1) {  // warp-uniform
+            const float2 u2 = splat2(ub[e]);
+#pragma unroll
+            for (int j = 0; j < kNSL / 2; ++j) h[j] = fma2(a[j], h[j], u2);
+        }
     }
 #pragma unroll
     for (int j = 0; j < kNSL / 2; ++j) {
@@ -97,27 +106,45 @@ s4_diag_kernel(const T *u, const float *A, const float *Bp, const float *Cp, con
             h[j] = fma2(aT[j], h[j], make_float2(ends[gp][lane][2 * j], ends[gp][lane][2 * j + 1]));
     }
     // ---- pass 2: the real run
-    fetch(t0, ub);
-    for (int t = t0; t < t1; t += TU) {
-        fetch(t + TU, un);
+    auto step_sum = [&](float uv) {
+        const float2 u2 = splat2(uv);
+        float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int e = 0; e < TU; ++e) {
-            if (t + e < t1) {  // warp-uniform
-                const float2 u2 = splat2(ub[e]);
-                float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-                for (int j = 0; j < kNSL / 2; ++j) {
-                    h[j] = fma2(a[j], h[j], u2);
-                    acc = fma2(k[j], h[j], acc);
-                }
-                float s = acc.x + acc.y;
-#pragma unroll
-                for (int o = LPC / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                if (chan_ok && q == (e % LPC)) st_f32(yp + (int64_t)(t + e) * D, s + dsk * ub[e]);
-            }
+        for (int j = 0; j < kNSL / 2; j += 2) {
+            h[j] = fma2(a[j], h[j], u2);
+            h[j + 1] = fma2(a[j + 1], h[j + 1], u2);
+            acc0 = fma2(k[j], h[j], acc0);
+            acc1 = fma2(k[j + 1], h[j + 1], acc1);
         }
+        return (acc0.x + acc0.y) + (acc1.x + acc1.y);
+    };
+    fetch(t0, ub);
+    t = t0;
+    for (; t + TU <= t1; t += TU) {
+        fetch(t + TU, un);
+        float sv[TU];
+#pragma unroll
+        for (int e = 0; e < TU; ++e) sv[e] = step_sum(ub[e]);
+        // the partial sums of all TU steps cross the lanes together, then lane q of a channel stores the steps
+        // e = q (mod LPC)
+#pragma unroll
+        for (int o = LPC / 2; o > 0; o >>= 1)
+#pragma unroll
+            for (int e = 0; e < TU; ++e) sv[e] += __shfl_xor_sync(0xffffffffu, sv[e], o);
+#pragma unroll
+        for (int e = 0; e < TU; ++e)
+            if (chan_ok && q == (e % LPC)) st_f32(yp + (int64_t)(t + e) * D, sv[e] + dsk * ub[e]);
 #pragma unroll
         for (int e = 0; e < TU; ++e) ub[e] = un[e];
+    }
+#pragma unroll
+    for (int e = 0; e < TU; ++e) {
+        if (t + e < t1) {  // warp-uniform
+            float sv = step_sum(ub[e]);
+#pragma unroll
+            for (int o = LPC / 2; o > 0; o >>= 1) sv += __shfl_xor_sync(0xffffffffu, sv, o);
+            if (chan_ok && q == (e % LPC)) st_f32(yp + (int64_t)(t + e) * D, sv + dsk * ub[e]);
+        }
     }
 }
 
