@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libhelix_b200.so")
 HX_OK = 0
 HX_F32, HX_BF16, HX_U8 = 0, 1, 2
 SCAN_AUTO, SCAN_SIMPLE, SCAN_TILED, SCAN_SEQSPLIT, SCAN_DIRECT = 0, 1, 2, 3, 4
-EPI_NONE, EPI_SILU, EPI_SOFTPLUS = 0, 1, 2
+EPI_NONE, EPI_SILU, EPI_SOFTPLUS, EPI_SILU_FAST = 0, 1, 2, 3
 
 STATUS_NAMES = ["Ok", "ShapeMismatch", "InvalidDimension", "DeviceMismatch", "DTypeMismatch", "UnsupportedOperation",
                 "AllocationFailed", "BackendError", "SerializationError", "InvalidCheckpoint", "InvalidInput"]
@@ -44,7 +44,7 @@ class ScanArgs(C.Structure):
         ("seq_splits", C.c_int32), ("a_geometric", C.c_int32), ("lanes_per_channel", C.c_int32),
         ("reserved", C.c_int32),
         ("dt_low", C.c_void_p), ("W_dt", C.c_void_p), ("dt_low_batch_stride", C.c_int64), ("dt_low_row_stride", C.c_int64),
-        ("dt_rank", C.c_int32), ("reserved2", C.c_int32),
+        ("dt_rank", C.c_int32), ("z_is_gate", C.c_int32),
     ]
 
 
@@ -109,6 +109,8 @@ _PROTOS = {
     "hx_s4_ref_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "hx_gemm_bf16": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "hx_gemm_bf16_cols": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
+                                    C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "hx_gemm_simt": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "hx_rmsnorm_fwd": (C.c_int, [C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int64,

@@ -6,18 +6,19 @@
 namespace hx {
 namespace gemm {
 
-enum : int { kEpiNone = 0, kEpiSilu = 1, kEpiSoftplus = 2 };
+enum : int { kEpiNone = 0, kEpiSilu = 1, kEpiSoftplus = 2, kEpiSiluFast = 3 };
 
 template <int EPI> __device__ __forceinline__ float apply_epilogue(float v) {
     if constexpr (EPI == kEpiSilu) return silu_acc(v);
     else if constexpr (EPI == kEpiSoftplus) return softplus_acc(v);
+    else if constexpr (EPI == kEpiSiluFast) return silu_fast(v);
     else return v;
 }
 
 // The few-rows kernel (gemm_skinny.cu): M <= 64, K a multiple of 32, operands 16-byte aligned with row strides
 // that are multiples of 8 elements.
 hx_status launch_skinny(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias, void *C, int64_t ldc,
-                        int c_dtype, int M, int N, int K, int epi, cudaStream_t st);
+                        int c_dtype, int M, int N, int K, int epi, int epi_col0, cudaStream_t st);
 
 hx_status validate_gemm(const void *A, int64_t lda, const void *W, int64_t ldw, void *C, int64_t ldc, int M, int N, int K);
 

@@ -21,7 +21,7 @@ constexpr int kSkinnyWarps = 16;
 template <int MT, typename TC, int EPI>
 __global__ void __launch_bounds__(kSkinnyWarps * 32)
 gemm_skinny_kernel(const __nv_bfloat16 *__restrict__ A, int64_t lda, const __nv_bfloat16 *__restrict__ W, int64_t ldw,
-                   const float *__restrict__ bias, TC *__restrict__ C, int64_t ldc, int M, int N, int K) {
+                   const float *__restrict__ bias, TC *__restrict__ C, int64_t ldc, int M, int N, int K, int epi_col0) {
     __shared__ float partial[kSkinnyWarps * MT * 128];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, tid = lane & 3;
@@ -91,20 +91,21 @@ gemm_skinny_kernel(const __nv_bfloat16 *__restrict__ A, int64_t lda, const __nv_
     const int c = n0 + 2 * (ln & 3) + (i & 1);
     if (r < M && c < N) {
         if (bias) v += bias[c];
-        st_f32(C + (int64_t)r * ldc + c, apply_epilogue<EPI>(v));
+        st_f32(C + (int64_t)r * ldc + c, c >= epi_col0 ? apply_epilogue<EPI>(v) : v);
     }
 }
 
 template <int MT, typename TC>
 static hx_status launch_skinny_epi(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias, void *C, int64_t ldc,
-                                   int M, int N, int K, int epi, cudaStream_t st) {
+                                   int M, int N, int K, int epi, int epi_col0, cudaStream_t st) {
     const dim3 grid((unsigned)((N + 7) / 8)), block(kSkinnyWarps * 32);
     auto a = static_cast<const __nv_bfloat16 *>(A), w = static_cast<const __nv_bfloat16 *>(W);
     auto c = static_cast<TC *>(C);
     switch (epi) {
-        case kEpiNone: gemm_skinny_kernel<MT, TC, kEpiNone><<<grid, block, 0, st>>>(a, lda, w, ldw, bias, c, ldc, M, N, K); break;
-        case kEpiSilu: gemm_skinny_kernel<MT, TC, kEpiSilu><<<grid, block, 0, st>>>(a, lda, w, ldw, bias, c, ldc, M, N, K); break;
-        case kEpiSoftplus: gemm_skinny_kernel<MT, TC, kEpiSoftplus><<<grid, block, 0, st>>>(a, lda, w, ldw, bias, c, ldc, M, N, K); break;
+        case kEpiNone: gemm_skinny_kernel<MT, TC, kEpiNone><<<grid, block, 0, st>>>(a, lda, w, ldw, bias, c, ldc, M, N, K, epi_col0); break;
+        case kEpiSilu: gemm_skinny_kernel<MT, TC, kEpiSilu><<<grid, block, 0, st>>>(a, lda, w, ldw, bias, c, ldc, M, N, K, epi_col0); break;
+        case kEpiSoftplus: gemm_skinny_kernel<MT, TC, kEpiSoftplus><<<grid, block, 0, st>>>(a, lda, w, ldw, bias, c, ldc, M, N, K, epi_col0); break;
+        case kEpiSiluFast: gemm_skinny_kernel<MT, TC, kEpiSiluFast><<<grid, block, 0, st>>>(a, lda, w, ldw, bias, c, ldc, M, N, K, epi_col0); break;
         default: return fail(HX_ERR_INVALID_INPUT, "unknown epilogue %d", epi);
     }
     return check_launch("gemm_skinny_kernel");
@@ -112,10 +113,10 @@ static hx_status launch_skinny_epi(const void *A, int64_t lda, const void *W, in
 
 // M <= 64, K a multiple of 32, lda / ldw multiples of 8 and 16-byte aligned bases (checked by the caller).
 hx_status launch_skinny(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias, void *C, int64_t ldc,
-                        int c_dtype, int M, int N, int K, int epi, cudaStream_t st) {
+                        int c_dtype, int M, int N, int K, int epi, int epi_col0, cudaStream_t st) {
 #define HX_SKINNY(MT)                                                                                                   \
-    return c_dtype == HX_BF16 ? launch_skinny_epi<MT, __nv_bfloat16>(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, st)    \
-                              : launch_skinny_epi<MT, float>(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, st)
+    return c_dtype == HX_BF16 ? launch_skinny_epi<MT, __nv_bfloat16>(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, epi_col0, st)    \
+                              : launch_skinny_epi<MT, float>(A, lda, W, ldw, bias, C, ldc, M, N, K, epi, epi_col0, st)
     if (M <= 16) { HX_SKINNY(1); }
     if (M <= 32) { HX_SKINNY(2); }
     HX_SKINNY(4);

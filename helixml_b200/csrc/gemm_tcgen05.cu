@@ -91,7 +91,7 @@ template <int BN> struct TcCfg {
 template <int BN, typename TC, int EPI>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
-               const __grid_constant__ CUtensorMap tm_c, const float *bias, TC *C, int64_t ldc, int M, int N, int K,
+               const __grid_constant__ CUtensorMap tm_c, const float *bias, TC *C, int64_t ldc, int M, int N, int K, int epi_col0,
                int vec_ok) {
     using Cfg = TcCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
@@ -215,12 +215,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
                     for (int half = 0; half < HALVES; ++half) {
                         float v[32];
+                        const bool act = nb + half * 32 >= epi_col0;  // warp-uniform: epi_col0 is a multiple of 32
 #pragma unroll
                         for (int j = 0; j < 32; ++j) {
                             float x = __uint_as_float(r[half][j]);
                             const int n = nb + half * 32 + j;
                             if (bias) x += (n < N) ? __ldg(bias + n) : 0.f;
-                            v[j] = apply_epilogue<EPI>(x);
+                            v[j] = x;
+                        }
+                        if (EPI != kEpiNone && act) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = apply_epilogue<EPI>(v[j]);
                         }
                         // 16-byte pieces of this lane's row, XOR-swizzled with the row index like the TMA box
                         if constexpr (sizeof(TC) == 2) {
@@ -265,7 +270,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         float x = __uint_as_float(r[j]);
                         if (nb + j < N) {
                             if (bias) x += __ldg(bias + nb + j);
-                            st_f32(crow + nb + j, apply_epilogue<EPI>(x));
+                            st_f32(crow + nb + j, nb + j >= epi_col0 ? apply_epilogue<EPI>(x) : x);
                         }
                     }
                 }
@@ -290,7 +295,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 
 template <int BN, typename TC, int EPI>
 static hx_status launch_tc_inst(const CUtensorMap &ma, const CUtensorMap &mw, const CUtensorMap &mc, const float *bias, void *C,
-                                int64_t ldc, int M, int N, int K, int vec_ok, cudaStream_t st) {
+                                int64_t ldc, int M, int N, int K, int epi_col0, int vec_ok, cudaStream_t st) {
     using Cfg = TcCfg<BN>;
     auto kern = gemm_tc_kernel<BN, TC, EPI>;
     static bool attr_set[64] = {false};
@@ -302,17 +307,18 @@ static hx_status launch_tc_inst(const CUtensorMap &ma, const CUtensorMap &mw, co
     }
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(ma, mw, mc, bias, static_cast<TC *>(C), ldc, M, N, K, vec_ok);
+    kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(ma, mw, mc, bias, static_cast<TC *>(C), ldc, M, N, K, epi_col0, vec_ok);
     return check_launch("gemm_tc_kernel");
 }
 
 template <int BN, typename TC>
 static hx_status launch_tc_epi(const CUtensorMap &ma, const CUtensorMap &mw, const CUtensorMap &mc, const float *bias, void *C,
-                               int64_t ldc, int M, int N, int K, int vec_ok, int epi, cudaStream_t st) {
+                               int64_t ldc, int M, int N, int K, int vec_ok, int epi, int epi_col0, cudaStream_t st) {
     switch (epi) {
-        case kEpiNone: return launch_tc_inst<BN, TC, kEpiNone>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, st);
-        case kEpiSilu: return launch_tc_inst<BN, TC, kEpiSilu>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, st);
-        case kEpiSoftplus: return launch_tc_inst<BN, TC, kEpiSoftplus>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, st);
+        case kEpiNone: return launch_tc_inst<BN, TC, kEpiNone>(ma, mw, mc, bias, C, ldc, M, N, K, epi_col0, vec_ok, st);
+        case kEpiSilu: return launch_tc_inst<BN, TC, kEpiSilu>(ma, mw, mc, bias, C, ldc, M, N, K, epi_col0, vec_ok, st);
+        case kEpiSoftplus: return launch_tc_inst<BN, TC, kEpiSoftplus>(ma, mw, mc, bias, C, ldc, M, N, K, epi_col0, vec_ok, st);
+        case kEpiSiluFast: return launch_tc_inst<BN, TC, kEpiSiluFast>(ma, mw, mc, bias, C, ldc, M, N, K, epi_col0, vec_ok, st);
         default: return fail(HX_ERR_INVALID_INPUT, "unknown epilogue %d", epi);
     }
 }
@@ -333,7 +339,16 @@ hx_status read_status_gemm(int *v, bool clear) {
 extern "C" hx_status hx_gemm_bf16(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias, void *C,
                                   int64_t ldc, int32_t c_dtype, int32_t M, int32_t N, int32_t K, int32_t epilogue,
                                   void *stream) {
+    return hx_gemm_bf16_cols(A, lda, W, ldw, bias, C, ldc, c_dtype, M, N, K, epilogue, 0, stream);
+}
+
+extern "C" hx_status hx_gemm_bf16_cols(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias, void *C,
+                                       int64_t ldc, int32_t c_dtype, int32_t M, int32_t N, int32_t K, int32_t epilogue,
+                                       int32_t epilogue_first_col, void *stream) {
     using namespace hx::gemm;
+    const int epi_col0 = epilogue_first_col;
+    HX_REQUIRE(epi_col0 >= 0 && epi_col0 % 32 == 0, HX_ERR_INVALID_INPUT,
+               "epilogue_first_col must be a non-negative multiple of 32 (got %d)", epi_col0);
     hx_status s = validate_gemm(A, lda, W, ldw, C, ldc, M, N, K);
     if (s != HX_OK) return s;
     if (M == 0 || N == 0) return HX_OK;
@@ -345,7 +360,7 @@ extern "C" hx_status hx_gemm_bf16(const void *A, int64_t lda, const void *W, int
     cudaStream_t st = (cudaStream_t)stream;
     // a handful of rows (a decode step): stream the weights through many small CTAs instead of one 128-row tile
     if (M <= 64 && K % 32 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0)
-        return launch_skinny(A, lda, W, ldw, bias, C, ldc, c_dtype, M, N, K, epilogue, st);
+        return launch_skinny(A, lda, W, ldw, bias, C, ldc, c_dtype, M, N, K, epilogue, epi_col0, st);
     const int BN = N > 128 ? 256 : 128;
     CUtensorMap ma, mw;
     const uint64_t dims_a[2] = {(uint64_t)K, (uint64_t)M}, dims_w[2] = {(uint64_t)K, (uint64_t)N};
@@ -364,9 +379,9 @@ extern "C" hx_status hx_gemm_bf16(const void *A, int64_t lda, const void *W, int
         if ((s = hx::encode_tensor_map(&mc, c_dtype, 2, C, dims_c, str_c, box_c, true)) != HX_OK) return s;
     }
     if (BN == 256) {
-        if (c_dtype == HX_BF16) return launch_tc_epi<256, __nv_bfloat16>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
-        return launch_tc_epi<256, float>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
+        if (c_dtype == HX_BF16) return launch_tc_epi<256, __nv_bfloat16>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, epi_col0, st);
+        return launch_tc_epi<256, float>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, epi_col0, st);
     }
-    if (c_dtype == HX_BF16) return launch_tc_epi<128, __nv_bfloat16>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
-    return launch_tc_epi<128, float>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, st);
+    if (c_dtype == HX_BF16) return launch_tc_epi<128, __nv_bfloat16>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, epi_col0, st);
+    return launch_tc_epi<128, float>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, epi_col0, st);
 }

@@ -123,7 +123,15 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     };
     mark(0);
     // 1. xz = x W_in^T                                  [T, 2E]
-    if ((s = gemm(a->x, M, a->W_in, M, xz, 2 * E, (int)T, 2 * E, M)) != HX_OK) return s;
+    // The GEMM's epilogue could write [x | silu(z)] (hx_gemm_bf16_cols) so that the scan multiplies by the gate
+    // instead of computing it.  Measured at d_model 768, 65 536 tokens: the in_proj GEMM becomes epilogue-bound
+    // (5.8 -> 7.1 ms over 24 blocks) and the scan gains nothing, so the block does not do it.
+    const bool gate_in_gemm = false;
+    if (gate_in_gemm)
+        s = hx_gemm_bf16_cols(a->x, M, a->W_in, M, nullptr, xz, 2 * E, HX_BF16, (int)T, 2 * E, M, 3 /* fast SiLU */, E, stream);
+    else
+        s = gemm(a->x, M, a->W_in, M, xz, 2 * E, (int)T, 2 * E, M);
+    if (s != HX_OK) return s;
     if (a->conv_state &&
         (s = hx_conv_state_from_prefill(xz, (int64_t)a->seq_len * 2 * E, 2 * E, a->conv_state, a->batch, a->seq_len, E,
                                         a->io_dtype, stream)) != HX_OK)
@@ -161,6 +169,7 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     sa.y = y; sa.y_batch_stride = (int64_t)a->seq_len * E; sa.y_row_stride = E;
     sa.A = a->A; sa.Dskip = a->Dskip; sa.dt_bias = a->b_dt;
     sa.h_last = a->h_last;
+    sa.z_is_gate = gate_in_gemm ? 1 : 0;
     sa.conv_w = nullptr; sa.conv_b = nullptr;  // u is already activated
     sa.a_geometric = a->a_geometric;
     if (l.splits > 1) {

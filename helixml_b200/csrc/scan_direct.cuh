@@ -22,8 +22,9 @@
 namespace hx {
 namespace scan {
 
-template <typename T, int CPL_, bool GEOM_, bool STD_, int STAGES_, bool FUSEDT_ = false>
+template <typename T, int CPL_, bool GEOM_, bool STD_, int STAGES_, bool FUSEDT_ = false, bool ZGATE_ = false>
 struct DirectCfg {
+    static constexpr bool ZGATE = ZGATE_;              // z is known at compile time to hold silu(z) already
     static constexpr bool FUSEDT = FUSEDT_;            // dt = dt_low . W_dt^T computed by the producer warp (bf16 only)
     static constexpr int RP = 64;                      // columns of the dt_low / W_dt tiles (dt_rank <= 64, zero filled)
     static constexpr int CPL = CPL_;
@@ -80,6 +81,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     constexpr int CPL = Cfg::CPL, TC = Cfg::TC, STAGES = Cfg::STAGES, NW = Cfg::NWARP, NB = Cfg::NB, ES = Cfg::ES;
     constexpr bool GEOM = Cfg::GEOM, FAST = Cfg::FAST, STD = Cfg::STD, FUSEDT = Cfg::FUSEDT;
     const bool has_conv = STD || p.K > 0, has_z = STD || p.has_z, use_softplus = STD || p.dt_softplus;
+    const bool z_gate = Cfg::ZGATE || p.z_gate;
 
     extern __shared__ __align__(16) char smem_raw[];
     // aligned by pointer arithmetic (keeps the shared address space): 1024 bytes when the swizzled W_dt tile is
@@ -398,7 +400,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 } else {
                     dtv = v;
                 }
-                const float g = has_z ? silu_sel<FAST>(zr[e]) : 1.f;
+                const float g = has_z ? (z_gate ? zr[e] : silu_sel<FAST>(zr[e])) : 1.f;
                 const float xin = dtv * u;
                 // ---- decays
                 float2 a[8];

@@ -39,6 +39,7 @@ enum : int { kWaitFull = 1, kWaitEmpty = 2, kWaitOutFull = 4, kWaitOutEmpty = 8,
 struct SimpleParams {
     int B, L, D, N, K;
     int dt_softplus;
+    int z_gate;  // z already holds silu(z)
     const void *x, *dt, *z, *Bm, *Cm;
     void *y;
     int64_t xb, xr, dtb, dtr, zb, zr, Bb, Br, Cb, Cr, yb, yr;
@@ -99,7 +100,10 @@ __global__ void __launch_bounds__(128) scan_simple_kernel(SimpleParams p) {
             }
         }
         acc += dsk * u;
-        if (z) acc *= silu_acc(ld_f32(z + t * p.zr));
+        if (z) {
+            const float zv = ld_f32(z + t * p.zr);
+            acc *= p.z_gate ? zv : silu_acc(zv);
+        }
         st_f32(y + t * p.yr, acc);
     }
     if (p.h_last) {
@@ -116,6 +120,7 @@ struct TiledParams {
     int B, L, D;
     int K;            // conv taps in use (0: no conv, x is u already)
     int has_z;
+    int z_gate;       // z already holds silu(z)
     int dt_softplus;
     int n_segments;   // sequence segments (1 unless split)
     int seg_len;      // steps per segment, a multiple of the chunk length
@@ -496,7 +501,9 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                 float2 g = make_float2(1.f, 1.f);
                 if (has_z) {
                     const float2 zz = ld_pair<T>(szs, doff[pass]);
-                    if constexpr (FAST) {
+                    if (p.z_gate) {
+                        g = zz;
+                    } else if constexpr (FAST) {
                         const float2 t = mul2(zz, splat2(-kLog2e));
                         const float2 den = add2(make_float2(ex2_approx(t.x), ex2_approx(t.y)), splat2(1.f));
                         g = mul2(zz, make_float2(rcp_approx(den.x), rcp_approx(den.y)));
@@ -709,6 +716,7 @@ static hx_status launch_simple(const hx_scan_args *a, cudaStream_t st) {
     SimpleParams p;
     p.B = a->batch; p.L = a->seq_len; p.D = a->d_inner; p.N = a->d_state; p.K = a->conv_w ? a->d_conv : 0;
     p.dt_softplus = a->dt_softplus;
+    p.z_gate = a->z_is_gate != 0;
     p.x = a->x; p.dt = a->dt; p.z = a->z; p.Bm = a->Bm; p.Cm = a->Cm; p.y = a->y;
     p.xb = a->x_batch_stride; p.xr = a->x_row_stride; p.dtb = a->dt_batch_stride; p.dtr = a->dt_row_stride;
     p.zb = a->z_batch_stride; p.zr = a->z_row_stride; p.Bb = a->B_batch_stride; p.Br = a->B_row_stride;
@@ -799,6 +807,7 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
     p.B = a->batch; p.L = a->seq_len; p.D = a->d_inner;
     p.K = a->conv_w ? a->d_conv : 0;
     p.has_z = a->z != nullptr;
+    p.z_gate = a->z_is_gate != 0;
     p.dt_softplus = a->dt_softplus;
     p.n_segments = n_seg; p.seg_len = seg_len;
     p.A = a->A; p.Dskip = a->Dskip; p.conv_w = a->conv_w; p.conv_b = a->conv_b; p.dt_bias = a->dt_bias;
@@ -893,10 +902,10 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
 }
 
 
-template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2, bool FUSEDT = false>
+template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2, bool FUSEDT = false, bool ZGATE = false>
 static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *maps, dim3 grid, cudaStream_t st, void *y,
                                     int64_t y_bs, int64_t y_rs) {
-    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES, FUSEDT>;
+    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES, FUSEDT, ZGATE>;
     auto kern = scan_direct_kernel<T, Cfg>;
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -932,6 +941,7 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
     p.B = a->batch; p.L = a->seq_len; p.D = a->d_inner;
     p.K = a->conv_w ? a->d_conv : 0;
     p.has_z = a->z != nullptr;
+    p.z_gate = a->z_is_gate != 0;
     p.dt_softplus = a->dt_softplus;
     p.n_segments = n_seg; p.seg_len = seg_len;
     p.A = a->A; p.Dskip = a->Dskip; p.conv_w = a->conv_w; p.conv_b = a->conv_b; p.dt_bias = a->dt_bias;
@@ -991,8 +1001,7 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
     if ((s = encode_tensor_map(&maps[3], a->io_dtype, 3, a->Bm, dims_n, sb, box_n, false)) != HX_OK) return s;
     strides(a->C_row_stride, a->C_batch_stride, sb);
     if ((s = encode_tensor_map(&maps[4], a->io_dtype, 3, a->Cm, dims_n, sb, box_n, false)) != HX_OK) return s;
-    strides(a->y_row_stride, a->y_batch_stride, sb);
-    if ((s = encode_tensor_map(&maps[5], a->io_dtype, 3, a->y, dims_d, sb, box_r, false)) != HX_OK) return s;
+    maps[5] = maps[0];  // y is stored straight from registers: no tensor map, no TMA alignment rule for it
 
     HX_REQUIRE(a->batch <= 65535 && n_seg <= 65535, HX_ERR_INVALID_DIMENSION, "batch %d or segments %d exceed the grid limit",
                a->batch, n_seg);
@@ -1014,6 +1023,16 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
         void *yv = a->y;
         const int64_t ybs = a->y_batch_stride, yrs = a->y_row_stride;
         // the block hands u (already convolved): conv flags are read at run time, so STD is false here
+        // the gate flag is a compile-time constant on this path (the block's), so the activation code is gone when
+        // in_proj has already applied it
+        if (p.z_gate) {
+            if (cpl == 2) {
+                if (geom) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, true, true>(p, maps, grid, st, yv, ybs, yrs);
+                return launch_direct_inst<__nv_bfloat16, 2, false, false, 2, true, true>(p, maps, grid, st, yv, ybs, yrs);
+            }
+            if (geom) return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, true, true>(p, maps, grid, st, yv, ybs, yrs);
+            return launch_direct_inst<__nv_bfloat16, 1, false, false, 2, true, true>(p, maps, grid, st, yv, ybs, yrs);
+        }
         if (cpl == 2) {
             if (geom) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
             return launch_direct_inst<__nv_bfloat16, 2, false, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);

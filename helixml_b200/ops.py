@@ -71,8 +71,9 @@ def scan_workspace_bytes(batch, seq_len, d_inner, dtype, seq_splits=0) -> int:
 
 def selective_scan(x, dt, A, Bm, Cm, D=None, z=None, conv_w=None, conv_b=None, dt_bias=None, dt_softplus=True,
                    variant=L.SCAN_AUTO, a_geometric=None, lanes_per_channel=0, return_state=False, out=None,
-                   workspace=None, seq_splits=0, tune=0, dt_low=None, W_dt=None):
-    """Fused selective scan (hx_selective_scan_fwd).  x, dt, z, y: [B, L, D]; Bm, Cm: [B, L, N]."""
+                   workspace=None, seq_splits=0, tune=0, dt_low=None, W_dt=None, z_is_gate=False):
+    """Fused selective scan (hx_selective_scan_fwd).  x, dt, z, y: [B, L, D]; Bm, Cm: [B, L, N].
+    z_is_gate: z already holds silu(z)."""
     Bsz, Lq, Dm = x.shape
     N = A.shape[1]
     y = out if out is not None else torch.empty((Bsz, Lq, Dm), dtype=x.dtype, device=x.device)
@@ -120,6 +121,7 @@ def selective_scan(x, dt, A, Bm, Cm, D=None, z=None, conv_w=None, conv_b=None, d
     a.lanes_per_channel = lanes_per_channel
     a.seq_splits = seq_splits
     a.reserved = tune
+    a.z_is_gate = 1 if z_is_gate else 0
     if variant == L.SCAN_SEQSPLIT or seq_splits > 1:
         n = C.c_size_t(0)
         L.check(L.lib().hx_selective_scan_workspace_bytes(C.byref(a), C.byref(n)))

@@ -142,7 +142,8 @@ typedef struct hx_scan_args {
     const void *W_dt;
     int64_t dt_low_batch_stride, dt_low_row_stride;
     int32_t dt_rank;
-    int32_t reserved2;
+    int32_t z_is_gate;        /* 1: `z` already holds the gate silu(z) (the block's in_proj writes it that way with
+                                 hx_gemm_bf16_cols), so the scan multiplies by it instead of activating it */
 } hx_scan_args;
 
 HX_API hx_status hx_selective_scan_fwd(const hx_scan_args *args, void *stream);
@@ -241,6 +242,12 @@ HX_API size_t hx_s4_ref_workspace_bytes(int32_t seq_len, int32_t d_state);
 HX_API hx_status hx_gemm_bf16(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias,
                        void *C, int64_t ldc, int32_t c_dtype, int32_t M, int32_t N, int32_t K,
                        int32_t epilogue, void *stream);
+/* Same, with the activation applied only to the columns n >= epilogue_first_col (a multiple of 32): the block's
+ * in_proj writes [x | silu(z)] in one pass, so that the scan multiplies by the gate instead of computing it.
+ * epilogue 3 = SiLU with the hardware's approximate exp2 / reciprocal (bf16 outputs). */
+HX_API hx_status hx_gemm_bf16_cols(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias,
+                            void *C, int64_t ldc, int32_t c_dtype, int32_t M, int32_t N, int32_t K,
+                            int32_t epilogue, int32_t epilogue_first_col, void *stream);
 /* Same contract on CUDA cores in fp32 (any alignment, fp32 or bf16 operands): the small-shape and
  * fp32 path (the reference is fp32 throughout). */
 HX_API hx_status hx_gemm_simt(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias,

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 
 def run_gpu(inp, dtype, *, variant, lpc=0, geom=None, gate=True, skip=True, conv=True, conv_b=None, dt_bias=None,
-            softplus=True, state=False, seq_splits=0, tune=0):
+            softplus=True, state=False, seq_splits=0, tune=0, z_is_gate=False):
     from helixml_b200 import ops
     cast = "bf16" if dtype == "bf16" else None
     out = ops.selective_scan(
@@ -21,7 +21,7 @@ def run_gpu(inp, dtype, *, variant, lpc=0, geom=None, gate=True, skip=True, conv
         D=to_dev(inp["D"]) if skip else None, z=to_dev(inp["z"], cast) if gate else None,
         conv_w=to_dev(inp["conv_w"]) if conv else None, conv_b=to_dev(conv_b), dt_bias=to_dev(dt_bias),
         dt_softplus=softplus, variant=variant, a_geometric=geom, lanes_per_channel=lpc, return_state=state,
-        seq_splits=seq_splits, tune=tune)
+        seq_splits=seq_splits, tune=tune, z_is_gate=z_is_gate)
     from helixml_b200 import _lib
     assert _lib.device_status() == 0, "a bounded device-side wait ran out"
     if state:
@@ -165,6 +165,20 @@ def test_optional_terms(gate, skip, conv, softplus):
     ref = run_ref(inp, gate=gate, skip=skip, conv=conv, softplus=softplus)
     for variant, lpc in ((SIMPLE, 0), (TILED, 4), (TILED, 2), (TILED, 1), (DIRECT, 0)):
         check(run_gpu(inp, "f32", variant=variant, lpc=lpc, gate=gate, skip=skip, conv=conv, softplus=softplus), ref, "f32")
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_gate_given_already_activated(dtype):
+    """z_is_gate: the caller (the block's in_proj epilogue) hands silu(z) instead of z; every kernel then
+    multiplies by it as it is.  The reference result is the oracle on the original z."""
+    inp = synth.scan_inputs(39, 2, 70, 128, 16, 4, bf16=dtype == "bf16")
+    ref = run_ref(inp)
+    pre = dict(inp)
+    g = inp["z"].astype(np.float64)
+    g = (g / (1.0 + np.exp(-g))).astype(np.float32)
+    pre["z"] = synth.round_bf16(g) if dtype == "bf16" else g
+    for variant, lpc in ((SIMPLE, 0), (TILED, 2), (TILED, 4), (DIRECT, 0)):
+        check(run_gpu(pre, dtype, variant=variant, lpc=lpc, z_is_gate=True), ref, dtype)
 
 
 def test_softplus_identity_branch():
