@@ -52,6 +52,14 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (same workload as the benchmark, one launch each).
+NCU_TRAFFIC_BYTES = {
+    "lm_cfg3": 609_017_344,    # profiles/scan_direct_kernel_lm_cfg3.md: 413.6 MB + 195.4 MB
+    "scan_cfg2": 791_900_000,  # profiles/scan_tiled_kernel_cfg2.md: 608.9 MB + 182.9 MB
+}
+
+
 def scan_algorithmic_bytes(batch, seq_len, d_inner, d_state, d_conv, es=2):
     """x, dt, z read + y written once; B and C read once; parameters once."""
     pts = batch * seq_len * d_inner
@@ -322,7 +330,8 @@ def run_scan(args, cfg, name):
                        "variant": args.variant, "lanes_per_channel": args.lpc, "tune": args.tune, "seq_splits": args.splits},
             "roofline": {"bound": "hbm", "kernel": "scan_tiled_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                         "algorithmic_bytes_per_launch": alg, "traffic": None},
+                         "algorithmic_bytes_per_launch": alg,
+                         "traffic": NCU_TRAFFIC_BYTES.get(name) if (args.variant == "auto" and world == 1) else None},
             "compute_roof": scan_compute_roof(cfg["batch"] * cfg["seq_len"] * cfg["d_inner"], cfg["d_state"], cfg["d_conv"], alg,
                                               peaks["hbm_gbs"], pipe_rates(), ms_step),
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks, "device_status": status,
@@ -473,7 +482,7 @@ def run_lm(args, cfg, name):
         if dominant_scan:
             roof = {"bound": "hbm", "kernel": "scan_direct_kernel", "achieved": scan_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": scan_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                    "algorithmic_bytes_per_launch": scan_bytes, "launch_ms": scan_ms, "traffic": None,
+                    "algorithmic_bytes_per_launch": scan_bytes, "launch_ms": scan_ms, "traffic": NCU_TRAFFIC_BYTES.get(name),
                     "note": "dt projection fused into this kernel: it reads u, z, B, C and the rank-48 dt input, writes y"}
         else:
             roof = {"bound": "tensor", "kernel": "gemm_tc_kernel (all projections)", "achieved": gemm_tflops,
