@@ -56,7 +56,7 @@ class MambaBlockArgs(C.Structure):
         ("W_out", C.c_void_p), ("conv_w", C.c_void_p), ("conv_b", C.c_void_p), ("b_dt", C.c_void_p),
         ("A", C.c_void_p), ("Dskip", C.c_void_p), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("scan_variant", C.c_int32), ("a_geometric", C.c_int32), ("stage_events", C.c_void_p),
-        ("h_last", C.c_void_p), ("conv_state", C.c_void_p),
+        ("h_last", C.c_void_p), ("conv_state", C.c_void_p), ("residual", C.c_void_p),
     ]
 
 
@@ -109,6 +109,8 @@ _PROTOS = {
     "hx_s4_ref_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "hx_gemm_bf16": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "hx_gemm_bf16_acc": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
+                                   C.c_int32, C.c_void_p]),
     "hx_gemm_bf16_cols": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                     C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "hx_gemm_simt": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,

@@ -232,7 +232,7 @@ rmsnorm_kernel(const TX *x, float *residual, const float *w, TY *y, int64_t rows
         float v = xr ? ld_f32(xr + j) : 0.f;
         if (rr) {
             v += rr[j];
-            rr[j] = v;
+            if (xr) rr[j] = v;
         }
         ss += v * v;
     }
@@ -284,10 +284,12 @@ rmsnorm_vec_kernel(const TX *x, float *residual, const float *w, TY *y, int64_t 
                 r1.load(residual + off + 4);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) { v[i][e] += r0.v[e]; v[i][4 + e] += r1.v[e]; }
+                if (x) {  // nothing was added when x is NULL: the stream is read, not rewritten
 #pragma unroll
-                for (int e = 0; e < 4; ++e) { r0.v[e] = v[i][e]; r1.v[e] = v[i][4 + e]; }
-                r0.store(residual + off);
-                r1.store(residual + off + 4);
+                    for (int e = 0; e < 4; ++e) { r0.v[e] = v[i][e]; r1.v[e] = v[i][4 + e]; }
+                    r0.store(residual + off);
+                    r1.store(residual + off + 4);
+                }
             }
 #pragma unroll
             for (int e = 0; e < 8; ++e) ss += v[i][e] * v[i][e];
@@ -364,7 +366,22 @@ __global__ void __launch_bounds__(256) silu_kernel(const T *x, T *y, int64_t n) 
     if (i < n) st_f32(y + i, silu_acc(ld_f32(x + i)));
 }
 
+template <typename T>
+__global__ void __launch_bounds__(256) residual_add_kernel(float *resid, const T *x, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) resid[i] += ld_f32(x + i);
+}
+
 }  // namespace ew
+
+hx_status residual_add(float *resid, const void *x, int x_dtype, int64_t n, cudaStream_t st) {
+    if (n <= 0) return HX_OK;
+    dim3 grid((unsigned)((n + 255) / 256)), block(256);
+    if (x_dtype == HX_BF16) ew::residual_add_kernel<<<grid, block, 0, st>>>(resid, static_cast<const __nv_bfloat16 *>(x), n);
+    else ew::residual_add_kernel<<<grid, block, 0, st>>>(resid, static_cast<const float *>(x), n);
+    return check_launch("residual_add_kernel");
+}
+
 }  // namespace hx
 
 extern "C" {

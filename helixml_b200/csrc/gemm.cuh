@@ -6,7 +6,7 @@
 namespace hx {
 namespace gemm {
 
-enum : int { kEpiNone = 0, kEpiSilu = 1, kEpiSoftplus = 2, kEpiSiluFast = 3 };
+enum : int { kEpiNone = 0, kEpiSilu = 1, kEpiSoftplus = 2, kEpiSiluFast = 3, kEpiAccumulate = 4 };  // 4: C += A W^T (fp32 C)
 
 template <int EPI> __device__ __forceinline__ float apply_epilogue(float v) {
     if constexpr (EPI == kEpiSilu) return silu_acc(v);

@@ -91,7 +91,8 @@ gemm_skinny_kernel(const __nv_bfloat16 *__restrict__ A, int64_t lda, const __nv_
     const int c = n0 + 2 * (ln & 3) + (i & 1);
     if (r < M && c < N) {
         if (bias) v += bias[c];
-        st_f32(C + (int64_t)r * ldc + c, c >= epi_col0 ? apply_epilogue<EPI>(v) : v);
+        if constexpr (EPI == kEpiAccumulate) C[(int64_t)r * ldc + c] += TC(v);  // fp32 C; this thread owns the element
+        else st_f32(C + (int64_t)r * ldc + c, c >= epi_col0 ? apply_epilogue<EPI>(v) : v);
     }
 }
 
@@ -106,6 +107,10 @@ static hx_status launch_skinny_epi(const void *A, int64_t lda, const void *W, in
         case kEpiSilu: gemm_skinny_kernel<MT, TC, kEpiSilu><<<grid, block, 0, st>>>(a, lda, w, ldw, bias, c, ldc, M, N, K, epi_col0); break;
         case kEpiSoftplus: gemm_skinny_kernel<MT, TC, kEpiSoftplus><<<grid, block, 0, st>>>(a, lda, w, ldw, bias, c, ldc, M, N, K, epi_col0); break;
         case kEpiSiluFast: gemm_skinny_kernel<MT, TC, kEpiSiluFast><<<grid, block, 0, st>>>(a, lda, w, ldw, bias, c, ldc, M, N, K, epi_col0); break;
+        case kEpiAccumulate:
+            if constexpr (sizeof(TC) == 4) gemm_skinny_kernel<MT, TC, kEpiAccumulate><<<grid, block, 0, st>>>(a, lda, w, ldw, bias, c, ldc, M, N, K, epi_col0);
+            else return fail(HX_ERR_DTYPE_MISMATCH, "accumulating GEMM needs an fp32 C");
+            break;
         default: return fail(HX_ERR_INVALID_INPUT, "unknown epilogue %d", epi);
     }
     return check_launch("gemm_skinny_kernel");

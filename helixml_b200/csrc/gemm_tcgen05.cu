@@ -251,7 +251,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_2d(&tm_c, smem_u32(buf), nb, m0 + wq * 32);
+                        if constexpr (EPI == kEpiAccumulate) tma_reduce_add_2d(&tm_c, smem_u32(buf), nb, m0 + wq * 32);
+                        else tma_store_2d(&tm_c, smem_u32(buf), nb, m0 + wq * 32);
                         tma_store_commit();
                     }
                 }
@@ -270,7 +271,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                         float x = __uint_as_float(r[j]);
                         if (nb + j < N) {
                             if (bias) x += __ldg(bias + nb + j);
-                            st_f32(crow + nb + j, nb + j >= epi_col0 ? apply_epilogue<EPI>(x) : x);
+                            if constexpr (EPI == kEpiAccumulate) crow[nb + j] += x;  // this thread owns the element
+                            else st_f32(crow + nb + j, nb + j >= epi_col0 ? apply_epilogue<EPI>(x) : x);
                         }
                     }
                 }
@@ -319,6 +321,9 @@ static hx_status launch_tc_epi(const CUtensorMap &ma, const CUtensorMap &mw, con
         case kEpiSilu: return launch_tc_inst<BN, TC, kEpiSilu>(ma, mw, mc, bias, C, ldc, M, N, K, epi_col0, vec_ok, st);
         case kEpiSoftplus: return launch_tc_inst<BN, TC, kEpiSoftplus>(ma, mw, mc, bias, C, ldc, M, N, K, epi_col0, vec_ok, st);
         case kEpiSiluFast: return launch_tc_inst<BN, TC, kEpiSiluFast>(ma, mw, mc, bias, C, ldc, M, N, K, epi_col0, vec_ok, st);
+        case kEpiAccumulate:
+            if constexpr (sizeof(TC) == 4) return launch_tc_inst<BN, TC, kEpiAccumulate>(ma, mw, mc, bias, C, ldc, M, N, K, epi_col0, vec_ok, st);
+            else return fail(HX_ERR_DTYPE_MISMATCH, "accumulating GEMM needs an fp32 C");
         default: return fail(HX_ERR_INVALID_INPUT, "unknown epilogue %d", epi);
     }
 }
@@ -340,6 +345,11 @@ extern "C" hx_status hx_gemm_bf16(const void *A, int64_t lda, const void *W, int
                                   int64_t ldc, int32_t c_dtype, int32_t M, int32_t N, int32_t K, int32_t epilogue,
                                   void *stream) {
     return hx_gemm_bf16_cols(A, lda, W, ldw, bias, C, ldc, c_dtype, M, N, K, epilogue, 0, stream);
+}
+
+extern "C" hx_status hx_gemm_bf16_acc(const void *A, int64_t lda, const void *W, int64_t ldw, float *C, int64_t ldc, int32_t M,
+                                      int32_t N, int32_t K, void *stream) {
+    return hx_gemm_bf16_cols(A, lda, W, ldw, nullptr, C, ldc, HX_F32, M, N, K, hx::gemm::kEpiAccumulate, 0, stream);
 }
 
 extern "C" hx_status hx_gemm_bf16_cols(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias, void *C,

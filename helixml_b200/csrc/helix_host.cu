@@ -434,11 +434,11 @@ size_t MambaBlock::workspace_bytes(int64_t batch, int64_t seq_len) const {
 
 Result<Unit> MambaBlock::forward_into(const void *x, void *out, int64_t batch, int64_t seq_len, void *workspace,
                                       size_t ws_bytes, void *stream, void **stage_events, float *h_last,
-                                      void *conv_state) const {
+                                      void *conv_state, float *residual) const {
     hx_mamba_block_args a = block_args(*this, batch, seq_len);
     a.x = x; a.out = out; a.workspace = workspace; a.workspace_bytes = ws_bytes;
     a.stage_events = stage_events;
-    a.h_last = h_last; a.conv_state = conv_state;
+    a.h_last = h_last; a.conv_state = conv_state; a.residual = residual;
     HELIX_TRY_ABI(hx_mamba_block_fwd(&a, stream));
     return Unit{};
 }
@@ -746,10 +746,9 @@ Result<Unit> ByteLM::run_layers(const uint8_t *tokens_dev, void *logits_dev, int
     // h = emb[tokens] (fp32 residual stream)
     HELIX_TRY_ABI(hx_embedding_fwd(tokens_dev, embedding.data(), (int)dtype, resid, HX_F32, T, (int)d_model, stream));
     for (size_t l = 0; l < blocks.size(); ++l) {
-        // residual += previous block output (none for the first layer); normed = rmsnorm(residual)
-        const void *delta = l == 0 ? nullptr : buf_->block_out.data();
+        // normed = rmsnorm(residual); the block adds its output into the residual stream itself (out_proj epilogue)
         mark(1);
-        HELIX_TRY_ABI(hx_rmsnorm_fwd(delta, (int)dtype, resid, static_cast<const float *>(norms[l]->weight.data()),
+        HELIX_TRY_ABI(hx_rmsnorm_fwd(nullptr, (int)dtype, resid, static_cast<const float *>(norms[l]->weight.data()),
                                      buf_->normed.data(), (int)dtype, T, (int)d_model, eps, stream));
         void *sev[7];
         void **sevp = nullptr;
@@ -765,10 +764,10 @@ Result<Unit> ByteLM::run_layers(const uint8_t *tokens_dev, void *logits_dev, int
         HELIX_TRY(blocks[l]->forward_into(buf_->normed.data(), buf_->block_out.data(), batch, seq_len, buf_->workspace.data(),
                                           (size_t)buf_->workspace.numel(), stream, sevp,
                                           keep_state ? static_cast<float *>(dec_->h[l].data()) : nullptr,
-                                          keep_state ? dec_->conv[l].data() : nullptr));
+                                          keep_state ? dec_->conv[l].data() : nullptr, resid));
     }
     mark(1);
-    HELIX_TRY_ABI(hx_rmsnorm_fwd(buf_->block_out.data(), (int)dtype, resid, static_cast<const float *>(norm_f.data()),
+    HELIX_TRY_ABI(hx_rmsnorm_fwd(nullptr, (int)dtype, resid, static_cast<const float *>(norm_f.data()),
                                  buf_->normed.data(), (int)dtype, T, (int)d_model, eps, stream));
     mark(8);
     // tied head: logits = normed . emb^T

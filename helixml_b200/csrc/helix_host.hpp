@@ -196,9 +196,11 @@ class MambaBlock : public Module {
     // forward into caller-provided buffers (no allocation): x and out are [batch*seq_len, d_model]
     // h_last [batch, d_inner, d_state] fp32 and conv_state [batch, 3, d_inner] (model dtype), when given, receive
     // the state a decode step continues from.
+    // residual [batch*seq_len, d_model] fp32, when given, receives `+= block output` (and `out` is only scratch for
+    // the fp32 path).
     Result<Unit> forward_into(const void *x, void *out, int64_t batch, int64_t seq_len, void *workspace,
                               size_t workspace_bytes, void *stream, void **stage_events = nullptr, float *h_last = nullptr,
-                              void *conv_state = nullptr) const;
+                              void *conv_state = nullptr, float *residual = nullptr) const;
     size_t workspace_bytes(int64_t batch, int64_t seq_len) const;
     // one decode step: x, out [batch, d_model]; h and conv_state are updated in place
     Result<Unit> step_into(const void *x, void *out, int64_t batch, float *h, void *conv_state, void *workspace,

@@ -42,6 +42,9 @@ inline size_t dtype_size(int dt) { return dt == HX_F32 ? 4 : dt == HX_BF16 ? 2 :
 // Number of SMs of the current device, cached per device.
 int sm_count();
 
+// resid[i] += x[i] (x fp32 or bf16): the residual update where no GEMM epilogue can do it.
+hx_status residual_add(float *resid, const void *x, int x_dtype, int64_t n, cudaStream_t st);
+
 // Translation units with bounded device-side waits keep a status word each; these read (and
 // optionally clear) them.  hx_device_status() ORs them together.
 hx_status read_status_scan(int *v, bool clear);

@@ -96,7 +96,7 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     hx_status s = validate(a);
     if (s != HX_OK) return s;
     if (a->batch == 0 || a->seq_len == 0) return HX_OK;
-    HX_REQUIRE(a->x && a->out && a->W_in && a->W_x && a->W_dt && a->W_out && a->conv_w && a->b_dt && a->A && a->Dskip,
+    HX_REQUIRE(a->x && (a->out || a->residual) && a->W_in && a->W_x && a->W_dt && a->W_out && a->conv_w && a->b_dt && a->A && a->Dskip,
                HX_ERR_INVALID_INPUT, "a required block operand is NULL");
     const Layout l = plan(a);
     HX_REQUIRE(a->workspace && a->workspace_bytes >= l.total, HX_ERR_INVALID_INPUT,
@@ -180,7 +180,21 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     if ((s = hx_selective_scan_fwd(&sa, stream)) != HX_OK) return s;
     mark(5);
     // 6. out = y W_out^T                                 [T, M]
-    s = gemm(y, E, a->W_out, E, a->out, M, (int)T, M, E);
+    // With a residual stream the tensor-core GEMM adds its tiles straight into it (fp32, TMA reduce): the bf16
+    // block output, its write and the read of it by the next norm disappear.
+    if (a->residual) {
+        const bool tc_out = bf && E % 8 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
+                            (reinterpret_cast<uintptr_t>(a->W_out) & 15) == 0;
+        if (tc_out) {
+            s = hx_gemm_bf16_acc(y, E, a->W_out, E, a->residual, M, (int)T, M, E, stream);
+        } else {
+            HX_REQUIRE(a->out != nullptr, HX_ERR_INVALID_INPUT, "this path needs `out` as scratch for the residual update");
+            if ((s = gemm(y, E, a->W_out, E, a->out, M, (int)T, M, E)) != HX_OK) return s;
+            s = hx::residual_add(a->residual, a->out, a->io_dtype, T * M, (cudaStream_t)stream);
+        }
+    } else {
+        s = gemm(y, E, a->W_out, E, a->out, M, (int)T, M, E);
+    }
     mark(6);
     return s;
 }

@@ -188,6 +188,19 @@ def gemm(a, w, bias=None, out_dtype=None, epilogue=L.EPI_NONE, tensor_cores=None
     return c
 
 
+def gemm_acc(a, w, c):
+    """c += a @ w.T (hx_gemm_bf16_acc): a [M, K], w [N, K] bf16, c [M, N] fp32, updated in place."""
+    M, K = a.shape
+    N = w.shape[0]
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or c.dtype != torch.float32:
+        raise L.HxError(4, "gemm_acc takes bf16 operands and an fp32 accumulator")
+    if tuple(c.shape) != (M, N) or w.shape[1] != K:
+        raise L.HxError(1, f"shapes {tuple(a.shape)}, {tuple(w.shape)}, {tuple(c.shape)} do not fit")
+    L.check(L.lib().hx_gemm_bf16_acc(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(0), c.data_ptr(), c.stride(0), M, N, K,
+                                     _stream()))
+    return c
+
+
 def rmsnorm(x, w, eps=1e-5, residual=None, out_dtype=None):
     """y = rmsnorm(residual + x) with residual (fp32) updated in place, or rmsnorm(x) without it."""
     src = x if x is not None else residual
@@ -228,7 +241,7 @@ def mamba_block_workspace_bytes(batch, seq_len, d_model, d_inner, d_state, d_con
 
 
 def mamba_block(x, w: dict, d_state: int, d_conv: int, workspace=None, scan_variant=L.SCAN_AUTO, a_geometric=None,
-                out=None, h_last=None, conv_state=None):
+                out=None, h_last=None, conv_state=None, residual=None):
     """One Mamba block forward (hx_mamba_block_fwd).  x [B, L, M]; w: device tensors W_in, W_x, W_dt,
     W_out in x.dtype and conv_w, conv_b, b_dt, A, D in fp32.  h_last [B, E, N] fp32 and conv_state [B, 3, E]
     (x.dtype), when given, receive the state a decode step continues from."""
@@ -265,6 +278,8 @@ def mamba_block(x, w: dict, d_state: int, d_conv: int, workspace=None, scan_vari
         a.h_last = h_last.data_ptr()
     if conv_state is not None:
         a.conv_state = conv_state.data_ptr()
+    if residual is not None:  # fp32 [B, L, M]: the block output is added into it
+        a.residual = residual.data_ptr()
     L.check(L.lib().hx_mamba_block_fwd(C.byref(a), _stream()))
     return y
 

@@ -248,6 +248,10 @@ HX_API hx_status hx_gemm_bf16(const void *A, int64_t lda, const void *W, int64_t
 HX_API hx_status hx_gemm_bf16_cols(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias,
                             void *C, int64_t ldc, int32_t c_dtype, int32_t M, int32_t N, int32_t K,
                             int32_t epilogue, int32_t epilogue_first_col, void *stream);
+/* C[M,N] += A[M,K] . W[N,K]^T with an fp32 C: the epilogue adds its tile into C through the memory system (TMA
+ * reduce), so a block's out_proj can accumulate straight into the fp32 residual stream. */
+HX_API hx_status hx_gemm_bf16_acc(const void *A, int64_t lda, const void *W, int64_t ldw, float *C, int64_t ldc,
+                           int32_t M, int32_t N, int32_t K, void *stream);
 /* Same contract on CUDA cores in fp32 (any alignment, fp32 or bf16 operands): the small-shape and
  * fp32 path (the reference is fp32 throughout). */
 HX_API hx_status hx_gemm_simt(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias,
@@ -299,6 +303,9 @@ typedef struct hx_mamba_block_args {
     void *conv_state;         /* NULL, or [batch, 3, d_inner] io dtype: the conv inputs of the last three steps
                                  (oldest first, zeros where seq_len < 3); with h_last, what hx_mamba_block_step
                                  continues from */
+    float *residual;          /* NULL, or the fp32 residual stream [batch*seq_len, d_model]: the block's output is
+                                 added into it (by the out_proj epilogue where the tensor-core GEMM runs) and
+                                 `out` is not written, unless the fp32 path needs it as scratch */
 } hx_mamba_block_args;
 
 HX_API hx_status hx_mamba_block_fwd(const hx_mamba_block_args *args, void *stream);

@@ -178,6 +178,56 @@ def test_gemm_few_rows_bf16(M, N, K):
     _status_ok()
 
 
+@pytest.mark.parametrize("M,N,K", [(300, 768, 1536), (129, 136, 72), (4096, 256, 768), (40, 768, 64), (513, 80, 1536)])
+def test_gemm_accumulates_into_fp32(M, N, K):
+    """C += A W^T: the epilogue adds its tiles into C (TMA reduce on the tensor-core path, plain read-modify-write
+    on the few-rows and unaligned paths); twice in a row to see that nothing is overwritten."""
+    import torch
+    from helixml_b200 import ops
+    a = synth.round_bf16(synth.normal(65, "a", (M, K)))
+    w = synth.round_bf16(synth.normal(65, "w", (N, K), 0, 0.05))
+    c0 = synth.normal(65, "c", (M, N))
+    c = to_dev(c0)
+    ops.gemm_acc(to_dev(a, "bf16"), to_dev(w, "bf16"), c)
+    prod = a.astype(np.float64) @ w.astype(np.float64).T
+    assert fp32_tol_err(to_np(c), c0 + prod) <= FP32_TOL
+    ops.gemm_acc(to_dev(a, "bf16"), to_dev(w, "bf16"), c)
+    assert fp32_tol_err(to_np(c), c0 + 2 * prod) <= FP32_TOL
+    _status_ok()
+    # an accumulator whose rows are not 16-byte aligned takes the plain-store path
+    wide = torch.zeros(M, N + 3, device="cuda")
+    view = wide[:, 1:N + 1]
+    view.copy_(to_dev(c0))
+    ops.gemm_acc(to_dev(a, "bf16"), to_dev(w, "bf16"), view)
+    assert fp32_tol_err(to_np(view), c0 + prod) <= FP32_TOL
+    assert float(wide[:, 0].abs().max()) == 0.0 and float(wide[:, N + 1:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_mamba_block_adds_into_residual(dtype):
+    """With a residual stream the block's output is added into it (out_proj epilogue on the bf16 path)."""
+    import torch
+    from helixml_b200 import ops
+    bf = dtype == "bf16"
+    B, L, M = 2, 90, 128
+    w = synth.mamba_block_weights(8, M, 16, 4, 2)
+    big = ("W_in", "W_x", "W_dt", "W_out")
+    wq = {k: (synth.round_bf16(v) if (bf and k in big) else v) for k, v in w.items()}
+    x = synth.normal(8, "x", (B, L, M))
+    if bf:
+        x = synth.round_bf16(x)
+    r0 = synth.normal(8, "r", (B, L, M))
+    dev = {k: to_dev(v, "bf16" if (bf and k in big) else None) for k, v in wq.items()}
+    resid = to_dev(r0)
+    ops.mamba_block(to_dev(x, "bf16" if bf else None), dev, 16, 4, residual=resid)
+    _status_ok()
+    ref = r0 + cbind.mamba_block(x, wq, 16, 4)
+    if bf:
+        assert rel_l2(to_np(resid) - r0, ref - r0) <= BF16_TOL
+    else:
+        assert fp32_tol_err(to_np(resid), ref) <= FP32_TOL
+
+
 # ------------------------------------------------------------------ the whole block
 def test_mamba_block_config0_f32(golden):
     """Benchmark configuration 0: batch 1, L 100, d_model 64, d_state 16, expand 2, conv 4, f32, seed 0."""
