@@ -164,8 +164,9 @@ def s4_ref_forward_ssm(u, A_real, A_imag, Bm, Cm, Dv, dt=0.1):
     return y
 
 
-def gemm(a, w, bias=None, out_dtype=None, epilogue=L.EPI_NONE, tensor_cores=None, out=None):
-    """C = a @ w.T (+ bias) (+ activation).  a [M, K] (row stride arbitrary), w [N, K]."""
+def gemm(a, w, bias=None, out_dtype=None, epilogue=L.EPI_NONE, tensor_cores=None, out=None, epilogue_first_col=0):
+    """C = a @ w.T (+ bias) (+ activation).  a [M, K] (row stride arbitrary), w [N, K].
+    epilogue_first_col (tensor-core path): the activation applies to columns >= it (a multiple of 32)."""
     M, K = a.shape
     N = w.shape[0]
     if w.shape[1] != K:
@@ -178,8 +179,8 @@ def gemm(a, w, bias=None, out_dtype=None, epilogue=L.EPI_NONE, tensor_cores=None
     if tensor_cores:
         if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
             raise L.HxError(4, "the tensor-core GEMM takes bf16 operands")
-        L.check(L.lib().hx_gemm_bf16(_p(a), a.stride(0), _p(w), w.stride(0), _p(_f32(bias)), _p(c), c.stride(0), _dt(c),
-                                     M, N, K, epilogue, _stream()))
+        L.check(L.lib().hx_gemm_bf16_cols(_p(a), a.stride(0), _p(w), w.stride(0), _p(_f32(bias)), _p(c), c.stride(0), _dt(c),
+                                          M, N, K, epilogue, epilogue_first_col, _stream()))
     else:
         if a.dtype != w.dtype:
             raise L.HxError(4, "a and w must share a dtype")

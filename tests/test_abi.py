@@ -106,6 +106,13 @@ def test_workspace_size_queries():
     assert lib.hx_selective_scan_workspace_bytes(C.byref(a), C.byref(n)) == 0
     assert n.value >= 3 * 2 * 128 * 16 * 4
     assert lib.hx_s4_ref_workspace_bytes(100, 16) == 100 * 16 * 4
+    st = L.MambaStepArgs()
+    st.batch, st.d_model, st.d_inner, st.d_state, st.d_conv, st.dt_rank, st.io_dtype = 4, 64, 128, 16, 4, 4, L.HX_F32
+    assert lib.hx_mamba_step_workspace_bytes(C.byref(st), C.byref(n)) == 0 and n.value >= 4 * (2 * 128 + 128 + 36 + 128) * 4
+    st.d_conv = 5
+    assert lib.hx_mamba_step_workspace_bytes(C.byref(st), C.byref(n)) == 2
+    assert lib.hx_mamba_block_step(None, None) == 10
+    assert lib.hx_gemm_bf16_cols(C.c_void_p(16), 8, C.c_void_p(16), 8, None, C.c_void_p(16), 8, L.HX_F32, 4, 4, 8, 1, 40, None) == 10
 
 
 def test_errors_are_thread_local():

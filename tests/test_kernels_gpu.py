@@ -178,6 +178,27 @@ def test_gemm_few_rows_bf16(M, N, K):
     _status_ok()
 
 
+@pytest.mark.parametrize("M", [300, 20])
+def test_gemm_activation_on_a_column_range(M):
+    """hx_gemm_bf16_cols: [x | silu(z)] in one pass, the activation starting at a column that is a multiple of 32
+    (both the tensor-memory kernel and the few-rows kernel)."""
+    import torch
+    from helixml_b200 import _lib, ops
+    N, K, first = 320, 64, 96
+    a = synth.round_bf16(synth.normal(66, "a", (M, K)))
+    w = synth.round_bf16(synth.normal(66, "w", (N, K), 0, 0.2))
+    lin = a.astype(np.float64) @ w.astype(np.float64).T
+    ref = lin.copy()
+    ref[:, first:] = lin[:, first:] / (1 + np.exp(-lin[:, first:]))
+    for epi, tol in ((_lib.EPI_SILU, FP32_TOL), (_lib.EPI_SILU_FAST, 2e-3)):
+        got = ops.gemm(to_dev(a, "bf16"), to_dev(w, "bf16"), out_dtype=torch.float32, epilogue=epi, epilogue_first_col=first)
+        assert fp32_tol_err(to_np(got), ref) <= tol
+    _status_ok()
+    with pytest.raises(_lib.HxError) as e:
+        ops.gemm(to_dev(a, "bf16"), to_dev(w, "bf16"), epilogue=_lib.EPI_SILU, epilogue_first_col=40)
+    assert e.value.variant == "InvalidInput"
+
+
 @pytest.mark.parametrize("M,N,K", [(300, 768, 1536), (129, 136, 72), (4096, 256, 768), (40, 768, 64), (513, 80, 1536)])
 def test_gemm_accumulates_into_fp32(M, N, K):
     """C += A W^T: the epilogue adds its tiles into C (TMA reduce on the tensor-core path, plain read-modify-write
