@@ -319,7 +319,7 @@ def run_scan(args, cfg, name):
         peaks = measured_peaks()
         alg = scan_algorithmic_bytes(cfg["batch"], cfg["seq_len"], cfg["d_inner"], cfg["d_state"], cfg["d_conv"])
         achieved = alg / (ms_step * 1e-3) / 1e9
-        cpu = None if args.no_cpu else cpu_baseline_scan(cfg)
+        cpu = None if (args.no_cpu or world > 1) else cpu_baseline_scan(cfg)  # the CPU leg is timed at N = 1 only
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if args.shard == "channels" else "weak",
@@ -488,7 +488,7 @@ def run_lm(args, cfg, name):
             roof = {"bound": "tensor", "kernel": "gemm_tc_kernel (all projections)", "achieved": gemm_tflops,
                     "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": gemm_tflops / peaks["bf16_tflops_sustained"],
                     "peak_source": peaks["source"] + " (sustained)", "traffic": None}
-        cpu = None if args.no_cpu else cpu_baseline_lm(cfg)
+        cpu = None if (args.no_cpu or world > 1) else cpu_baseline_lm(cfg)  # the CPU leg is timed at N = 1 only
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
