@@ -22,8 +22,11 @@
 namespace hx {
 namespace scan {
 
-template <typename T, int CPL_, bool GEOM_, bool STD_, int STAGES_, bool FUSEDT_ = false, bool ZGATE_ = false>
+template <typename T, int CPL_, bool GEOM_, bool STD_, int STAGES_, bool FUSEDT_ = false, bool ZGATE_ = false,
+          bool BLOCK_ = false>
 struct DirectCfg {
+    static constexpr bool BLOCK = BLOCK_;              // the Mamba block's call: no conv (u is given), gate and softplus
+                                                       // present, all known at compile time
     static constexpr bool ZGATE = ZGATE_;              // z is known at compile time to hold silu(z) already
     static constexpr bool FUSEDT = FUSEDT_;            // dt = dt_low . W_dt^T computed by the producer warp (bf16 only)
     static constexpr int RP = 64;                      // columns of the dt_low / W_dt tiles (dt_rank <= 64, zero filled)
@@ -80,7 +83,9 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                    const int64_t y_rs) {
     constexpr int CPL = Cfg::CPL, TC = Cfg::TC, STAGES = Cfg::STAGES, NW = Cfg::NWARP, NB = Cfg::NB, ES = Cfg::ES;
     constexpr bool GEOM = Cfg::GEOM, FAST = Cfg::FAST, STD = Cfg::STD, FUSEDT = Cfg::FUSEDT;
-    const bool has_conv = STD || p.K > 0, has_z = STD || p.has_z, use_softplus = STD || p.dt_softplus;
+    constexpr bool BLOCK = Cfg::BLOCK;
+    const bool has_conv = !BLOCK && (STD || p.K > 0), has_z = STD || BLOCK || p.has_z,
+               use_softplus = STD || BLOCK || p.dt_softplus;
     const bool z_gate = Cfg::ZGATE || p.z_gate;
 
     extern __shared__ __align__(16) char smem_raw[];

@@ -902,10 +902,10 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
 }
 
 
-template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2, bool FUSEDT = false, bool ZGATE = false>
+template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2, bool FUSEDT = false, bool ZGATE = false, bool BLOCK = false>
 static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *maps, dim3 grid, cudaStream_t st, void *y,
                                     int64_t y_bs, int64_t y_rs) {
-    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES, FUSEDT, ZGATE>;
+    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES, FUSEDT, ZGATE, BLOCK>;
     auto kern = scan_direct_kernel<T, Cfg>;
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -1032,6 +1032,12 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
             }
             if (geom) return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, true, true>(p, maps, grid, st, yv, ybs, yrs);
             return launch_direct_inst<__nv_bfloat16, 1, false, false, 2, true, true>(p, maps, grid, st, yv, ybs, yrs);
+        }
+        // the block's own call (u already convolved, gate and softplus present, geometric A): every flag is a
+        // compile-time constant, which saves the per-point flag tests and the registers of the unused conv window
+        if (geom && !p.z_gate && a->conv_w == nullptr && a->z != nullptr && a->dt_softplus != 0) {
+            if (cpl == 2) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, true, false, true>(p, maps, grid, st, yv, ybs, yrs);
+            return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, true, false, true>(p, maps, grid, st, yv, ybs, yrs);
         }
         if (cpl == 2) {
             if (geom) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
