@@ -199,7 +199,7 @@ conv_silu_strip_kernel(const __nv_bfloat16 *__restrict__ x, int64_t xb, int64_t 
             c0 = fmaf(w[1][e], w1[e], c0); c1 = fmaf(w[1][e + 1], w1[e + 1], c1);
             c0 = fmaf(w[2][e], w2[e], c0); c1 = fmaf(w[2][e + 1], w2[e + 1], c1);
             c0 = fmaf(w[3][e], cur[e], c0); c1 = fmaf(w[3][e + 1], cur[e + 1], c1);
-            const __nv_bfloat162 ob = __floats2bfloat162_rn(silu_fast(c0), silu_fast(c1));
+            const __nv_bfloat162 ob = __floats2bfloat162_rn(silu_tanh(c0), silu_tanh(c1));
             op[e / 2] = *reinterpret_cast<const uint32_t *>(&ob);
         }
         *reinterpret_cast<V *>(up + (int64_t)k * ur) = o;
