@@ -187,7 +187,7 @@ template <> __device__ __forceinline__ float2 ld_pair<__nv_bfloat16>(const char 
 }
 
 template <bool FAST> __device__ __forceinline__ float silu_sel(float x) {
-    if constexpr (FAST) return silu_fast(x);
+    if constexpr (FAST) return silu_tanh(x);  // bf16 I/O: one special-function result, error below the output rounding
     else return silu_acc(x);
 }
 
