@@ -15,6 +15,7 @@
 // not be tile multiples (K and the leading dimensions must be multiples of 8 for the 16-byte rule).
 // Every wait is bounded; a wait that runs out raises the per-device status word, the CTA drains,
 // frees its tensor memory and returns.
+#include <atomic>
 #include "gemm.cuh"
 #include "hx_tma.cuh"
 
@@ -300,12 +301,12 @@ static hx_status launch_tc_inst(const CUtensorMap &ma, const CUtensorMap &mw, co
                                 int64_t ldc, int M, int N, int K, int epi_col0, int vec_ok, cudaStream_t st) {
     using Cfg = TcCfg<BN>;
     auto kern = gemm_tc_kernel<BN, TC, EPI>;
-    static bool attr_set[64] = {false};
+    static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice is harmless
     int dev = 0;
     HX_CUDA(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
         HX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        attr_set[dev] = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();

@@ -21,6 +21,7 @@
 // The reference has no selective scan to follow (its conv1d is the identity and selective_ssm
 // ignores B and C, crates/nn/src/ssm.rs:467-483); the arithmetic is the one written in
 // include/helix_b200.h above hx_scan_args.
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -767,12 +768,12 @@ static hx_status launch_tiled_inst(const hx_scan_args *a, const TiledParams &p, 
                                    cudaStream_t st) {
     using Cfg = TiledCfg<T, LPC, GEOM, TC, STAGES, STD>;
     auto kern = scan_tiled_kernel<T, Cfg>;
-    static bool attr_set[64] = {false};
+    static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice is harmless
     int dev = 0;
     HX_CUDA(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
         HX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        attr_set[dev] = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[5], p);
     return check_launch("scan_tiled_kernel");
@@ -907,12 +908,12 @@ static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *map
                                     int64_t y_bs, int64_t y_rs) {
     using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES, FUSEDT, ZGATE, BLOCK>;
     auto kern = scan_direct_kernel<T, Cfg>;
-    static bool attr_set[64] = {false};
+    static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice is harmless
     int dev = 0;
     HX_CUDA(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
         HX_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        attr_set[dev] = true;
+        attr_set[dev].store(true, std::memory_order_release);
     }
     kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(maps[0], maps[1], maps[2], maps[3], maps[4], maps[6], maps[7], p,
                                                       static_cast<T *>(y), y_bs, y_rs);
