@@ -247,7 +247,7 @@ rmsnorm_kernel(const TX *x, float *residual, const float *w, TY *y, int64_t rows
 
 // Vector path: d is a multiple of 8 and at most 8*32*NV; every lane keeps its NV groups of 8 values in
 // registers between the two passes, so each operand crosses HBM once.
-template <typename TX, typename TY, int NV>
+template <typename TX, typename TY, int NV, bool HAS_X>
 __global__ void __launch_bounds__(256)
 rmsnorm_vec_kernel(const TX *x, float *residual, const float *w, TY *y, int64_t rows, int d, float eps) {
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -261,7 +261,7 @@ rmsnorm_vec_kernel(const TX *x, float *residual, const float *w, TY *y, int64_t 
         const int g = lane + 32 * i;
         if (g < groups) {
             const int64_t off = row * d + g * 8;
-            if (x) {
+            if constexpr (HAS_X) {
                 if constexpr (sizeof(TX) == 2) {
                     Vec<__nv_bfloat16> t;
                     t.load(reinterpret_cast<const __nv_bfloat16 *>(x) + off);
@@ -284,7 +284,7 @@ rmsnorm_vec_kernel(const TX *x, float *residual, const float *w, TY *y, int64_t 
                 r1.load(residual + off + 4);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) { v[i][e] += r0.v[e]; v[i][4 + e] += r1.v[e]; }
-                if (x) {  // nothing was added when x is NULL: the stream is read, not rewritten
+                if constexpr (HAS_X) {  // nothing was added when x is NULL: the stream is read, not rewritten
 #pragma unroll
                     for (int e = 0; e < 4; ++e) { r0.v[e] = v[i][e]; r1.v[e] = v[i][4 + e]; }
                     r0.store(residual + off);
@@ -453,8 +453,12 @@ hx_status hx_rmsnorm_fwd(const void *x, int32_t x_dtype, float *residual, const 
     if (d % 8 == 0 && d <= 8 * 32 * 4 && al16(x) && al16(residual) && al16(w) && al16(y)) {
         // every lane holds up to 4 groups of 8 values (d <= 1024)
 #define HX_NORM_VEC(TX, TY)                                                                                      \
-        rmsnorm_vec_kernel<TX, TY, 4><<<grid, block, 0, st>>>(static_cast<const TX *>(x), residual, w, static_cast<TY *>(y), \
-                                                              rows, d, eps)
+        do {                                                                                                     \
+            if (x) rmsnorm_vec_kernel<TX, TY, 4, true><<<grid, block, 0, st>>>(static_cast<const TX *>(x), residual, w,  \
+                                                                               static_cast<TY *>(y), rows, d, eps);  \
+            else rmsnorm_vec_kernel<TX, TY, 4, false><<<grid, block, 0, st>>>(static_cast<const TX *>(x), residual, w,   \
+                                                                              static_cast<TY *>(y), rows, d, eps);  \
+        } while (0)
         if (xb && yb) HX_NORM_VEC(__nv_bfloat16, __nv_bfloat16);
         else if (xb) HX_NORM_VEC(__nv_bfloat16, float);
         else if (yb) HX_NORM_VEC(float, __nv_bfloat16);

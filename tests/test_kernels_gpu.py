@@ -249,6 +249,49 @@ def test_mamba_block_adds_into_residual(dtype):
         assert fp32_tol_err(to_np(resid), ref) <= FP32_TOL
 
 
+def test_four_threads_call_concurrently():
+    """The reference's 4-thread concurrent matmul test (crates/backend-cpu/tests/integration_tests.rs:68-99) at this
+    boundary: four host threads, each on its own stream, run the tensor-core GEMM and the fused scan at the same
+    time; every result must equal the single-threaded one."""
+    import threading
+    import torch
+    from helixml_b200 import _lib, ops
+    a = to_dev(synth.round_bf16(synth.normal(67, "a", (700, 256))), "bf16")
+    w = to_dev(synth.round_bf16(synth.normal(67, "w", (384, 256), 0, 0.05)), "bf16")
+    inp = synth.scan_inputs(67, 2, 300, 256, 16, 4, bf16=True)
+    dev = {k: to_dev(v, "bf16" if k in ("x", "dt", "z", "B", "C") else None) for k, v in inp.items()}
+
+    def work():
+        c = ops.gemm(a, w)
+        y = ops.selective_scan(dev["x"], dev["dt"], dev["A"], dev["B"], dev["C"], D=dev["D"], z=dev["z"], conv_w=dev["conv_w"],
+                               variant=_lib.SCAN_DIRECT, seq_splits=2)
+        return c, y
+
+    want_c, want_y = work()
+    torch.cuda.synchronize()
+    results, errors = [None] * 4, []
+
+    def run(i):
+        try:
+            st = torch.cuda.Stream()
+            with torch.cuda.stream(st):
+                for _ in range(5):
+                    results[i] = work()
+            st.synchronize()
+        except Exception as e:  # pragma: no cover - reported below
+            errors.append(e)
+
+    threads = [threading.Thread(target=run, args=(i,)) for i in range(4)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    _status_ok()
+    for c, y in results:
+        assert torch.equal(c, want_c) and torch.equal(y, want_y)
+
+
 # ------------------------------------------------------------------ the whole block
 def test_mamba_block_config0_f32(golden):
     """Benchmark configuration 0: batch 1, L 100, d_model 64, d_state 16, expand 2, conv 4, f32, seed 0."""
