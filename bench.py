@@ -60,6 +60,16 @@ NCU_TRAFFIC_BYTES = {
 }
 
 
+def scan_kernel_name(variant, cfg):
+    """The kernel hx_selective_scan_fwd runs for this variant (HX_SCAN_AUTO: one lane per channel when there are at
+    least 8 warps of chains per SM, the lane-split kernel otherwise)."""
+    if variant == "auto":
+        import torch
+        sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        variant = "direct" if cfg["batch"] * cfg["d_inner"] / 32.0 >= 8.0 * sms else "tiled"
+    return {"direct": "scan_direct_kernel", "simple": "scan_simple_kernel"}.get(variant, "scan_tiled_kernel")
+
+
 def scan_algorithmic_bytes(batch, seq_len, d_inner, d_state, d_conv, es=2):
     """x, dt, z read + y written once; B and C read once; parameters once."""
     pts = batch * seq_len * d_inner
@@ -328,7 +338,7 @@ def run_scan(args, cfg, name):
                        "per_gpu": ("channel shard of %d channels, B and C replicated" % cfg["d_inner"]) if args.shard == "channels"
                        else "full workload on every rank", "l2": "inputs (0.8 GB+) exceed the 126 MB L2, no flush",
                        "variant": args.variant, "lanes_per_channel": args.lpc, "tune": args.tune, "seq_splits": args.splits},
-            "roofline": {"bound": "hbm", "kernel": "scan_tiled_kernel", "achieved": achieved, "peak": peaks["hbm_gbs"],
+            "roofline": {"bound": "hbm", "kernel": scan_kernel_name(args.variant, cfg), "achieved": achieved, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "algorithmic_bytes_per_launch": alg,
                          "traffic": NCU_TRAFFIC_BYTES.get(name) if (args.variant == "auto" and world == 1) else None},
