@@ -307,3 +307,37 @@ def test_full_size_config2_sampled_chains():
                                to_np(Cm[rows]), D=to_np(Dk[sl]), z=to_np(z[rows][:, :, sl]), conv_w=to_np(cw[sl]))
     for lpc, y in outs.items():
         assert rel_l2(to_np(y[rows][:, :, sl]), ref) <= BF16_TOL
+
+
+def test_config4_shard_long_sequences_sampled_chains():
+    """Benchmark configuration 4 as one GPU of eight sees it (channel shard: batch 64, L 16 384, 640 channels,
+    bf16, 5.4 GB): the longest sequences on the path.  AUTO (direct kernel, with and without sequence segments)
+    agrees with the simple kernel everywhere and with the CPU oracle on sampled (batch, channel) chains, and the
+    final states agree too."""
+    import torch
+    from helixml_b200 import _lib, ops
+    Bsz, L, D, N = 64, 16384, 640, 16
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn((Bsz, L, D), device="cuda", generator=g).to(torch.bfloat16)
+    z = torch.randn((Bsz, L, D), device="cuda", generator=g).to(torch.bfloat16)
+    dt = (torch.rand((Bsz, L, D), device="cuda", generator=g) * 3 - 4).to(torch.bfloat16)
+    Bm = torch.randn((Bsz, L, N), device="cuda", generator=g).to(torch.bfloat16)
+    Cm = torch.randn((Bsz, L, N), device="cuda", generator=g).to(torch.bfloat16)
+    A = to_dev((-np.exp(synth.a_log_s4d_real(D, N))).astype(np.float32))
+    Dk = torch.ones(D, device="cuda")
+    cw = to_dev(synth.uniform(4, "conv_w", (D, 4), -0.5, 0.5))
+    base, hb = ops.selective_scan(x, dt, A, Bm, Cm, D=Dk, z=z, conv_w=cw, variant=SIMPLE, return_state=True)
+    outs = {
+        "auto": ops.selective_scan(x, dt, A, Bm, Cm, D=Dk, z=z, conv_w=cw, return_state=True),
+        "direct, 4 segments": ops.selective_scan(x, dt, A, Bm, Cm, D=Dk, z=z, conv_w=cw, variant=DIRECT, seq_splits=4,
+                                                 return_state=True),
+    }
+    assert _lib.device_status() == 0
+    for name, (y, h) in outs.items():
+        assert float((y.float() - base.float()).norm() / base.float().norm()) <= 1e-2, name
+        assert float((h - hb).norm() / hb.norm()) <= 1e-2, name
+    rows, sl = [0, 63], slice(608, 640)  # the last channels of the shard, first and last batch row
+    ref = cbind.selective_scan(to_np(x[rows][:, :, sl]), to_np(dt[rows][:, :, sl]), to_np(A[sl]), to_np(Bm[rows]),
+                               to_np(Cm[rows]), D=to_np(Dk[sl]), z=to_np(z[rows][:, :, sl]), conv_w=to_np(cw[sl]))
+    for name, (y, _) in outs.items():
+        assert rel_l2(to_np(y[rows][:, :, sl]), ref) <= BF16_TOL, name
