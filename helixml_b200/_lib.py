@@ -73,6 +73,7 @@ class MambaStepArgs(C.Structure):
         ("W_out", C.c_void_p), ("conv_w", C.c_void_p), ("conv_b", C.c_void_p), ("b_dt", C.c_void_p),
         ("A", C.c_void_p), ("Dskip", C.c_void_p), ("h", C.c_void_p), ("conv_state", C.c_void_p),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("residual", C.c_void_p), ("norm_w", C.c_void_p), ("norm_eps", C.c_float), ("reserved2", C.c_int32),
     ]
 
 

@@ -467,10 +467,11 @@ size_t MambaBlock::step_workspace_bytes(int64_t batch) const {
 }
 
 Result<Unit> MambaBlock::step_into(const void *x, void *out, int64_t batch, float *h, void *conv_state, void *workspace,
-                                   size_t ws_bytes, void *stream) const {
+                                   size_t ws_bytes, void *stream, float *residual, const float *norm_w, float norm_eps) const {
     hx_mamba_step_args a = step_args(*this, batch);
     a.x = x; a.out = out; a.h = h; a.conv_state = conv_state;
     a.workspace = workspace; a.workspace_bytes = ws_bytes;
+    a.residual = residual; a.norm_w = norm_w; a.norm_eps = norm_eps;
     HELIX_TRY_ABI(hx_mamba_block_step(&a, stream));
     return Unit{};
 }
@@ -665,13 +666,13 @@ Result<Unit> ByteLM::enqueue_step(void *stream) {
     HELIX_TRY_ABI(hx_embedding_fwd(static_cast<const uint8_t *>(dec_->tokens.data()), embedding.data(), (int)dtype, resid, HX_F32,
                                    B, (int)d_model, stream));
     for (size_t l = 0; l < blocks.size(); ++l) {
-        const void *delta = l == 0 ? nullptr : dec_->block_out.data();
-        HELIX_TRY_ABI(hx_rmsnorm_fwd(delta, (int)dtype, resid, static_cast<const float *>(norms[l]->weight.data()),
-                                     dec_->normed.data(), (int)dtype, B, (int)d_model, eps, stream));
-        HELIX_TRY(blocks[l]->step_into(dec_->normed.data(), dec_->block_out.data(), B, static_cast<float *>(dec_->h[l].data()),
-                                       dec_->conv[l].data(), dec_->workspace.data(), (size_t)dec_->workspace.numel(), stream));
+        // residual form: the norm runs inside the step (inside its in_proj kernel on the bf16 path) and the block
+        // output is added into the stream by out_proj
+        HELIX_TRY(blocks[l]->step_into(nullptr, dec_->block_out.data(), B, static_cast<float *>(dec_->h[l].data()),
+                                       dec_->conv[l].data(), dec_->workspace.data(), (size_t)dec_->workspace.numel(), stream,
+                                       resid, static_cast<const float *>(norms[l]->weight.data()), eps));
     }
-    HELIX_TRY_ABI(hx_rmsnorm_fwd(dec_->block_out.data(), (int)dtype, resid, static_cast<const float *>(norm_f.data()),
+    HELIX_TRY_ABI(hx_rmsnorm_fwd(nullptr, (int)dtype, resid, static_cast<const float *>(norm_f.data()),
                                  dec_->normed.data(), (int)dtype, B, (int)d_model, eps, stream));
     if (dtype == DType::BF16 && d_model % 8 == 0)
         HELIX_TRY_ABI(hx_gemm_bf16(dec_->normed.data(), d_model, embedding.data(), d_model, nullptr, dec_->logits.data(), 256,
@@ -680,6 +681,14 @@ Result<Unit> ByteLM::enqueue_step(void *stream) {
         HELIX_TRY_ABI(hx_gemm_simt(dec_->normed.data(), d_model, embedding.data(), d_model, nullptr, dec_->logits.data(), 256,
                                    (int)dtype, (int)dtype, (int)B, 256, (int)d_model, 0, stream));
     return Unit{};
+}
+
+int64_t ByteLM::launches_per_decode_step() const {
+    // embedding + per layer (fused: in_proj with norm and conv step, x_proj, state step, out_proj with the add;
+    // otherwise: norm, in_proj, conv step, x_proj, state step, out_proj, residual add) + final norm + head
+    const int64_t batch = dec_ ? dec_->batch : 1;
+    const int64_t per_layer = (!blocks.empty() && blocks[0]->step_is_fused(batch)) ? 4 : 7;
+    return 1 + (int64_t)blocks.size() * per_layer + 2;
 }
 
 Result<Unit> ByteLM::decode_step_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, void *stream) {

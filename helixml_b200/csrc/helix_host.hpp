@@ -203,8 +203,13 @@ class MambaBlock : public Module {
                               void *conv_state = nullptr, float *residual = nullptr) const;
     size_t workspace_bytes(int64_t batch, int64_t seq_len) const;
     // one decode step: x, out [batch, d_model]; h and conv_state are updated in place
+    // With `residual` (fp32 [batch, d_model]) and `norm_w`: the input is rmsnorm(residual) * norm_w and the output
+    // is added into residual (x may be NULL, out is scratch for the fp32 path).
     Result<Unit> step_into(const void *x, void *out, int64_t batch, float *h, void *conv_state, void *workspace,
-                           size_t workspace_bytes, void *stream) const;
+                           size_t workspace_bytes, void *stream, float *residual = nullptr, const float *norm_w = nullptr,
+                           float norm_eps = 1e-5f) const;
+    // true when a residual-form step runs as four kernels (norm and conv step inside in_proj, add inside out_proj)
+    bool step_is_fused(int64_t batch) const { return dtype == DType::BF16 && d_model % 32 == 0 && batch <= 64 && d_inner % 8 == 0; }
     size_t step_workspace_bytes(int64_t batch) const;
     std::vector<const DeviceTensor *> parameters() const override;
     std::vector<DeviceTensor *> parameters_mut() override;
@@ -242,7 +247,7 @@ class ByteLM : public Module {
     Result<Unit> prefill_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream);
     Result<Unit> decode_step_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, void *stream);
     void set_decode_graph(bool enable) { decode_graph_ = enable; }
-    int64_t launches_per_decode_step() const { return 1 + (int64_t)blocks.size() * 6 + 2; }
+    int64_t launches_per_decode_step() const;
     // per-stage CUDA-event timing (see hx_byte_lm_profile in the C header)
     Result<Unit> set_profile(bool enable);
     Result<Unit> read_profile(float *ms9, int *forwards);

@@ -285,9 +285,11 @@ def mamba_block(x, w: dict, d_state: int, d_conv: int, workspace=None, scan_vari
     return y
 
 
-def mamba_block_step(x, w: dict, d_state: int, d_conv: int, h, conv_state, workspace=None, out=None):
+def mamba_block_step(x, w: dict, d_state: int, d_conv: int, h, conv_state, workspace=None, out=None, residual=None,
+                     norm_w=None, norm_eps=1e-5):
     """One decode step of the block (hx_mamba_block_step): x [B, M]; h [B, E, N] fp32 and conv_state [B, 3, E]
-    (x.dtype) are updated in place."""
+    (x.dtype) are updated in place.  Residual form: residual [B, M] fp32 and norm_w [M] given, x only supplies the
+    dtype: the input is rmsnorm(residual) * norm_w and the output is added into residual."""
     Bsz, M = x.shape
     x = x.contiguous()
     E = w["W_in"].shape[0] // 2
@@ -310,6 +312,8 @@ def mamba_block_step(x, w: dict, d_state: int, d_conv: int, h, conv_state, works
     if h.dtype != torch.float32 or conv_state.dtype != x.dtype:
         raise L.HxError(4, "h must be fp32 and conv_state must have the dtype of x")
     a.h, a.conv_state = h.data_ptr(), conv_state.data_ptr()
+    if residual is not None:
+        a.residual, a.norm_w, a.norm_eps = residual.data_ptr(), _f32(norm_w).data_ptr(), norm_eps
     n = C.c_size_t(0)
     L.check(L.lib().hx_mamba_step_workspace_bytes(C.byref(a), C.byref(n)))
     if workspace is None:

@@ -332,6 +332,14 @@ typedef struct hx_mamba_step_args {
     void *conv_state;         /* [batch, 3, d_inner] io dtype, in/out */
     void *workspace;          /* hx_mamba_step_workspace_bytes() bytes */
     size_t workspace_bytes;
+    /* Residual form (all three or none): the block input is rmsnorm(residual) * norm_w instead of `x`, and the
+     * block output is added into `residual` instead of written to `out` (`x` and `out` may then be NULL).  With
+     * bf16 weights and d_model a multiple of 32 the norm and the conv step run inside the in_proj kernel and the
+     * add inside out_proj: four launches per step instead of six with the norm counted. */
+    float *residual;          /* [batch, d_model] fp32, in/out */
+    const float *norm_w;      /* [d_model] */
+    float norm_eps;
+    int32_t reserved2;
 } hx_mamba_step_args;
 HX_API hx_status hx_mamba_block_step(const hx_mamba_step_args *args, void *stream);
 HX_API hx_status hx_mamba_step_workspace_bytes(const hx_mamba_step_args *args, size_t *bytes);
@@ -396,7 +404,8 @@ HX_API hx_status hx_byte_lm_forward_device(hx_module *m, const uint8_t *tokens_d
  * scan's final state and the conv window; hx_byte_lm_decode_step_device then advances every sequence of that
  * batch by one token: tokens_dev [batch] u8 in, logits_dev [batch, 256] (model dtype) out, state updated in the
  * module.  The first step after a prefill runs as plain launches, the second is captured into a CUDA graph over
- * the module's own step buffers and every later step replays it (1 + 6 per layer + 2 kernels in one launch);
+ * the module's own step buffers and every later step replays it (1 + 4 per layer + 2 kernels in one launch on
+ * the bf16 path: the norm and the conv step run inside in_proj, the residual add inside out_proj);
  * hx_byte_lm_decode_graph(m, 0) keeps plain launches.  The state belongs to the module: one decoding stream per
  * module.  The reference's example has no decode loop (examples/ssm_byte_lm/src/main.rs:423-444 are placeholders). */
 HX_API hx_status hx_byte_lm_prefill_device(hx_module *m, const uint8_t *tokens_dev, void *logits_dev, int64_t batch,

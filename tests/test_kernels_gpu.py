@@ -336,14 +336,14 @@ def test_mamba_block_bf16_direct_scan_with_fused_dt():
     assert rel_l2(outs[0], outs[1]) <= 1e-2  # fused and unfused dt projection agree
 
 
-@pytest.mark.parametrize("dtype,L0,steps", [("f32", 37, 5), ("f32", 2, 4), ("bf16", 150, 6)])
-def test_mamba_block_decode_steps_continue_prefill(dtype, L0, steps):
+@pytest.mark.parametrize("dtype,L0,steps,M", [("f32", 37, 5, 64), ("f32", 2, 4, 64), ("bf16", 150, 6, 64), ("bf16", 60, 4, 128)])
+def test_mamba_block_decode_steps_continue_prefill(dtype, L0, steps, M):
     """Prefill L0 tokens keeping (h, conv window), then `steps` single-token steps: every step's output must be
     the oracle's full-sequence output at that position (the oracle has no step function: it re-runs the block
     over the longer sequence)."""
     import torch
     from helixml_b200 import ops
-    B, M, N, K = 2, 64, 16, 4
+    B, N, K = 2, 16, 4  # d_model 128 gives dt_rank 8 and d_inner 256: the vectorised state-step kernel
     E = 2 * M
     w = synth.mamba_block_weights(7, M, N, K, 2)
     big = ("W_in", "W_x", "W_dt", "W_out")
@@ -375,6 +375,45 @@ def test_mamba_block_decode_steps_continue_prefill(dtype, L0, steps):
     tol = 2e-2 if bf else 1e-4
     assert torch.allclose(cs.float(), cs2.float(), atol=tol, rtol=tol)
     assert (h - h2).abs().max().item() <= tol * (1 + h2.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype,B,M", [("bf16", 2, 64), ("bf16", 33, 128), ("bf16", 5, 96), ("f32", 3, 64)])
+def test_mamba_block_step_residual_form(dtype, B, M):
+    """The residual form of the step (norm inside in_proj, add inside out_proj on the bf16 path) against the plain
+    form fed with an explicit RMSNorm, and against the oracle's norm + block on a one-token sequence."""
+    import torch
+    from helixml_b200 import ops
+    bf = dtype == "bf16"
+    N, K = 16, 4
+    E = 2 * M
+    w = synth.mamba_block_weights(10, M, N, K, 2)
+    big = ("W_in", "W_x", "W_dt", "W_out")
+    wq = {k: (synth.round_bf16(v) if (bf and k in big) else v) for k, v in w.items()}
+    dev = {k: to_dev(v, "bf16" if (bf and k in big) else None) for k, v in wq.items()}
+    td = torch.bfloat16 if bf else torch.float32
+    r0 = synth.normal(10, "resid", (B, M))
+    nw = synth.uniform(10, "nw", (M,), 0.8, 1.2)
+    h0 = synth.normal(10, "h", (B, E, N), 0, 0.1)
+    c0 = synth.normal(10, "cs", (B, 3, E))
+    if bf:
+        c0 = synth.round_bf16(c0)
+    # plain form: explicit norm, then the step, then the add
+    normed = ops.rmsnorm(to_dev(r0), to_dev(nw), 1e-5, out_dtype=td)
+    h_a, cs_a = to_dev(h0), to_dev(c0, "bf16" if bf else None)
+    out = ops.mamba_block_step(normed, dev, N, K, h_a, cs_a)
+    want = r0 + to_np(out)
+    # residual form
+    h_b, cs_b = to_dev(h0), to_dev(c0, "bf16" if bf else None)
+    resid = to_dev(r0)
+    ops.mamba_block_step(torch.empty(B, M, device="cuda", dtype=td), dev, N, K, h_b, cs_b, residual=resid, norm_w=to_dev(nw))
+    _status_ok()
+    got = to_np(resid)
+    if bf:
+        assert rel_l2(got - r0, want - r0) <= BF16_TOL
+        assert rel_l2(to_np(h_b), to_np(h_a)) <= BF16_TOL and rel_l2(to_np(cs_b), to_np(cs_a)) <= BF16_TOL
+    else:
+        assert fp32_tol_err(got, want) <= FP32_TOL
+        assert fp32_tol_err(to_np(h_b), to_np(h_a)) <= FP32_TOL and np.array_equal(to_np(cs_b), to_np(cs_a))
 
 
 def test_mamba_block_step_rejects_bad_arguments():

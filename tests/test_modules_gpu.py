@@ -188,7 +188,7 @@ def test_byte_lm_prefill_then_decode_steps(dtype_name):
         else:
             assert fp32_tol_err(pre.cpu().numpy(), ref[:, :L0]) <= FP32_TOL
             assert fp32_tol_err(got, ref[:, L0:]) <= FP32_TOL
-        assert lm.launches_per_decode_step == 1 + nl * 6 + 2
+        assert lm.launches_per_decode_step == 1 + nl * (4 if bf else 7) + 2
         runs.append(got)
     assert np.array_equal(runs[0], runs[1])  # graph replay and plain launches agree bit for bit
 
