@@ -50,6 +50,8 @@ def check_geometric(A: torch.Tensor) -> bool:
 def probe_pipe(kind: str) -> float:
     """Results per second of one arithmetic pipe on the current GPU: 'fma' (scalar fp32 fused multiply-adds),
     'fma2' (the packed two-wide form, counted per lane) or 'ex2' (special-function exponentials)."""
+    if kind not in ("fma", "fma2", "ex2"):
+        raise L.HxError(10, f"unknown probe {kind!r}")
     code = {"fma": 0, "fma2": 1, "ex2": 2}[kind]
     sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
     scratch = torch.empty(sms * 8 * 256, device="cuda", dtype=torch.float32)

@@ -249,6 +249,22 @@ def test_mamba_block_adds_into_residual(dtype):
         assert fp32_tol_err(to_np(resid), ref) <= FP32_TOL
 
 
+def test_pipe_probes_report_plausible_rates():
+    """hx_probe_pipe: the rates the benchmark divides by.  A B200 retires about 128 fp32 FMAs and 16 ex2 results per
+    clock and SM; anything within a factor of two of that on the device under test is accepted, and the packed form
+    must not be slower per lane than the scalar one."""
+    import torch
+    from helixml_b200 import _lib, ops
+    props = torch.cuda.get_device_properties(0)
+    per_clk = props.multi_processor_count * 1.0e9  # at 1 GHz; real clocks are 1.5-2 GHz
+    fma, fma2, ex2 = ops.probe_pipe("fma"), ops.probe_pipe("fma2"), ops.probe_pipe("ex2")
+    assert 64 * per_clk < fma < 2 * 128 * 2.2 * per_clk
+    assert 8 * per_clk < ex2 < 2 * 16 * 2.2 * per_clk
+    assert fma2 >= 0.9 * fma
+    with pytest.raises(_lib.HxError):
+        ops.probe_pipe("fma3")
+
+
 def test_four_threads_call_concurrently():
     """The reference's 4-thread concurrent matmul test (crates/backend-cpu/tests/integration_tests.rs:68-99) at this
     boundary: four host threads, each on its own stream, run the tensor-core GEMM and the fused scan at the same
