@@ -306,7 +306,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             int v;
             asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.flags + fidx) : "memory");
             if (v == p.epoch) { ok = true; break; }
-            __nanosleep(200);
+            __nanosleep(40);
         }
         if (!ok) {
             if (lane == 0) atomicOr(&g_wait_status, kWaitCarry);
