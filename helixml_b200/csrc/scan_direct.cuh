@@ -351,7 +351,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             }
         }
 
-#pragma unroll 4
+#pragma unroll 8
         for (int t = 0; t < steps; ++t) {
             float xc[CPL], dr[CPL], zr[CPL];
             if constexpr (CPL == 2) {
