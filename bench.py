@@ -55,7 +55,7 @@ def measured_peaks():
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (same workload as the benchmark, one launch each).
 NCU_TRAFFIC_BYTES = {
-    "lm_cfg3": 610_989_568,    # profiles/scan_direct_kernel_lm_cfg3.md: 413.7 MB + 197.3 MB
+    "lm_cfg3": 608_549_120,    # profiles/scan_direct_kernel_lm_cfg3.md: 413.6 MB + 194.9 MB
     "scan_cfg2": 791_900_000,  # profiles/scan_tiled_kernel_cfg2.md: 608.9 MB + 182.9 MB
 }
 
