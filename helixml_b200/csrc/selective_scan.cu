@@ -1052,6 +1052,12 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
             return launch_direct_inst<__nv_bfloat16, 2, true, true, 3>(p, maps, grid, st, a->y, a->y_batch_stride, a->y_row_stride);
         return launch_direct_inst<__nv_bfloat16, 1, true, true, 3>(p, maps, grid, st, a->y, a->y_batch_stride, a->y_row_stride);
     }
+    if (bf && geom && !p.z_gate && a->conv_w == nullptr && a->z != nullptr && a->dt_softplus != 0) {
+        // the block's configuration with dt read from memory: compile-time flags as in the fused form
+        if (cpl == 2)
+            return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, false, false, true>(p, maps, grid, st, a->y, a->y_batch_stride, a->y_row_stride);
+        return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, false, false, true>(p, maps, grid, st, a->y, a->y_batch_stride, a->y_row_stride);
+    }
     if (bf) {
         if (cpl == 2) HX_DIRECT_CASE(__nv_bfloat16, 2);
         HX_DIRECT_CASE(__nv_bfloat16, 1);
