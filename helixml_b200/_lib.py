@@ -10,7 +10,7 @@ LIB_PATH = os.path.join(_HERE, "libhelix_b200.so")
 
 HX_OK = 0
 HX_F32, HX_BF16, HX_U8 = 0, 1, 2
-SCAN_AUTO, SCAN_SIMPLE, SCAN_TILED, SCAN_SEQSPLIT, SCAN_DIRECT = 0, 1, 2, 3, 4
+SCAN_AUTO, SCAN_SIMPLE, SCAN_TILED, SCAN_SEQSPLIT, SCAN_DIRECT, SCAN_LOOKBACK = 0, 1, 2, 3, 4, 5
 EPI_NONE, EPI_SILU, EPI_SOFTPLUS, EPI_SILU_FAST = 0, 1, 2, 3
 
 STATUS_NAMES = ["Ok", "ShapeMismatch", "InvalidDimension", "DeviceMismatch", "DTypeMismatch", "UnsupportedOperation",

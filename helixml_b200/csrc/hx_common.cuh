@@ -45,6 +45,13 @@ int sm_count();
 // resid[i] += x[i] (x fp32 or bf16): the residual update where no GEMM epilogue can do it.
 hx_status residual_add(float *resid, const void *x, int x_dtype, int64_t n, cudaStream_t st);
 
+// The kernel HX_SCAN_AUTO picks for a d_state == 16 problem on the current device (selective_scan.cu); the Mamba
+// block plans its launches and its workspace with the same rule.
+namespace scan {
+enum class ScanKind { Tiled, Direct, LookBack };
+ScanKind auto_kind(const hx_scan_args *a);
+}  // namespace scan
+
 // Translation units with bounded device-side waits keep a status word each; these read (and
 // optionally clear) them.  hx_device_status() ORs them together.
 hx_status read_status_scan(int *v, bool clear);

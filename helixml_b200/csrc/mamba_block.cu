@@ -21,6 +21,8 @@ static hx_scan_args scan_shape(const hx_mamba_block_args *a) {
     memset(&sa, 0, sizeof(sa));
     sa.batch = a->batch; sa.seq_len = a->seq_len; sa.d_inner = a->d_inner; sa.d_state = a->d_state;
     sa.io_dtype = a->io_dtype; sa.variant = a->scan_variant;
+    // the block's scan call: u already convolved, gate and softplus present
+    sa.a_geometric = a->a_geometric; sa.dt_softplus = 1; sa.z = a->x;  // (z only has to be non-NULL for planning)
     return sa;
 }
 
@@ -39,6 +41,9 @@ static Layout plan(const hx_mamba_block_args *a) {
     l.y = off; off += up(T * E * es);
     // carries of a split scan (the split evens out the load; see hx_selective_scan_suggest_splits)
     hx_scan_args sa = scan_shape(a);
+    // variants that chain their segments are planned as such (the parallel-segment suggestion is for the look-back form)
+    if (a->scan_variant == HX_SCAN_TILED || a->scan_variant == HX_SCAN_SEQSPLIT || a->scan_variant == HX_SCAN_DIRECT)
+        sa.a_geometric = 0;
     l.splits = (a->scan_variant == HX_SCAN_SIMPLE || a->d_state != 16) ? 1 : hx_selective_scan_suggest_splits(&sa);
     sa.seq_splits = l.splits;
     l.scan_ws_bytes = 0;
@@ -60,13 +65,21 @@ static hx_status validate(const hx_mamba_block_args *a) {
     return HX_OK;
 }
 
-// True when the dt projection runs inside the scan kernel instead of as a GEMM of its own.
-static bool fuses_dt(const hx_mamba_block_args *a, int W) {
+// True when the dt projection runs inside the scan kernel instead of as a GEMM of its own: bf16, d_state 16,
+// a rank the kernel's operand tiles hold, every operand meeting the TMA rules of the scan's tensor maps (rows of
+// d_inner and of the x_proj output a multiple of 16 bytes, W_dt 16-byte aligned), and a scan variant that runs the
+// one-lane-per-channel kernel (chained or look-back).
+static bool fuses_dt(const hx_mamba_block_args *a, int W, int splits) {
     const int R = a->dt_rank;
-    const double chains = (double)a->batch * a->d_inner;
-    return a->io_dtype == HX_BF16 && a->d_state == 16 && R >= 8 && R <= 64 && R % 8 == 0 && W % 8 == 0 &&
-           (a->scan_variant == HX_SCAN_DIRECT ||
-            (a->scan_variant == HX_SCAN_AUTO && chains / 32.0 >= 8.0 * hx::sm_count()));
+    if (!(a->io_dtype == HX_BF16 && a->d_state == 16 && R >= 8 && R <= 64 && R % 8 == 0 && W % 8 == 0 &&
+          a->d_inner % 8 == 0 && (reinterpret_cast<uintptr_t>(a->W_dt) & 15) == 0))
+        return false;
+    if (a->scan_variant == HX_SCAN_DIRECT) return true;
+    if (a->scan_variant == HX_SCAN_LOOKBACK) return a->a_geometric != 0;
+    if (a->scan_variant != HX_SCAN_AUTO) return false;
+    hx_scan_args sa = scan_shape(a);
+    sa.seq_splits = splits;
+    return hx::scan::auto_kind(&sa) != hx::scan::ScanKind::Tiled;
 }
 
 }  // namespace block
@@ -87,7 +100,19 @@ hx_status hx_mamba_block_kernel_launches(const hx_mamba_block_args *a, int32_t *
     hx_status s = hx::block::validate(a);
     if (s != HX_OK) return s;
     // in_proj, conv, x_proj, dt_proj (unless fused into the scan), scan, out_proj
-    *launches = (a->batch == 0 || a->seq_len == 0) ? 0 : (hx::block::fuses_dt(a, (int)hx::block::plan(a).W) ? 5 : 6);
+    if (a->batch == 0 || a->seq_len == 0) {
+        *launches = 0;
+        return HX_OK;
+    }
+    const hx::block::Layout l = hx::block::plan(a);
+    const bool fused = hx::block::fuses_dt(a, (int)l.W, l.splits);
+    // the look-back scan is two launches (aggregate pass, output pass)
+    hx_scan_args sa = hx::block::scan_shape(a);
+    sa.seq_splits = l.splits;
+    const bool lookback = l.splits > 1 && a->d_state == 16 &&
+                          (a->scan_variant == HX_SCAN_LOOKBACK ||
+                           (a->scan_variant == HX_SCAN_AUTO && hx::scan::auto_kind(&sa) == hx::scan::ScanKind::LookBack));
+    *launches = (fused ? 5 : 6) + (lookback ? 1 : 0);
     return HX_OK;
 }
 
@@ -148,7 +173,7 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     // 4. dt_lin = dt_low W_dt^T                          [T, E]   (bias and softplus happen inside the scan)
     // With bf16 operands and enough chains for the one-lane-per-channel scan, the projection is done inside the
     // scan kernel (its producer warp, tensor cores) and this GEMM, its 2*T*E-byte write and read disappear.
-    const bool fuse_dt = fuses_dt(a, W);
+    const bool fuse_dt = fuses_dt(a, W, l.splits);
     if (!fuse_dt && (s = gemm(dbc, W, a->W_dt, R, dtl, E, (int)T, E, R)) != HX_OK) return s;
     mark(4);
     // 5. fused scan on strided views

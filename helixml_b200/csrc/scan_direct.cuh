@@ -17,14 +17,27 @@
 // fp32 once per CTA.  y needs no staging: each step a warp writes one contiguous run of 32*CPL channels
 // straight from registers.  Bounded waits, carry hand-over for split sequences and the status word are those
 // of scan_tiled_kernel.
+//
+// Split sequences come in two forms.  MODE 0 chains the segments: segment s+1 starts from the state segment s
+// hands over (carry + flag), so the segments of one chain run one after the other; that evens out the load when
+// chains are plentiful.  MODES 1 and 2 are the look-back form for few chains (geometric A only), two launches in
+// stream order with no flag between CTAs:
+//   MODE 1, the aggregate pass, runs segments 0 .. S-2 at the same time, each from a zero state and backwards in
+//           time: with w_t = exp2(A0 * sum_{tau > t} dt_tau) the end state is q[n] = sum_t (dt_t u_t w_t^(n+1)) B_t[n],
+//           i.e. one multiply for the power (the input is folded into the chain of powers) and one FMA per state,
+//           no C contraction, no gate, no output.  It writes q and sum(dt) per (segment, chain).
+//   MODE 2, the output pass, runs all S segments at the same time: a segment first folds the aggregates of its
+//           predecessors, h <- exp(A sum dt_j) h + q_j for j = 0 .. s-1 (the look-back), then scans its steps
+//           with outputs like MODE 0.
 #pragma once
 
 namespace hx {
 namespace scan {
 
 template <typename T, int CPL_, bool GEOM_, bool STD_, int STAGES_, bool FUSEDT_ = false, bool ZGATE_ = false,
-          bool BLOCK_ = false>
+          bool BLOCK_ = false, int MODE_ = 0>
 struct DirectCfg {
+    static constexpr int MODE = MODE_;                 // 0 chained segments, 1 aggregate pass, 2 output pass (see above)
     static constexpr bool BLOCK = BLOCK_;              // the Mamba block's call: no conv (u is given), gate and softplus
                                                        // present, all known at compile time
     static constexpr bool ZGATE = ZGATE_;              // z is known at compile time to hold silu(z) already
@@ -60,6 +73,7 @@ struct DirectCfg {
     static_assert(WC * ES <= 128, "a warp's channels must fit one 128-byte box");
     static_assert(3 * STAGES + 1 <= 16, "barrier area too small");
     static_assert(!FUSEDT || sizeof(T) == 2, "the fused dt projection takes bf16 operands");
+    static_assert(MODE == 0 || GEOM, "the look-back passes need geometric A");
 };
 
 template <typename T> __device__ __forceinline__ float2 ld_chan2(const char *p);  // two adjacent channels
@@ -84,7 +98,8 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     constexpr int CPL = Cfg::CPL, TC = Cfg::TC, STAGES = Cfg::STAGES, NW = Cfg::NWARP, NB = Cfg::NB, ES = Cfg::ES;
     constexpr bool GEOM = Cfg::GEOM, FAST = Cfg::FAST, STD = Cfg::STD, FUSEDT = Cfg::FUSEDT;
     constexpr bool BLOCK = Cfg::BLOCK;
-    const bool has_conv = !BLOCK && (STD || p.K > 0), has_z = STD || BLOCK || p.has_z,
+    constexpr int MODE = Cfg::MODE;
+    const bool has_conv = !BLOCK && (STD || p.K > 0), has_z = MODE != 1 && (STD || BLOCK || p.has_z),
                use_softplus = STD || BLOCK || p.dt_softplus;
     const bool z_gate = Cfg::ZGATE || p.z_gate;
 
@@ -136,8 +151,9 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             tma_prefetch_desc(&tm_C);
             if (has_z) tma_prefetch_desc(&tm_z);
         }
+        // the aggregate pass reads neither z nor C
         const uint32_t stage_tx = live_boxes * ((TC + 3) * 128 + TC * 128 * ((has_z ? 1 : 0) + (FUSEDT ? 0 : 1))) +
-                                  2 * TC * 16 * ES + Cfg::DTLOW_BYTES;
+                                  (MODE == 1 ? 1 : 2) * TC * 16 * ES + Cfg::DTLOW_BYTES;
         if constexpr (FUSEDT) {
             if (lane == 0) {
                 tma_prefetch_desc(&tm_dtlow);
@@ -148,7 +164,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         }
         auto issue = [&](int i) {
             const int s = i % STAGES;
-            const int t0 = t_seg0 + i * TC;
+            const int t0 = t_seg0 + (MODE == 1 ? nchunks - 1 - i : i) * TC;  // the aggregate pass walks backwards
             const uint32_t sb = smem_u32(stage_base + s * Cfg::STAGE_BYTES);
             mbar_expect_tx(bar_full(s), stage_tx);
             for (int bx = 0; bx < live_boxes; ++bx) {
@@ -160,7 +176,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             }
             if constexpr (FUSEDT) tma_load_3d(sb + OFF_DTLOW, &tm_dtlow, bar_full(s), 0, t0, b);
             tma_load_3d(sb + OFF_BC, &tm_B, bar_full(s), 0, t0, b);
-            tma_load_3d(sb + OFF_C, &tm_C, bar_full(s), 0, t0, b);
+            if constexpr (MODE != 1) tma_load_3d(sb + OFF_C, &tm_C, bar_full(s), 0, t0, b);
         };
         int issued = 0;
         for (; issued < STAGES && issued < nchunks; ++issued)
@@ -222,6 +238,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 for (int r = 0; r < ROUNDS; ++r) {
                     const int e0 = (r * 32 + lane) * 8;
                     const int arr = e0 / (TC * 16), ea = e0 % (TC * 16);
+                    if (MODE == 1 && arr) continue;  // C is not loaded in the aggregate pass
                     const char *src = st + (arr ? OFF_C : OFF_BC) + ea * ES;
                     float *dst = reinterpret_cast<float *>(st + (arr ? OFF_CF : OFF_BF)) + ea;
                     if constexpr (ES == 2) {
@@ -299,7 +316,144 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll
         for (int j = 0; j < 8; ++j) h[e][j] = make_float2(0.f, 0.f);
 
-    if (p.n_segments > 1 && seg > 0) {
+    if constexpr (MODE == 1) {
+        // ============================================================ aggregate pass (look-back form)
+        // End state of this segment from a zero state, walking backwards: w = exp2(A0 * (sum of dt after t)) is the
+        // decay from step t to the end of the segment, and q[n] += (dt_t u_t w^(n+1)) B_t[n].
+        float sacc[CPL];
+        float2 q[CPL][8];
+#pragma unroll
+        for (int e = 0; e < CPL; ++e) {
+            sacc[e] = 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) q[e][j] = make_float2(0.f, 0.f);
+        }
+        for (int i = 0; i < nchunks; ++i) {
+            const int s = i % STAGES;
+            const int c = nchunks - 1 - i;
+            if (!mbar_wait(bar_ready(s), (i / STAGES) & 1)) {
+                if (lane == 0) atomicOr(&g_wait_status, kWaitFull);
+                return;
+            }
+            const char *sbox = stage_base + s * Cfg::STAGE_BYTES + OFF_BOX0 + box * Cfg::BOX_BYTES;
+            const char *sx = sbox + lane_byte;  // row r = step r - 3 of the chunk
+            const char *sd = sbox + OFF_DTT + (FUSEDT ? (lane_byte / ES) * 4 : lane_byte);
+            constexpr int DROW = Cfg::DTROW;
+            const float4 *sBf = reinterpret_cast<const float4 *>(stage_base + s * Cfg::STAGE_BYTES + OFF_BF);
+            const int steps = min(TC, t_seg1 - (t_seg0 + c * TC));
+            // conv window for the walk backwards: x of the three steps that follow the row read next
+            float xa[CPL], xb[CPL], xc3[CPL];
+#pragma unroll
+            for (int e = 0; e < CPL; ++e) {
+                xa[e] = ld_chan1<T>(sx + (steps + 2) * 128 + e * ES);
+                xb[e] = ld_chan1<T>(sx + (steps + 1) * 128 + e * ES);
+                xc3[e] = ld_chan1<T>(sx + steps * 128 + e * ES);
+            }
+#pragma unroll 8
+            for (int tt = 0; tt < steps; ++tt) {
+                const int t = steps - 1 - tt;
+                float xn[CPL], dr[CPL];
+#pragma unroll
+                for (int e = 0; e < CPL; ++e) {
+                    xn[e] = ld_chan1<T>(sx + t * 128 + e * ES);  // x three steps before step t
+                    if constexpr (FUSEDT) dr[e] = *reinterpret_cast<const float *>(sd + t * DROW + e * 4);
+                    else dr[e] = ld_chan1<T>(sd + t * DROW + e * ES);
+                }
+                float4 Bv[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) Bv[k] = sBf[t * 4 + k];
+#pragma unroll
+                for (int e = 0; e < CPL; ++e) {
+                    float u;
+                    if (has_conv) {
+                        float cv = cb_[e];
+                        cv = fmaf(w_[e][0], xn[e], cv);
+                        cv = fmaf(w_[e][1], xc3[e], cv);
+                        cv = fmaf(w_[e][2], xb[e], cv);
+                        cv = fmaf(w_[e][3], xa[e], cv);
+                        u = silu_sel<FAST>(cv);
+                    } else {
+                        u = xa[e];
+                    }
+                    xa[e] = xb[e]; xb[e] = xc3[e]; xc3[e] = xn[e];
+                    const float v = dr[e] + db_[e];
+                    float dtv;
+                    if (use_softplus) {
+                        if constexpr (FAST) {
+                            const float sp = kLn2 * lg2_approx(1.f + ex2_approx(v * kLog2e));
+                            dtv = v > 20.f ? v : sp;
+                        } else {
+                            dtv = softplus_acc(v);
+                        }
+                    } else {
+                        dtv = v;
+                    }
+                    const float xin = dtv * u;
+                    float r;
+                    if constexpr (FAST) r = ex2_approx(sacc[e] * a0_[e]);
+                    else r = exp2f(sacc[e] * a0_[e]);
+                    sacc[e] += dtv;
+                    const float r2 = r * r, r4 = r2 * r2, r8 = r4 * r4;
+                    float2 a[8];
+                    a[0] = mul2(make_float2(r, r2), splat2(xin));
+                    a[1] = mul2(a[0], splat2(r2));
+                    a[2] = mul2(a[0], splat2(r4));
+                    a[3] = mul2(a[1], splat2(r4));
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) a[4 + j] = mul2(a[j], splat2(r8));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        q[e][2 * k] = fma2(a[2 * k], make_float2(Bv[k].x, Bv[k].y), q[e][2 * k]);
+                        q[e][2 * k + 1] = fma2(a[2 * k + 1], make_float2(Bv[k].z, Bv[k].w), q[e][2 * k + 1]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty(s));
+        }
+#pragma unroll
+        for (int e = 0; e < CPL; ++e) {
+            if (dch + e >= p.D) continue;
+            const int64_t ci = ((int64_t)seg * p.B + b) * p.D + dch + e;
+            float2 *dst = reinterpret_cast<float2 *>(p.carry + ci * 16);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) dst[j] = q[e][j];
+            p.sdt[ci] = sacc[e];
+        }
+        return;
+    }
+
+    if constexpr (MODE == 2) {
+        // ============================================================ look-back: fold the predecessors' aggregates
+        if (seg > 0) {
+#pragma unroll
+            for (int e = 0; e < CPL; ++e) {
+                if (dch + e >= p.D) continue;
+                const int64_t c0 = (int64_t)b * p.D + dch + e, cs = (int64_t)p.B * p.D;
+                const float2 *q0 = reinterpret_cast<const float2 *>(p.carry + c0 * 16);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) h[e][j] = q0[j];  // segment 0 starts from zero: its aggregate is its end state
+                for (int js = 1; js < seg; ++js) {
+                    const float sd = p.sdt[c0 + js * cs];
+                    float r;
+                    if constexpr (FAST) r = ex2_approx(sd * a0_[e]);
+                    else r = exp2f(sd * a0_[e]);
+                    float2 a[8];
+                    a[0] = make_float2(r, r * r);
+                    a[1] = mul2(a[0], splat2(a[0].y));
+                    a[2] = mul2(a[0], splat2(a[1].y));
+                    a[3] = mul2(a[1], splat2(a[1].y));
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) a[4 + j] = mul2(a[j], splat2(a[3].y));
+                    const float2 *qj = reinterpret_cast<const float2 *>(p.carry + (c0 + js * cs) * 16);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) h[e][j] = fma2(a[j], h[e][j], qj[j]);
+                }
+            }
+        }
+    }
+
+    if (MODE == 0 && p.n_segments > 1 && seg > 0) {
         const int fidx = (((seg - 1) * p.B + b) * gridDim.x + tile) * 8 + warp;
         bool ok = false;
         for (int it = 0; it < (1 << 22); ++it) {
@@ -472,13 +626,13 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         if (dch + e >= p.D) continue;
         float2 *dst = nullptr;
         if (last_seg && p.h_last) dst = reinterpret_cast<float2 *>(p.h_last + ((int64_t)b * p.D + dch + e) * 16);
-        if (!last_seg) dst = reinterpret_cast<float2 *>(p.carry + (((int64_t)seg * p.B + b) * p.D + dch + e) * 16);
+        if (MODE == 0 && !last_seg) dst = reinterpret_cast<float2 *>(p.carry + (((int64_t)seg * p.B + b) * p.D + dch + e) * 16);
         if (dst) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) dst[j] = h[e][j];
         }
     }
-    if (!last_seg) {
+    if (MODE == 0 && !last_seg) {
         __threadfence();
         __syncwarp();
         if (lane == 0) {

@@ -131,6 +131,8 @@ struct TiledParams {
     int *flags;       // [n_segments-1, B, tiles, 8] one per consumer warp, set to `epoch` once its carry is written
     int epoch;
     int dt_rank;      // > 0: dt is produced in the kernel from dt_low and W_dt (direct kernel only)
+    float *sdt;       // look-back form: [n_segments-1, B, D] sum of dt over each segment (its aggregate decay is
+                      // exp(A * sdt)); `carry` then holds the segments' end states from a zero state
 };
 
 template <typename T, int LPC_, bool GEOM_, int TC_, int STAGES_, bool STD_>
@@ -750,18 +752,32 @@ static void seg_plan(const hx_scan_args *a, int chunk, int *n_seg, int *seg_len)
 }
 
 constexpr int kChunkBf16 = 32, kChunkF32 = 32;
+constexpr int kPlanChunk = 32;  // segment lengths are multiples of this
 
 static int tiles_of(const hx_scan_args *a) {
     const int DT = a->io_dtype == HX_BF16 ? 64 : 32;
     return (a->d_inner + DT - 1) / DT;
 }
 
-static size_t workspace_bytes(const hx_scan_args *a, int n_seg) {
-    if (n_seg <= 1) return 0;
-    const size_t carry = (size_t)(n_seg - 1) * a->batch * a->d_inner * 16 * sizeof(float);
-    const size_t flags = (size_t)(n_seg - 1) * a->batch * tiles_of(a) * 8 * sizeof(int);
-    return (carry + 255) / 256 * 256 + (flags + 255) / 256 * 256 + 256;
+// Workspace of a split scan, one layout for every form: the per-segment states (chained form: the carries;
+// look-back form: the aggregates), the chained form's flags, the look-back form's sums of dt.
+struct WsLayout {
+    size_t carry, flags, sdt, total;  // byte offsets from the 256-aligned base; total includes the alignment slack
+    size_t flag_bytes;
+};
+static WsLayout ws_layout(const hx_scan_args *a, int n_seg) {
+    WsLayout l{0, 0, 0, 0, 0};
+    if (n_seg <= 1) return l;
+    auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+    const size_t chains = (size_t)(n_seg - 1) * a->batch * a->d_inner;
+    l.flag_bytes = (size_t)(n_seg - 1) * a->batch * tiles_of(a) * 8 * sizeof(int);
+    l.carry = 0;
+    l.flags = up(chains * 16 * sizeof(float));
+    l.sdt = l.flags + up(l.flag_bytes);
+    l.total = l.sdt + up(chains * sizeof(float)) + 256;
+    return l;
 }
+static size_t workspace_bytes(const hx_scan_args *a, int n_seg) { return ws_layout(a, n_seg).total; }
 
 template <typename T, int LPC, bool GEOM, int TC, int STAGES, bool STD>
 static hx_status launch_tiled_inst(const hx_scan_args *a, const TiledParams &p, const CUtensorMap *maps, dim3 grid,
@@ -798,11 +814,14 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
     const bool bf = a->io_dtype == HX_BF16;
     // `reserved` picks another (chunk, stages) pair for the bf16 / geometric / standard path (tuning knob)
     const bool stdp0 = a->conv_w != nullptr && a->z != nullptr && a->dt_softplus != 0;
-    const int tune = (bf && a->a_geometric && stdp0) ? a->reserved : 0;
+    // only 1 and 2 name a tuning variant; anything else (the direct kernel's selector among them) is the default
+    const int tune = (bf && a->a_geometric && stdp0 && (a->reserved == 1 || a->reserved == 2)) ? a->reserved : 0;
     const int ES = bf ? 2 : 4, DT = 128 / ES, TC = tune >= 1 ? 16 : (bf ? kChunkBf16 : kChunkF32);
     const int tiles = (a->d_inner + DT - 1) / DT;
     int n_seg = 1, seg_len = (a->seq_len + TC - 1) / TC * TC;
-    if (split) seg_plan(a, TC, &n_seg, &seg_len);
+    // segments are planned on 32-step chunks whatever the kernel's own chunk (16 or 32), so that the size query
+    // and every launcher agree on the plan
+    if (split) seg_plan(a, kPlanChunk, &n_seg, &seg_len);
 
     TiledParams p;
     p.B = a->batch; p.L = a->seq_len; p.D = a->d_inner;
@@ -813,17 +832,16 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
     p.n_segments = n_seg; p.seg_len = seg_len;
     p.A = a->A; p.Dskip = a->Dskip; p.conv_w = a->conv_w; p.conv_b = a->conv_b; p.dt_bias = a->dt_bias;
     p.h_last = a->h_last;
-    p.carry = nullptr; p.flags = nullptr; p.epoch = 1; p.dt_rank = 0;
+    p.carry = nullptr; p.flags = nullptr; p.epoch = 1; p.dt_rank = 0; p.sdt = nullptr;
     if (n_seg > 1) {
-        const size_t need = workspace_bytes(a, n_seg);
-        HX_REQUIRE(a->workspace && a->workspace_bytes >= need, HX_ERR_INVALID_INPUT,
-                   "HX_SCAN_SEQSPLIT needs a workspace of %zu bytes (got %zu)", need, a->workspace_bytes);
+        const WsLayout wl = ws_layout(a, n_seg);
+        HX_REQUIRE(a->workspace && a->workspace_bytes >= wl.total, HX_ERR_INVALID_INPUT,
+                   "the sequence-split scan needs a workspace of %zu bytes (got %zu)", wl.total, a->workspace_bytes);
         char *ws = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(a->workspace) + 255) & ~uintptr_t(255));
-        const size_t carry = ((size_t)(n_seg - 1) * a->batch * a->d_inner * 16 * sizeof(float) + 255) / 256 * 256;
-        p.carry = reinterpret_cast<float *>(ws);
-        p.flags = reinterpret_cast<int *>(ws + carry);
+        p.carry = reinterpret_cast<float *>(ws + wl.carry);
+        p.flags = reinterpret_cast<int *>(ws + wl.flags);
         // flags are compared against a per-launch epoch, so they are cleared on every call
-        HX_CUDA(cudaMemsetAsync(p.flags, 0, (size_t)(n_seg - 1) * a->batch * tiles * 8 * sizeof(int), st));
+        HX_CUDA(cudaMemsetAsync(p.flags, 0, wl.flag_bytes, st));
     }
 
     // tensor maps: x/dt/z/y are [B, L, D] with D innermost; B/C are [B, L, 16]
@@ -903,10 +921,11 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
 }
 
 
-template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2, bool FUSEDT = false, bool ZGATE = false, bool BLOCK = false>
+template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2, bool FUSEDT = false, bool ZGATE = false, bool BLOCK = false,
+          int MODE = 0>
 static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *maps, dim3 grid, cudaStream_t st, void *y,
                                     int64_t y_bs, int64_t y_rs) {
-    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES, FUSEDT, ZGATE, BLOCK>;
+    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES, FUSEDT, ZGATE, BLOCK, MODE>;
     auto kern = scan_direct_kernel<T, Cfg>;
     static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice is harmless
     int dev = 0;
@@ -920,6 +939,17 @@ static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *map
     return check_launch("scan_direct_kernel");
 }
 
+// The two launches of the look-back form: the aggregate pass over segments 0 .. S-2, then the output pass over
+// all S segments (stream order is the only dependency between them).
+template <typename T, bool STD, bool FUSEDT, bool BLOCK>
+static hx_status launch_lookback_pair(const TiledParams &p, const CUtensorMap *maps, dim3 grid, cudaStream_t st, void *y,
+                                      int64_t y_bs, int64_t y_rs) {
+    dim3 g1(grid.x, grid.y, grid.z - 1);
+    hx_status s = launch_direct_inst<T, 1, true, STD, 2, FUSEDT, false, BLOCK, 1>(p, maps, g1, st, y, y_bs, y_rs);
+    if (s != HX_OK) return s;
+    return launch_direct_inst<T, 1, true, STD, 2, FUSEDT, false, BLOCK, 2>(p, maps, grid, st, y, y_bs, y_rs);
+}
+
 // channels per lane for the direct kernel: 2 when that still leaves about two warps per scheduler
 static int choose_cpl(const hx_scan_args *a) {
     if (a->io_dtype != HX_BF16) return 1;
@@ -928,15 +958,27 @@ static int choose_cpl(const hx_scan_args *a) {
     return chains / 64.0 >= 8.0 * sm_count() ? 2 : 1;
 }
 
-static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t st) {
+// What the look-back form supports: geometric A, and where the dt projection is fused the block's configuration.
+static bool lookback_ok(const hx_scan_args *a) {
+    if (a->d_state != 16 || !a->a_geometric || a->z_is_gate) return false;
+    if (a->W_dt) return a->conv_w == nullptr && a->z != nullptr && a->dt_softplus != 0;
+    return true;
+}
+
+// form: 0 = one pass (segments, if any, chained through carries), 1 = look-back (aggregate pass + output pass)
+static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t st, int form = 0) {
     HX_REQUIRE(a->d_state == 16, HX_ERR_UNSUPPORTED_OPERATION, "the direct scan needs d_state == 16 (got %d)", a->d_state);
     const bool bf = a->io_dtype == HX_BF16;
     const int ES = bf ? 2 : 4, BOXC = 128 / ES, TC = 16;
-    const int cpl = choose_cpl(a);
+    if (form == 1)
+        HX_REQUIRE(lookback_ok(a), HX_ERR_UNSUPPORTED_OPERATION,
+                   "the look-back scan needs a_geometric = 1 (and, with a fused dt projection, the block's configuration)");
+    const int cpl = form == 1 ? 1 : choose_cpl(a);
     const int DT = bf ? (cpl == 2 ? 256 : 128) : 128;  // channels per CTA (4 consumer warps)
     const int tiles = (a->d_inner + DT - 1) / DT;
     int n_seg = 1, seg_len = (a->seq_len + TC - 1) / TC * TC;
-    if (split) seg_plan(a, bf ? kChunkBf16 : kChunkF32, &n_seg, &seg_len);
+    if (split) seg_plan(a, kPlanChunk, &n_seg, &seg_len);
+    if (n_seg <= 1) form = 0;
 
     TiledParams p;
     p.B = a->batch; p.L = a->seq_len; p.D = a->d_inner;
@@ -947,17 +989,19 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
     p.n_segments = n_seg; p.seg_len = seg_len;
     p.A = a->A; p.Dskip = a->Dskip; p.conv_w = a->conv_w; p.conv_b = a->conv_b; p.dt_bias = a->dt_bias;
     p.h_last = a->h_last;
-    p.carry = nullptr; p.flags = nullptr; p.epoch = 1;
+    p.carry = nullptr; p.flags = nullptr; p.epoch = 1; p.sdt = nullptr;
     p.dt_rank = a->W_dt ? a->dt_rank : 0;
     if (n_seg > 1) {
-        const size_t need = workspace_bytes(a, n_seg);
-        HX_REQUIRE(a->workspace && a->workspace_bytes >= need, HX_ERR_INVALID_INPUT,
-                   "the sequence-split scan needs a workspace of %zu bytes (got %zu)", need, a->workspace_bytes);
+        const WsLayout wl = ws_layout(a, n_seg);
+        HX_REQUIRE(a->workspace && a->workspace_bytes >= wl.total, HX_ERR_INVALID_INPUT,
+                   "the sequence-split scan needs a workspace of %zu bytes (got %zu)", wl.total, a->workspace_bytes);
         char *ws = reinterpret_cast<char *>((reinterpret_cast<uintptr_t>(a->workspace) + 255) & ~uintptr_t(255));
-        const size_t carry = ((size_t)(n_seg - 1) * a->batch * a->d_inner * 16 * sizeof(float) + 255) / 256 * 256;
-        p.carry = reinterpret_cast<float *>(ws);
-        p.flags = reinterpret_cast<int *>(ws + carry);
-        HX_CUDA(cudaMemsetAsync(p.flags, 0, (size_t)(n_seg - 1) * a->batch * tiles_of(a) * 8 * sizeof(int), st));
+        p.carry = reinterpret_cast<float *>(ws + wl.carry);
+        p.flags = reinterpret_cast<int *>(ws + wl.flags);
+        p.sdt = reinterpret_cast<float *>(ws + wl.sdt);
+        // chained form: the flags are compared against a per-launch epoch, so they are cleared on every call.
+        // The look-back form has no flags: every aggregate is written by the first launch before the second reads it.
+        if (form == 0) HX_CUDA(cudaMemsetAsync(p.flags, 0, wl.flag_bytes, st));
     }
 
     CUtensorMap maps[8];
@@ -1009,10 +1053,19 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
     dim3 grid(tiles, a->batch, n_seg);
     const bool geom = a->a_geometric != 0;
     const bool stdp = a->conv_w != nullptr && a->z != nullptr && a->dt_softplus != 0;
+    // the block's own call: u already convolved, gate and softplus present, geometric A
+    const bool blockp = bf && geom && !p.z_gate && a->conv_w == nullptr && a->z != nullptr && a->dt_softplus != 0;
+    void *yv = a->y;
+    const int64_t ybs = a->y_batch_stride, yrs = a->y_row_stride;
+    if (form == 1) {
+        if (fused_dt) return launch_lookback_pair<__nv_bfloat16, false, true, true>(p, maps, grid, st, yv, ybs, yrs);
+        if (blockp) return launch_lookback_pair<__nv_bfloat16, false, false, true>(p, maps, grid, st, yv, ybs, yrs);
+        if (bf && stdp) return launch_lookback_pair<__nv_bfloat16, true, false, false>(p, maps, grid, st, yv, ybs, yrs);
+        if (bf) return launch_lookback_pair<__nv_bfloat16, false, false, false>(p, maps, grid, st, yv, ybs, yrs);
+        return launch_lookback_pair<float, false, false, false>(p, maps, grid, st, yv, ybs, yrs);
+    }
 #define HX_DIRECT_CASE(T, CPL)                                                                                         \
     do {                                                                                                               \
-        void *yv = a->y;                                                                                               \
-        const int64_t ybs = a->y_batch_stride, yrs = a->y_row_stride;                                                  \
         if (geom && stdp) return launch_direct_inst<T, CPL, true, true>(p, maps, grid, st, yv, ybs, yrs);              \
         if (geom) return launch_direct_inst<T, CPL, true, false>(p, maps, grid, st, yv, ybs, yrs);                     \
         if (stdp) return launch_direct_inst<T, CPL, false, true>(p, maps, grid, st, yv, ybs, yrs);                     \
@@ -1021,8 +1074,6 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
     if (fused_dt) {
         HX_REQUIRE(stdp || (a->z != nullptr && a->dt_softplus != 0), HX_ERR_UNSUPPORTED_OPERATION,
                    "the fused dt projection is built for the block's configuration (gate and softplus present)");
-        void *yv = a->y;
-        const int64_t ybs = a->y_batch_stride, yrs = a->y_row_stride;
         // the block hands u (already convolved): conv flags are read at run time, so STD is false here
         // the gate flag is a compile-time constant on this path (the block's), so the activation code is gone when
         // in_proj has already applied it
@@ -1034,9 +1085,9 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
             if (geom) return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, true, true>(p, maps, grid, st, yv, ybs, yrs);
             return launch_direct_inst<__nv_bfloat16, 1, false, false, 2, true, true>(p, maps, grid, st, yv, ybs, yrs);
         }
-        // the block's own call (u already convolved, gate and softplus present, geometric A): every flag is a
-        // compile-time constant, which saves the per-point flag tests and the registers of the unused conv window
-        if (geom && !p.z_gate && a->conv_w == nullptr && a->z != nullptr && a->dt_softplus != 0) {
+        // the block's own call: every flag is a compile-time constant, which saves the per-point flag tests and the
+        // registers of the unused conv window
+        if (blockp) {
             if (cpl == 2) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, true, false, true>(p, maps, grid, st, yv, ybs, yrs);
             return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, true, false, true>(p, maps, grid, st, yv, ybs, yrs);
         }
@@ -1048,15 +1099,13 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
         return launch_direct_inst<__nv_bfloat16, 1, false, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
     }
     if (bf && geom && stdp && a->reserved / 10 == 1) {  // tuning: three stages instead of two
-        if (cpl == 2)
-            return launch_direct_inst<__nv_bfloat16, 2, true, true, 3>(p, maps, grid, st, a->y, a->y_batch_stride, a->y_row_stride);
-        return launch_direct_inst<__nv_bfloat16, 1, true, true, 3>(p, maps, grid, st, a->y, a->y_batch_stride, a->y_row_stride);
+        if (cpl == 2) return launch_direct_inst<__nv_bfloat16, 2, true, true, 3>(p, maps, grid, st, yv, ybs, yrs);
+        return launch_direct_inst<__nv_bfloat16, 1, true, true, 3>(p, maps, grid, st, yv, ybs, yrs);
     }
-    if (bf && geom && !p.z_gate && a->conv_w == nullptr && a->z != nullptr && a->dt_softplus != 0) {
+    if (blockp) {
         // the block's configuration with dt read from memory: compile-time flags as in the fused form
-        if (cpl == 2)
-            return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, false, false, true>(p, maps, grid, st, a->y, a->y_batch_stride, a->y_row_stride);
-        return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, false, false, true>(p, maps, grid, st, a->y, a->y_batch_stride, a->y_row_stride);
+        if (cpl == 2) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, false, false, true>(p, maps, grid, st, yv, ybs, yrs);
+        return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, false, false, true>(p, maps, grid, st, yv, ybs, yrs);
     }
     if (bf) {
         if (cpl == 2) HX_DIRECT_CASE(__nv_bfloat16, 2);
@@ -1065,6 +1114,19 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
     HX_DIRECT_CASE(float, 1);
 #undef HX_DIRECT_CASE
     return HX_OK;
+}
+
+// ---- kernel choice of HX_SCAN_AUTO (d_state == 16), shared with the Mamba block's planning
+// Chains are (batch, channel) pairs; a one-lane-per-channel warp holds 32 of them.  With at least 8 such warps per
+// SM the direct kernel runs them one pass, chained segments evening out the load.  Below that the machine is short
+// of independent work: with geometric A and a split the look-back form runs the segments of a chain at the same
+// time; otherwise the lane-split kernel spreads a chain's states over 2 or 4 lanes.
+ScanKind auto_kind(const hx_scan_args *a) {
+    const double warps_per_sm = (double)a->batch * a->d_inner / 32.0 / sm_count();
+    if (warps_per_sm >= 8.0) return ScanKind::Direct;
+    if (a->seq_splits > 1 && lookback_ok(a)) return ScanKind::LookBack;
+    if (a->W_dt != nullptr) return ScanKind::Direct;  // the fused dt projection exists only there
+    return ScanKind::Tiled;
 }
 
 }  // namespace scan
@@ -1093,12 +1155,14 @@ hx_status hx_selective_scan_fwd(const hx_scan_args *a, void *stream) {
         case HX_SCAN_TILED: return hx::scan::launch_tiled(a, split, st);
         case HX_SCAN_SEQSPLIT: return hx::scan::launch_tiled(a, true, st);
         case HX_SCAN_DIRECT: return hx::scan::launch_direct(a, split, st);
+        case HX_SCAN_LOOKBACK: return hx::scan::launch_direct(a, true, st, 1);
         case HX_SCAN_AUTO: {
             if (a->d_state == 16) {
-                // enough independent chains for one lane per channel -> direct kernel, else split the states
-                const double chains = (double)a->batch * a->d_inner;
-                const bool direct = a->W_dt != nullptr || chains / 32.0 >= 8.0 * hx::sm_count();
-                s = direct ? hx::scan::launch_direct(a, split, st) : hx::scan::launch_tiled(a, split, st);
+                switch (hx::scan::auto_kind(a)) {
+                    case hx::scan::ScanKind::Direct: s = hx::scan::launch_direct(a, split, st); break;
+                    case hx::scan::ScanKind::LookBack: s = hx::scan::launch_direct(a, true, st, 1); break;
+                    default: s = hx::scan::launch_tiled(a, split, st); break;
+                }
                 // an operand that does not meet the TMA alignment rules goes to the simple kernel
                 if (s != HX_ERR_UNSUPPORTED_OPERATION) return s;
             }
@@ -1110,9 +1174,17 @@ hx_status hx_selective_scan_fwd(const hx_scan_args *a, void *stream) {
 
 int32_t hx_selective_scan_suggest_splits(const hx_scan_args *a) {
     if (!a || a->d_state != 16 || a->batch <= 0 || a->seq_len <= 0 || a->d_inner <= 0) return 1;
-    // CTAs of the kernel AUTO would pick, against the CTA slots of the device (about 3 per SM)
     const double chains = (double)a->batch * a->d_inner;
-    const bool direct = chains / 32.0 >= 8.0 * hx::sm_count();
+    const double warps_per_sm = chains / 32.0 / hx::sm_count();
+    const bool direct = warps_per_sm >= 8.0;
+    if (!direct && a->a_geometric && !a->z_is_gate) {
+        // few chains, geometric A: the look-back form runs the segments of a chain at the same time, so split
+        // until there are about 16 one-lane-per-channel warps per SM, keeping segments of at least 64 steps
+        int splits = 1;
+        while (splits < 16 && splits * warps_per_sm < 16.0 && a->seq_len / (2 * splits) >= 64) splits *= 2;
+        return splits;
+    }
+    // chained segments: CTAs of the kernel AUTO would pick, against the CTA slots of the device (about 3 per SM)
     const int tile = direct ? 128 : (a->io_dtype == HX_BF16 ? 64 : 32);
     const double ctas = (double)a->batch * ((a->d_inner + tile - 1) / tile);
     const double slots = 3.0 * hx::sm_count();
@@ -1127,11 +1199,10 @@ int32_t hx_selective_scan_suggest_splits(const hx_scan_args *a) {
 hx_status hx_selective_scan_workspace_bytes(const hx_scan_args *a, size_t *bytes) {
     HX_REQUIRE(a && bytes, HX_ERR_INVALID_INPUT, "hx_selective_scan_workspace_bytes: NULL argument");
     *bytes = 0;
-    if (a->variant != HX_SCAN_SEQSPLIT && a->seq_splits <= 1) return HX_OK;
+    if (a->variant != HX_SCAN_SEQSPLIT && a->variant != HX_SCAN_LOOKBACK && a->seq_splits <= 1) return HX_OK;
     if (a->variant == HX_SCAN_SIMPLE) return HX_OK;
-    const int TC = a->io_dtype == HX_BF16 ? hx::scan::kChunkBf16 : hx::scan::kChunkF32;
     int n_seg, seg_len;
-    hx::scan::seg_plan(a, TC, &n_seg, &seg_len);
+    hx::scan::seg_plan(a, hx::scan::kPlanChunk, &n_seg, &seg_len);
     *bytes = hx::scan::workspace_bytes(a, n_seg);
     return HX_OK;
 }
@@ -1152,7 +1223,7 @@ static size_t host_stage_bytes(const hx_scan_args *a, size_t *off /* x, dt, z, B
     off[5] = o; o += big;
     off[6] = o;
     size_t inner = 0;
-    if (a->variant == HX_SCAN_SEQSPLIT) hx_selective_scan_workspace_bytes(a, &inner);
+    hx_selective_scan_workspace_bytes(a, &inner);  // 0 unless the call splits the sequence
     return o + inner + 256;
 }
 
@@ -1170,6 +1241,8 @@ hx_status hx_selective_scan_host(const hx_scan_args *a, void *dev_workspace, siz
     hx_status s = hx::scan::validate(a);
     if (s != HX_OK) return s;
     if (a->batch == 0 || a->seq_len == 0 || a->d_inner == 0) return HX_OK;
+    HX_REQUIRE(a->W_dt == nullptr && a->dt != nullptr, HX_ERR_UNSUPPORTED_OPERATION,
+               "hx_selective_scan_host takes dt as a host tensor; the fused dt projection is a device-side form");
     size_t off[7];
     const size_t need = host_stage_bytes(a, off);
     HX_REQUIRE(dev_workspace && dev_workspace_bytes >= need, HX_ERR_INVALID_INPUT,

@@ -124,7 +124,7 @@ def selective_scan(x, dt, A, Bm, Cm, D=None, z=None, conv_w=None, conv_b=None, d
     a.seq_splits = seq_splits
     a.reserved = tune
     a.z_is_gate = 1 if z_is_gate else 0
-    if variant == L.SCAN_SEQSPLIT or seq_splits > 1:
+    if variant in (L.SCAN_SEQSPLIT, L.SCAN_LOOKBACK) or seq_splits > 1:
         n = C.c_size_t(0)
         L.check(L.lib().hx_selective_scan_workspace_bytes(C.byref(a), C.byref(n)))
         if workspace is None:

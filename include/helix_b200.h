@@ -63,8 +63,14 @@ typedef enum hx_scan_variant {
     HX_SCAN_TILED = 2,    /* state split over lanes, shared-memory staged tiles; d_state == 16 */
     HX_SCAN_SEQSPLIT = 3, /* HX_SCAN_TILED with the sequence split over CTAs and carries passed
                              through `workspace` by a bounded look-back */
-    HX_SCAN_DIRECT = 4    /* one lane per channel (all 16 states in its registers), 1 or 2 channels per lane,
+    HX_SCAN_DIRECT = 4,   /* one lane per channel (all 16 states in its registers), 1 or 2 channels per lane,
                              no traffic between lanes; d_state == 16; best when batch * d_inner is large */
+    HX_SCAN_LOOKBACK = 5  /* HX_SCAN_DIRECT with the sequence cut into seq_splits segments that run at the SAME time
+                             (for few chains: small batch * d_inner, long sequences).  Two launches: every segment
+                             but the last first computes its aggregate from a zero state (end state and sum of dt,
+                             no outputs), then every segment folds the aggregates of its predecessors into its start
+                             state (the look-back) and scans with outputs.  Needs a_geometric = 1, d_state == 16 and
+                             `workspace`; no flag or wait between CTAs */
 } hx_scan_variant;
 
 HX_API const char *hx_version(void);
@@ -122,10 +128,12 @@ typedef struct hx_scan_args {
     float *h_last;            /* [batch, d_inner, d_state] fp32 final state, or NULL */
     void *workspace;          /* split sequences only: hx_selective_scan_workspace_bytes() bytes */
     size_t workspace_bytes;
-    int32_t seq_splits;       /* > 1: cut the sequence into this many segments that run as separate CTAs in order,
-                                 each starting from its predecessor's final state (needs `workspace`); this
-                                 evens out the load when batch * d_inner / tile is not a multiple of the SM
-                                 slots.  HX_SCAN_SEQSPLIT: 0 = choose */
+    int32_t seq_splits;       /* > 1: cut the sequence into this many segments that run as separate CTAs (needs
+                                 `workspace`).  HX_SCAN_TILED / DIRECT: in order, each starting from its
+                                 predecessor's final state, which evens out the load when batch * d_inner / tile
+                                 is not a multiple of the SM slots.  HX_SCAN_LOOKBACK: at the same time.
+                                 HX_SCAN_AUTO: chained when chains are plentiful, look-back when they are few and
+                                 A is geometric.  HX_SCAN_SEQSPLIT / LOOKBACK: 0 = four segments */
     int32_t a_geometric;      /* 1: the caller asserts A[d][n] == (n+1) * A[d][0] (checked once with
                                  hx_scan_check_geometric); then exp(dt*A[d][n]) is evaluated as a power of
                                  exp(dt*A[d][0]), one exp per point instead of d_state */
@@ -147,10 +155,12 @@ typedef struct hx_scan_args {
 } hx_scan_args;
 
 HX_API hx_status hx_selective_scan_fwd(const hx_scan_args *args, void *stream);
-/* Bytes of `workspace` HX_SCAN_SEQSPLIT needs for these dimensions (0 for the other variants). */
+/* Bytes of `workspace` a split scan of these dimensions needs (HX_SCAN_SEQSPLIT, HX_SCAN_LOOKBACK, or any variant
+ * with seq_splits > 1; 0 otherwise).  One size serves the chained and the look-back form. */
 HX_API hx_status hx_selective_scan_workspace_bytes(const hx_scan_args *args, size_t *bytes);
-/* Number of sequence segments (a power of two, 1 = do not split) that evens out the load for these dimensions
- * on the current device; pass it as args->seq_splits together with a workspace. */
+/* Number of sequence segments (a power of two, 1 = do not split) HX_SCAN_AUTO works best with for these dimensions
+ * on the current device: chained segments that even out the load when chains are plentiful, parallel segments
+ * (look-back form, needs args->a_geometric) when they are few.  Pass it as args->seq_splits with a workspace. */
 HX_API int32_t hx_selective_scan_suggest_splits(const hx_scan_args *args);
 /* The same operation on HOST activations: x, dt, z, Bm, Cm are read from (preferably pinned) host memory
  * with the strides given in args, staged into `dev_workspace` (caller-owned device memory of
@@ -172,7 +182,7 @@ HX_API hx_status hx_selective_scan_host_workspace_bytes(const hx_scan_args *args
  * library's device image (HX_SCAN_NOALLOC_SCRATCH_BYTES; each GPU that loads the library holds it until the
  * process exits).  args->variant, args->workspace and args->workspace_bytes are ignored; inputs and outputs
  * are the caller's as usual.  It calls no cudaMalloc / cudaFree and no allocating library routine.
- *  - Limit: the carries need 64 * (segments - 1) * batch * d_inner bytes plus flags; a problem that needs more
+ *  - Limit: the carries need 68 * (segments - 1) * batch * d_inner bytes plus flags; a problem that needs more
  *    than HX_SCAN_NOALLOC_SCRATCH_BYTES is refused with HX_ERR_INVALID_INPUT and a message giving both sizes.
  *  - The first call on a device looks up the array's device address (once per device, that device must be
  *    current); make that first call before starting any stream capture.

@@ -42,7 +42,20 @@ def check(got, ref, dtype):
         assert fp32_tol_err(got, ref) <= FP32_TOL
 
 
-SIMPLE, TILED, SEQSPLIT, DIRECT = 1, 2, 3, 4
+SIMPLE, TILED, SEQSPLIT, DIRECT, LOOKBACK = 1, 2, 3, 4, 5
+
+
+def check_blocks(got, ref, dtype, seg_len, tile=64):
+    """The parity gate on every (batch row, sequence segment, channel tile) block by itself: a carry lost at one
+    segment boundary of one tile changes a few thousand outputs, which a whole-tensor norm would not show."""
+    B, L, D = ref.shape
+    worst = 0.0
+    for b in range(B):
+        for t0 in range(0, L, seg_len):
+            for d0 in range(0, D, tile):
+                g, r = got[b, t0:t0 + seg_len, d0:d0 + tile], ref[b, t0:t0 + seg_len, d0:d0 + tile]
+                worst = max(worst, rel_l2(g, r) if dtype == "bf16" else fp32_tol_err(g, r))
+    assert worst <= (BF16_TOL if dtype == "bf16" else FP32_TOL), worst
 
 
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
@@ -116,6 +129,99 @@ def test_direct_fused_dt_projection(cpl, geom, conv, B, L, D, R):
         ops.selective_scan(to_dev(inp["x"], "bf16"), None, to_dev(inp["A"]), wide[:, :, R:R + 16], wide[:, :, R + 16:],
                            variant=TILED, dt_low=wide[:, :, :R], W_dt=to_dev(W_dt, "bf16"))
     assert e.value.variant == "UnsupportedOperation"
+
+
+@pytest.mark.parametrize("splits", [2, 8])
+def test_direct_fused_dt_projection_chained_segments(splits):
+    """The fused dt projection with the sequence cut into chained segments, in the block's configuration (no conv,
+    gate and softplus present, geometric A): the instantiation the byte LM runs at full size.  Gate on every
+    (row, segment, tile) block, small steps so that a lost carry shows."""
+    import torch
+    from helixml_b200 import _lib, ops
+    B, L, D, R = 3, 520, 200, 48
+    inp = synth.scan_inputs(46, B, L, D, 16, 4, bf16=True)
+    dt_low = synth.round_bf16(synth.normal(46, "dt_low", (B, L, R)))
+    W_dt = synth.round_bf16(synth.normal(46, "W_dt", (D, R), 0.0, 0.4 / np.sqrt(R)))
+    bias = synth.uniform(46, "bias", (D,), -5.0, -3.0)
+    dt = (dt_low.reshape(-1, R).astype(np.float64) @ W_dt.astype(np.float64).T).reshape(B, L, D).astype(np.float32)
+    ref, hr = cbind.selective_scan(inp["x"], dt, inp["A"], inp["B"], inp["C"], D=inp["D"], z=inp["z"], dt_bias=bias,
+                                   return_state=True)
+    wide = torch.zeros((B, L, R + 32), dtype=torch.bfloat16, device="cuda")
+    wide[:, :, :R] = to_dev(dt_low, "bf16")
+    wide[:, :, R:R + 16] = to_dev(inp["B"], "bf16")
+    wide[:, :, R + 16:] = to_dev(inp["C"], "bf16")
+    for variant in (DIRECT, LOOKBACK):
+        y, h = ops.selective_scan(to_dev(inp["x"], "bf16"), None, to_dev(inp["A"]), wide[:, :, R:R + 16], wide[:, :, R + 16:],
+                                  D=to_dev(inp["D"]), z=to_dev(inp["z"], "bf16"), dt_bias=to_dev(bias), variant=variant,
+                                  a_geometric=True, dt_low=wide[:, :, :R], W_dt=to_dev(W_dt, "bf16"), seq_splits=splits,
+                                  return_state=True)
+        assert _lib.device_status() == 0
+        seg = -(-(-(-L // splits)) // 32) * 32
+        check_blocks(to_np(y), ref, "bf16", seg, tile=128)
+        assert rel_l2(to_np(h), hr) <= BF16_TOL
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("splits", [2, 3, 5, 8])
+@pytest.mark.parametrize("conv", [True, False])
+def test_lookback_parallel_segments(dtype, splits, conv):
+    """HX_SCAN_LOOKBACK: the segments of a chain run at the same time (aggregate pass, then look-back + output
+    pass).  L is neither a multiple of the segment nor of the chunk, D not a multiple of the tile, steps are small
+    so that the state carries across every boundary; gate on every (row, segment, tile) block and on the final
+    state, and agreement with the one-pass kernel."""
+    inp = synth.scan_inputs(47, 2, 333, 168, 16, 4, bf16=dtype == "bf16")
+    inp["dt"] -= 2.0
+    if dtype == "bf16":
+        inp["dt"] = synth.round_bf16(inp["dt"])
+    got, hg = run_gpu(inp, dtype, variant=LOOKBACK, seq_splits=splits, geom=True, state=True, conv=conv)
+    ref, hr = run_ref(inp, state=True, conv=conv)
+    seg = -(-(-(-333 // splits)) // 32) * 32
+    check_blocks(got, ref, dtype, seg)
+    check(hg, hr, dtype)
+    one = run_gpu(inp, dtype, variant=DIRECT, geom=True, conv=conv)
+    assert (fp32_tol_err(got, one) <= FP32_TOL) if dtype == "f32" else (rel_l2(got, one) <= 1e-2)
+
+
+def test_lookback_optional_terms_and_single_segment():
+    inp = synth.scan_inputs(48, 2, 200, 64, 16, 4, bf16=False)
+    inp["dt"] -= 1.5
+    cb = synth.uniform(48, "cb", (64,), -0.3, 0.3)
+    db = synth.uniform(48, "db", (64,), -1.0, 0.5)
+    # no gate, no skip, conv bias and dt bias
+    ref = run_ref(inp, gate=False, skip=False, conv_b=cb, dt_bias=db)
+    check_blocks(run_gpu(inp, "f32", variant=LOOKBACK, seq_splits=4, geom=True, gate=False, skip=False, conv_b=cb, dt_bias=db),
+                 ref, "f32", 64)
+    # dt used as given (no softplus)
+    raw = dict(inp)
+    raw["dt"] = np.abs(inp["dt"]) * 0.02
+    check_blocks(run_gpu(raw, "f32", variant=LOOKBACK, seq_splits=3, geom=True, softplus=False), run_ref(raw, softplus=False),
+                 "f32", 96)
+    # a sequence shorter than one planning chunk is a single segment: plain one-pass kernel
+    short = synth.scan_inputs(49, 1, 20, 32, 16, 4, bf16=False)
+    check(run_gpu(short, "f32", variant=LOOKBACK, seq_splits=4, geom=True), run_ref(short), "f32")
+
+
+def test_lookback_needs_geometric_decay():
+    """With a general A the aggregate of a segment is not a power of one exponential: HX_SCAN_LOOKBACK says so,
+    HX_SCAN_AUTO with seq_splits falls back to a kernel that handles it."""
+    from helixml_b200 import _lib
+    inp = synth.scan_inputs(50, 1, 300, 64, 16, 4, bf16=False)
+    inp["A"] = -np.exp(synth.uniform(50, "Alog", (64, 16), -1.0, 2.0)).astype(np.float32)
+    with pytest.raises(_lib.HxError) as e:
+        run_gpu(inp, "f32", variant=LOOKBACK, seq_splits=4, geom=False)
+    assert e.value.variant == "UnsupportedOperation"
+    check(run_gpu(inp, "f32", variant=0, seq_splits=4), run_ref(inp), "f32")
+
+
+def test_auto_picks_lookback_for_few_chains():
+    """Few chains, geometric A, a split given: HX_SCAN_AUTO runs the look-back form (two launches of the direct
+    kernel); the result is the oracle's."""
+    inp = synth.scan_inputs(51, 1, 1024, 256, 16, 4, bf16=True)
+    inp["dt"] = synth.round_bf16(inp["dt"] - 2.0)
+    got, hg = run_gpu(inp, "bf16", variant=0, seq_splits=8, state=True)
+    ref, hr = run_ref(inp, state=True)
+    check_blocks(got, ref, "bf16", 128)
+    check(hg, hr, "bf16")
 
 
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
@@ -240,6 +346,11 @@ def test_sequence_split_with_carry(dtype, lpc, splits):
     ref, hr = run_ref(inp, state=True)
     check(got, ref, dtype)
     check(hg, hr, dtype)
+    check_blocks(got, ref, dtype, -(-(-(-300 // splits)) // 32) * 32, tile=40)
+    # the one-lane-per-channel kernel with the same chained segments
+    got_d, hd = run_gpu(inp, dtype, variant=DIRECT, seq_splits=splits, state=True)
+    check_blocks(got_d, ref, dtype, -(-(-(-300 // splits)) // 32) * 32, tile=40)
+    check(hd, hr, dtype)
     # and it is the same function as the unsplit kernel
     one = run_gpu(inp, dtype, variant=TILED, lpc=lpc)
     assert np.max(np.abs(one - got)) <= (1e-5 if dtype == "f32" else 1e-1)
