@@ -108,6 +108,8 @@ _PROTOS = {
                                         C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_size_t,
                                         C.c_void_p]),
     "hx_s4_ref_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
+    "hx_mamba_ssm_ref_forward": (C.c_int, [C.c_void_p] * 9 + [C.c_int32, C.c_int32, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "hx_mamba_ssm_ref_workspace_bytes": (C.c_size_t, [C.c_int32, C.c_int32]),
     "hx_gemm_bf16": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32,
                                C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "hx_gemm_bf16_acc": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int32, C.c_int32,
@@ -138,6 +140,25 @@ _PROTOS = {
                                  C.POINTER(C.c_int32)]),
     "hx_tensor_data": (C.c_void_p, [C.c_void_p]),
     "hx_tensor_free": (None, [C.c_void_p]),
+    # ---- tensor primitives (TensorOps / TensorBroadcast / TensorActivation / TensorRandom / TensorMixedPrecision)
+    "hx_tensor_binary": (C.c_int, [C.c_int32, C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "hx_tensor_unary": (C.c_int, [C.c_int32, C.c_void_p, C.c_float, C.c_float, C.POINTER(C.c_void_p)]),
+    "hx_tensor_matmul": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),
+    "hx_matmul_ref": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "hx_tensor_transpose": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.POINTER(C.c_void_p)]),
+    "hx_tensor_slice": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_tensor_cat": (C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int64, C.POINTER(C.c_void_p)]),
+    "hx_tensor_stack": (C.c_int, [C.POINTER(C.c_void_p), C.c_int32, C.c_int64, C.POINTER(C.c_void_p)]),
+    "hx_tensor_reshape": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_tensor_clone": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "hx_tensor_broadcast_to": (C.c_int, [C.c_void_p, C.POINTER(C.c_int64), C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_tensor_cast": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_tensor_to_scalar": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
+    "hx_tensor_full": (C.c_int, [C.c_float, C.POINTER(C.c_int64), C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_tensor_eye": (C.c_int, [C.c_int64, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_tensor_arange": (C.c_int, [C.c_float, C.c_float, C.c_float, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_tensor_random": (C.c_int, [C.c_int32, C.POINTER(C.c_int64), C.c_int32, C.c_float, C.c_float, C.c_int32,
+                                   C.POINTER(C.c_void_p)]),
     "hx_mamba_block_new": (C.c_int, [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
     "hx_s4_block_new": (C.c_int, [C.c_int64, C.c_int64, C.c_int32, C.POINTER(C.c_void_p)]),
     "hx_linear_new": (C.c_int, [C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),

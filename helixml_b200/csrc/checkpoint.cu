@@ -135,7 +135,7 @@ hx_status write_file(const char *path, const hx_checkpoint_meta *meta, int32_t n
     return HX_OK;
 }
 
-hx_status read_file(const char *path, hx_checkpoint *ck) {
+hx_status read_file_impl(const char *path, hx_checkpoint *ck) {
     FILE *f = fopen(path, "rb");
     HX_REQUIRE(f != nullptr, HX_ERR_SERIALIZATION, "hx_checkpoint_open: cannot open %s", path);
     std::vector<unsigned char> buf;
@@ -173,12 +173,17 @@ hx_status read_file(const char *path, hx_checkpoint *ck) {
         HX_REQUIRE(r.ok && nd <= 8, HX_ERR_SERIALIZATION, "hx_checkpoint_open: tensor %" PRIu64 " has %" PRIu64 " dimensions", i, nd);
         std::vector<int64_t> dims(nd);
         uint64_t numel = 1;
+        bool wrapped = false;
         for (auto &d : dims) {
-            d = (int64_t)r.u64();
-            numel *= (uint64_t)d;
+            const uint64_t dv = r.u64();
+            d = (int64_t)dv;
+            // sizes come from the file: a product that wraps, or a dimension beyond int64, is a malformed file
+            if (dv > (uint64_t)INT64_MAX || (dv != 0 && numel > UINT64_MAX / dv)) wrapped = true;
+            else numel *= dv;
         }
+        HX_REQUIRE(r.ok && !wrapped, HX_ERR_SERIALIZATION, "hx_checkpoint_open: tensor %" PRIu64 " has an implausible shape", i);
         const uint64_t cnt = r.u64();
-        HX_REQUIRE(r.ok && cnt == numel && cnt * 4 <= (uint64_t)(r.end - r.p), HX_ERR_SERIALIZATION,
+        HX_REQUIRE(r.ok && cnt == numel && cnt <= (uint64_t)(r.end - r.p) / 4, HX_ERR_SERIALIZATION,
                    "hx_checkpoint_open: tensor %" PRIu64 " holds %" PRIu64 " elements for a shape of %" PRIu64, i, cnt, numel);
         std::vector<float> data(cnt);
         r.take(data.data(), cnt * 4);
@@ -198,6 +203,17 @@ hx_status read_file(const char *path, hx_checkpoint *ck) {
     }
     HX_REQUIRE(r.p == r.end, HX_ERR_SERIALIZATION, "hx_checkpoint_open: %zu trailing bytes", (size_t)(r.end - r.p));
     return HX_OK;
+}
+
+// No C++ exception crosses the C ABI: a file whose sizes ask for more memory than there is becomes a status.
+hx_status read_file(const char *path, hx_checkpoint *ck) {
+    try {
+        return read_file_impl(path, ck);
+    } catch (const std::bad_alloc &) {
+        return hx::fail(HX_ERR_ALLOCATION_FAILED, "hx_checkpoint_open: out of host memory while reading %s", path);
+    } catch (const std::exception &e) {
+        return hx::fail(HX_ERR_SERIALIZATION, "hx_checkpoint_open: %s", e.what());
+    }
 }
 
 }  // namespace

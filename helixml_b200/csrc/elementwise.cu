@@ -156,7 +156,7 @@ conv_silu_strip_kernel(const __nv_bfloat16 *__restrict__ x, int64_t xb, int64_t 
     float w[4][CH], bias[CH];
 #pragma unroll
     for (int e = 0; e < CH; ++e) {
-        if (K == 4) {
+        if (K == 4 && (reinterpret_cast<uintptr_t>(cw) & 15) == 0) {  // a 4-byte-aligned slice takes the scalar loads
             const float4 q = __ldg(reinterpret_cast<const float4 *>(cw) + d + e);
             w[0][e] = q.x; w[1][e] = q.y; w[2][e] = q.z; w[3][e] = q.w;
         } else {

@@ -190,17 +190,27 @@ Result<DeviceTensor> DeviceTensor::reshape(const Shape &shape) const {
     return t;
 }
 
-// Normal(0, std) / constant initialisers
-static Result<DeviceTensor> init_normal(const Shape &shape, double stddev, DType dtype, const Device &device) {
+// Normal(mean, std) / uniform / Bernoulli / constant initialisers (TensorRandom, crates/tensor-core/src/tensor.rs:212-233),
+// drawn on the host from the seeded counter streams above
+Result<DeviceTensor> init_normal(const Shape &shape, double stddev, DType dtype, const Device &device, double mean) {
+    if (shape.numel() < 0) return err(HX_ERR_INVALID_DIMENSION, "negative dimension in shape " + shape_str(shape));
     std::vector<float> h((size_t)shape.numel());
     Rng rng;
-    for (auto &v : h) v = (float)(stddev * rng.normal());
+    for (auto &v : h) v = (float)(mean + stddev * rng.normal());
     return DeviceTensor::from_host_f32(h.data(), shape, dtype, device);
 }
-static Result<DeviceTensor> init_uniform(const Shape &shape, double lo, double hi, DType dtype, const Device &device) {
+Result<DeviceTensor> init_uniform(const Shape &shape, double lo, double hi, DType dtype, const Device &device) {
+    if (shape.numel() < 0) return err(HX_ERR_INVALID_DIMENSION, "negative dimension in shape " + shape_str(shape));
     std::vector<float> h((size_t)shape.numel());
     Rng rng;
     for (auto &v : h) v = (float)(lo + (hi - lo) * rng.uniform01());
+    return DeviceTensor::from_host_f32(h.data(), shape, dtype, device);
+}
+Result<DeviceTensor> init_bernoulli(const Shape &shape, double p, DType dtype, const Device &device) {
+    if (shape.numel() < 0) return err(HX_ERR_INVALID_DIMENSION, "negative dimension in shape " + shape_str(shape));
+    std::vector<float> h((size_t)shape.numel());
+    Rng rng;
+    for (auto &v : h) v = rng.uniform01() < p ? 1.f : 0.f;
     return DeviceTensor::from_host_f32(h.data(), shape, dtype, device);
 }
 static Result<DeviceTensor> init_const(const Shape &shape, float value, DType dtype, const Device &device) {

@@ -283,6 +283,31 @@ class ByteLM : public Module {
 // crates/backend-cpu/src/lib.rs:1209; here initialisation is reproducible).
 void manual_seed(uint64_t seed);
 
+// TensorRandom::{random_normal, random_uniform, random_bernoulli} (crates/tensor-core/src/tensor.rs:212-221)
+Result<DeviceTensor> init_normal(const Shape &shape, double stddev, DType dtype, const Device &device, double mean = 0.0);
+Result<DeviceTensor> init_uniform(const Shape &shape, double lo, double hi, DType dtype, const Device &device);
+Result<DeviceTensor> init_bernoulli(const Shape &shape, double p, DType dtype, const Device &device);
+
+// The tensor primitives the reference's generic blocks call on T (csrc/tensor_ops.cu): TensorOps
+// (tensor.rs:62-134), TensorBroadcast (:137-149), TensorActivation (:191-209), TensorMixedPrecision::cast (:238),
+// Tensor::{transpose, slice, cat, stack} (:37-46), TensorRandom::{zeros, ones, eye, arange} (:223-232).
+// `op` is an hx_binary_op / hx_unary_op code.
+namespace tops {
+Result<DeviceTensor> binary(int op, const DeviceTensor &a, const DeviceTensor &b);
+Result<DeviceTensor> unary(int op, const DeviceTensor &a, float p0 = 0.f, float p1 = 0.f);
+Result<DeviceTensor> matmul(const DeviceTensor &a, const DeviceTensor &b);
+Result<DeviceTensor> transpose(const DeviceTensor &a, int64_t dim0, int64_t dim1);
+Result<DeviceTensor> slice(const DeviceTensor &a, const std::vector<int64_t> &start, const std::vector<int64_t> &end);
+Result<DeviceTensor> cat(const std::vector<const DeviceTensor *> &tensors, int64_t dim);
+Result<DeviceTensor> stack(const std::vector<const DeviceTensor *> &tensors, int64_t dim);
+Result<DeviceTensor> broadcast_to(const DeviceTensor &a, const Shape &shape);
+Result<DeviceTensor> cast(const DeviceTensor &a, DType dtype);
+Result<float> to_scalar(const DeviceTensor &a);
+Result<DeviceTensor> full(float value, const Shape &shape, DType dtype, const Device &device);
+Result<DeviceTensor> eye(int64_t n, DType dtype, const Device &device);
+Result<DeviceTensor> arange(float start, float end, float step, DType dtype, const Device &device);
+}  // namespace tops
+
 }  // namespace helix
 
 // The opaque handles of the C ABI (include/helix_b200.h) wrap these.

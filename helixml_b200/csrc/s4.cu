@@ -228,6 +228,13 @@ static hx_status launch_diag(const void *u, const float *A, const float *Bp, con
     return fail(HX_ERR_INVALID_DIMENSION, "d_state %d exceeds 256", N);
 }
 
+// out[i][j] *= gate[j]: the row-broadcast gate of the reference's ssm-Mamba block
+__global__ void row_gate_kernel(float *out, const float *gate, int rows, int cols) {
+    const int64_t n = (int64_t)rows * cols;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        out[i] = __fmul_rn(out[i], gate[i % cols]);
+}
+
 }  // namespace s4
 }  // namespace hx
 
@@ -280,6 +287,37 @@ hx_status hx_s4_ref_forward_ssm(const float *u, const float *A_real, const float
     s4_ref_out_kernel<<<dim3((d_model + 127) / 128, seq_len), 128, d_state * sizeof(float), st>>>(V, Cm, Dv, u, y, d_model,
                                                                                                  seq_len, d_state);
     return hx::check_launch("s4_ref_out_kernel");
+}
+
+size_t hx_mamba_ssm_ref_workspace_bytes(int32_t d_model, int32_t d_state) {
+    if (d_model <= 0 || d_state <= 0) return 0;
+    return ((size_t)d_model * d_model * sizeof(float) + 255) / 256 * 256 + hx_s4_ref_workspace_bytes(d_model, d_state);
+}
+
+hx_status hx_mamba_ssm_ref_forward(const float *x, const float *delta_proj, const float *gate, const float *A_real,
+                                   const float *A_imag, const float *Bm, const float *Cm, const float *Dv, float *out,
+                                   int32_t d_model, int32_t d_state, void *workspace, size_t workspace_bytes, void *stream) {
+    HX_REQUIRE(d_model >= 0, HX_ERR_INVALID_DIMENSION, "negative dimension");
+    HX_REQUIRE(d_state >= 1 && d_state <= 256, HX_ERR_INVALID_DIMENSION, "d_state %d outside [1, 256]", d_state);
+    if (d_model == 0) return HX_OK;
+    HX_REQUIRE(x && delta_proj && gate && A_real && A_imag && Bm && Cm && Dv && out, HX_ERR_INVALID_INPUT, "NULL operand");
+    const size_t need = hx_mamba_ssm_ref_workspace_bytes(d_model, d_state);
+    HX_REQUIRE(workspace && workspace_bytes >= need, HX_ERR_INVALID_INPUT,
+               "hx_mamba_ssm_ref_forward needs a workspace of %zu bytes (got %zu)", need, workspace_bytes);
+    const int M = d_model;
+    float *delta = static_cast<float *>(workspace);
+    char *s4ws = static_cast<char *>(workspace) + ((size_t)M * M * sizeof(float) + 255) / 256 * 256;
+    // delta = x . delta_proj in the reference's matmul arithmetic (crates/nn/src/ssm.rs:447)
+    hx_status s = hx_matmul_ref(x, delta_proj, delta, M, M, M, HX_F32, stream);
+    if (s != HX_OK) return s;
+    // selective_ssm ignores B and C and runs the S4 recurrence on delta with dt = 0.1 (ssm.rs:474-483, :151)
+    s = hx_s4_ref_forward_ssm(delta, A_real, A_imag, Bm, Cm, Dv, 0.1f, out, M, M, d_state, s4ws, workspace_bytes - (size_t)(s4ws - static_cast<char *>(workspace)),
+                              stream);
+    if (s != HX_OK) return s;
+    const int64_t n = (int64_t)M * M;
+    const int blocks = (int)((n + 255) / 256 > 65535 ? 65535 : (n + 255) / 256);
+    hx::s4::row_gate_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(out, gate, M, M);
+    return hx::check_launch("row_gate_kernel");
 }
 
 }  // extern "C"

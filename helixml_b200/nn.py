@@ -74,6 +74,158 @@ class Tensor:
     def data_ptr(self) -> int:
         return L.lib().hx_tensor_data(self._h) or 0
 
+    # ---- the reference's tensor traits on the device tensor (crates/tensor-core/src/tensor.rs:34-275), same
+    # names, same shape rules and error variants as CpuTensor (crates/backend-cpu/src/lib.rs)
+    _BINARY = {"add": 0, "sub": 1, "mul": 2, "div": 3, "max": 4, "min": 5, "gt": 6}
+    _UNARY = {"sqrt": 16, "exp": 17, "log": 18, "sin": 19, "cos": 20, "tan": 21, "abs": 22, "sign": 23, "neg": 24,
+              "relu": 25, "gelu": 26, "silu": 27, "sigmoid": 28, "tanh": 29, "pow": 30, "clamp": 31, "add_scalar": 32,
+              "mul_scalar": 33, "gt_scalar": 34, "leaky_relu": 35}
+
+    def _binary(self, name, other: "Tensor") -> "Tensor":
+        out = C.c_void_p()
+        L.check(L.lib().hx_tensor_binary(self._BINARY[name], self._h, other._h, C.byref(out)))
+        return Tensor(out)
+
+    def _unary(self, name, p0=0.0, p1=0.0) -> "Tensor":
+        out = C.c_void_p()
+        L.check(L.lib().hx_tensor_unary(self._UNARY[name], self._h, p0, p1, C.byref(out)))
+        return Tensor(out)
+
+    def add(self, o): return self._binary("add", o)
+    def sub(self, o): return self._binary("sub", o)
+    def mul(self, o): return self._binary("mul", o)
+    def div(self, o): return self._binary("div", o)
+    def max(self, o): return self._binary("max", o)
+    def min(self, o): return self._binary("min", o)
+    def gt(self, o): return self._binary("gt", o)
+    def sqrt(self): return self._unary("sqrt")
+    def exp(self): return self._unary("exp")
+    def log(self): return self._unary("log")
+    def sin(self): return self._unary("sin")
+    def cos(self): return self._unary("cos")
+    def tan(self): return self._unary("tan")
+    def abs(self): return self._unary("abs")
+    def sign(self): return self._unary("sign")
+    def neg(self): return self._unary("neg")
+    def relu(self): return self._unary("relu")
+    def gelu(self): return self._unary("gelu")
+    def silu(self): return self._unary("silu")
+    def sigmoid(self): return self._unary("sigmoid")
+    def tanh(self): return self._unary("tanh")
+    def pow(self, exponent): return self._unary("pow", exponent)
+    def clamp(self, lo, hi): return self._unary("clamp", lo, hi)
+    def add_scalar(self, v): return self._unary("add_scalar", v)
+    def mul_scalar(self, v): return self._unary("mul_scalar", v)
+    def gt_scalar(self, v): return self._unary("gt_scalar", v)
+    def leaky_relu(self, slope): return self._unary("leaky_relu", slope)
+
+    def matmul(self, other: "Tensor") -> "Tensor":
+        out = C.c_void_p()
+        L.check(L.lib().hx_tensor_matmul(self._h, other._h, C.byref(out)))
+        return Tensor(out)
+
+    def transpose(self, dim0: int, dim1: int) -> "Tensor":
+        out = C.c_void_p()
+        L.check(L.lib().hx_tensor_transpose(self._h, dim0, dim1, C.byref(out)))
+        return Tensor(out)
+
+    def slice(self, start, end) -> "Tensor":
+        n = max(len(start), len(end))
+        out = C.c_void_p()
+        if len(start) != len(end):
+            raise L.HxError(1, "slice: start and end differ in length")
+        L.check(L.lib().hx_tensor_slice(self._h, (C.c_int64 * n)(*start), (C.c_int64 * n)(*end), n, C.byref(out)))
+        return Tensor(out)
+
+    @staticmethod
+    def _many(fn, tensors, dim) -> "Tensor":
+        arr = (C.c_void_p * len(tensors))(*[t._h.value if isinstance(t._h, C.c_void_p) else t._h for t in tensors])
+        out = C.c_void_p()
+        L.check(fn(arr, len(tensors), dim, C.byref(out)))
+        return Tensor(out)
+
+    @staticmethod
+    def cat(tensors, dim: int) -> "Tensor":
+        return Tensor._many(L.lib().hx_tensor_cat, tensors, dim)
+
+    @staticmethod
+    def stack(tensors, dim: int) -> "Tensor":
+        return Tensor._many(L.lib().hx_tensor_stack, tensors, dim)
+
+    def _shaped(self, fn, shape) -> "Tensor":
+        out = C.c_void_p()
+        L.check(fn(self._h, (C.c_int64 * len(shape))(*shape), len(shape), C.byref(out)))
+        return Tensor(out)
+
+    def reshape(self, shape) -> "Tensor":
+        return self._shaped(L.lib().hx_tensor_reshape, shape)
+
+    def broadcast_to(self, shape) -> "Tensor":
+        return self._shaped(L.lib().hx_tensor_broadcast_to, shape)
+
+    expand = broadcast_to
+
+    def clone(self) -> "Tensor":
+        out = C.c_void_p()
+        L.check(L.lib().hx_tensor_clone(self._h, C.byref(out)))
+        return Tensor(out)
+
+    def cast(self, dtype: int) -> "Tensor":
+        out = C.c_void_p()
+        L.check(L.lib().hx_tensor_cast(self._h, dtype, C.byref(out)))
+        return Tensor(out)
+
+    to_dtype = cast
+
+    def to_scalar(self) -> float:
+        v = C.c_float()
+        L.check(L.lib().hx_tensor_to_scalar(self._h, C.byref(v)))
+        return v.value
+
+    @staticmethod
+    def from_scalar(value, shape, dtype: int = F32, device: Device = Device(0)) -> "Tensor":
+        out = C.c_void_p()
+        L.check(L.lib().hx_tensor_full(value, (C.c_int64 * len(shape))(*shape), len(shape), dtype, device.index, C.byref(out)))
+        return Tensor(out)
+
+    @staticmethod
+    def zeros(shape, dtype: int = F32, device: Device = Device(0)) -> "Tensor":
+        return Tensor.from_scalar(0.0, shape, dtype, device)
+
+    @staticmethod
+    def ones(shape, dtype: int = F32, device: Device = Device(0)) -> "Tensor":
+        return Tensor.from_scalar(1.0, shape, dtype, device)
+
+    @staticmethod
+    def eye(n: int, dtype: int = F32, device: Device = Device(0)) -> "Tensor":
+        out = C.c_void_p()
+        L.check(L.lib().hx_tensor_eye(n, dtype, device.index, C.byref(out)))
+        return Tensor(out)
+
+    @staticmethod
+    def arange(start, end, step, dtype: int = F32, device: Device = Device(0)) -> "Tensor":
+        out = C.c_void_p()
+        L.check(L.lib().hx_tensor_arange(start, end, step, dtype, device.index, C.byref(out)))
+        return Tensor(out)
+
+    @staticmethod
+    def _random(kind, shape, p0, p1, device) -> "Tensor":
+        out = C.c_void_p()
+        L.check(L.lib().hx_tensor_random(kind, (C.c_int64 * len(shape))(*shape), len(shape), p0, p1, device.index, C.byref(out)))
+        return Tensor(out)
+
+    @staticmethod
+    def random_normal(shape, mean, std, device: Device = Device(0)) -> "Tensor":
+        return Tensor._random(0, shape, mean, std, device)
+
+    @staticmethod
+    def random_uniform(shape, lo, hi, device: Device = Device(0)) -> "Tensor":
+        return Tensor._random(1, shape, lo, hi, device)
+
+    @staticmethod
+    def random_bernoulli(shape, p, device: Device = Device(0)) -> "Tensor":
+        return Tensor._random(2, shape, p, 0.0, device)
+
     def __del__(self):
         try:
             if self._h:

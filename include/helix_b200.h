@@ -240,6 +240,19 @@ HX_API hx_status hx_s4_ref_forward_ssm(const float *u, const float *A_real, cons
                                 void *workspace, size_t workspace_bytes, void *stream);
 HX_API size_t hx_s4_ref_workspace_bytes(int32_t seq_len, int32_t d_state);
 
+/* ---- the reference-literal nn::ssm::MambaBlock::forward_mamba (crates/nn/src/ssm.rs:435-464): the conv is the
+ * identity (:467-471), B and C are computed and dropped (:447-449), selective_ssm is the S4 recurrence on delta
+ * (:474-483), and the result is scaled by the gate broadcast along rows (:458-459):
+ *   delta = x . delta_proj           [M, M] . [M, M]   (x must be square: forward_ssm wants dim0 == d_model)
+ *   y     = S4.forward_ssm(delta)    buffer [M, M] time-major, dt = 0.1
+ *   out[i][j] = y[i][j] * gate[j]
+ * All operands fp32.  workspace: hx_mamba_ssm_ref_workspace_bytes(d_model, d_state) bytes of device memory. */
+HX_API hx_status hx_mamba_ssm_ref_forward(const float *x, const float *delta_proj, const float *gate, const float *A_real,
+                                   const float *A_imag, const float *Bm, const float *Cm, const float *Dv, float *out,
+                                   int32_t d_model, int32_t d_state, void *workspace, size_t workspace_bytes,
+                                   void *stream);
+HX_API size_t hx_mamba_ssm_ref_workspace_bytes(int32_t d_model, int32_t d_state);
+
 /* ---- dense projections: C[M,N] = A[M,K] . W[N,K]^T (+ bias[N]), bf16 operands, fp32 accumulation
  *      in tensor memory (tcgen05), C written as bf16 or fp32.  Stands in for nn::Linear::forward
  *      (crates/nn/src/lib.rs:120-134) and the orphan cuBLAS sgemm call
@@ -386,6 +399,67 @@ HX_API hx_status hx_tensor_copy_from_host(hx_tensor *t, const float *data, int64
 HX_API hx_status hx_tensor_info(const hx_tensor *t, int32_t *ndim, int64_t *dims8, int32_t *dtype, int32_t *device_id);
 HX_API void *hx_tensor_data(const hx_tensor *t);                                      /* device pointer */
 HX_API void hx_tensor_free(hx_tensor *t);
+
+/* ---- tensor primitives on device tensors: what `impl TensorOps / TensorBroadcast / TensorActivation /
+ *      TensorRandom / TensorMixedPrecision for DeviceTensor` forwards to, so that the reference's generic blocks
+ *      (T: Tensor + TensorOps + TensorRandom + TensorBroadcast + TensorMixedPrecision, crates/nn/src/lib.rs:846,
+ *      crates/nn/src/ssm.rs:37) compile and run with the device tensor as T.  Semantics are the CPU tensor's
+ *      (crates/backend-cpu/src/lib.rs): every call returns a NEW tensor on the input's device (default stream);
+ *      F32 and BF16 storage, arithmetic in fp32.  Utility kernels, not the hot path. */
+/* TensorOps::{add, sub, mul, div, max, min, gt} (tensor.rs:64-73,106-109,127; lib.rs:570-632,852-899,951-975):
+ * identical shapes or HX_ERR_SHAPE_MISMATCH; gt gives 1.0 / 0.0. */
+typedef enum hx_binary_op {
+    HX_OP_ADD = 0, HX_OP_SUB = 1, HX_OP_MUL = 2, HX_OP_DIV = 3, HX_OP_MAX = 4, HX_OP_MIN = 5, HX_OP_GT = 6
+} hx_binary_op;
+HX_API hx_status hx_tensor_binary(int32_t op, const hx_tensor *a, const hx_tensor *b, hx_tensor **out);
+/* TensorOps::{sqrt, exp, log, sin, cos, tan, abs, sign, neg, pow(p0), clamp(p0, p1), add_scalar(p0),
+ * mul_scalar(p0), gt_scalar(p0)} (tensor.rs:79-130; lib.rs:759-949) and TensorActivation::{relu, gelu, silu,
+ * sigmoid, tanh, leaky_relu(p0)} (tensor.rs:191-209; lib.rs:1100-1198).  sign is f32::signum (+-1 also for +-0),
+ * gelu the tanh form, silu x / (1 + exp(-x)). */
+typedef enum hx_unary_op {
+    HX_OP_SQRT = 16, HX_OP_EXP = 17, HX_OP_LOG = 18, HX_OP_SIN = 19, HX_OP_COS = 20, HX_OP_TAN = 21, HX_OP_ABS = 22,
+    HX_OP_SIGN = 23, HX_OP_NEG = 24, HX_OP_RELU = 25, HX_OP_GELU = 26, HX_OP_SILU = 27, HX_OP_SIGMOID = 28,
+    HX_OP_TANH = 29, HX_OP_POW = 30, HX_OP_CLAMP = 31, HX_OP_ADD_SCALAR = 32, HX_OP_MUL_SCALAR = 33,
+    HX_OP_GT_SCALAR = 34, HX_OP_LEAKY_RELU = 35
+} hx_unary_op;
+HX_API hx_status hx_tensor_unary(int32_t op, const hx_tensor *a, float p0, float p1, hx_tensor **out);
+/* TensorOps::matmul (tensor.rs:76; lib.rs:634-757): [M,K].[K,N], [K].[K,N] or [M,K].[K]; the sum runs over k
+ * ascending in one fp32 accumulator with the product and the sum rounded separately, as the reference's loop does,
+ * so fp32 results are bit-identical to it.  Other ranks: HX_ERR_UNSUPPORTED_OPERATION. */
+HX_API hx_status hx_tensor_matmul(const hx_tensor *a, const hx_tensor *b, hx_tensor **out);
+/* The same product on raw device pointers, queued on `stream`: C[M,N] = A[M,K] . B[K,N], row-major, dense. */
+HX_API hx_status hx_matmul_ref(const void *A, const void *B, void *C, int32_t M, int32_t N, int32_t K, int32_t dtype,
+                        void *stream);
+/* Tensor::{transpose, slice, cat, stack, reshape, clone} (tensor.rs:34-46; lib.rs:94-335).  slice is 2-D only and
+ * cat 1-D only, like the reference.  stack of 1- to 3-D tensors lays the operands one after the other whatever
+ * `dim` is and puts the new axis at `dim` in the shape only (lib.rs:281-296: S4Block::forward_ssm relies on it). */
+HX_API hx_status hx_tensor_transpose(const hx_tensor *a, int64_t dim0, int64_t dim1, hx_tensor **out);
+HX_API hx_status hx_tensor_slice(const hx_tensor *a, const int64_t *start, const int64_t *end, int32_t n, hx_tensor **out);
+HX_API hx_status hx_tensor_cat(const hx_tensor *const *tensors, int32_t count, int64_t dim, hx_tensor **out);
+HX_API hx_status hx_tensor_stack(const hx_tensor *const *tensors, int32_t count, int64_t dim, hx_tensor **out);
+HX_API hx_status hx_tensor_reshape(const hx_tensor *a, const int64_t *dims, int32_t ndim, hx_tensor **out);
+HX_API hx_status hx_tensor_clone(const hx_tensor *a, hx_tensor **out);
+/* TensorBroadcast::{broadcast_to, expand} (tensor.rs:139-142; lib.rs:1352-1518): trailing axes aligned, axes of
+ * size 1 repeated; from 1 to 2, 2 to 3 and 1 to 3 dimensions in the reference's cases, equal ranks axis by axis.
+ * unsqueeze / squeeze are hx_tensor_reshape. */
+HX_API hx_status hx_tensor_broadcast_to(const hx_tensor *a, const int64_t *dims, int32_t ndim, hx_tensor **out);
+/* TensorMixedPrecision::cast / Tensor::to_dtype (tensor.rs:52,238): F32 <-> BF16, round to nearest even.  The device
+ * tensor has no other storage type: F16, F64, I8, I32, Bool give HX_ERR_UNSUPPORTED_OPERATION (the reference keeps
+ * f32 storage under every label, lib.rs:350-361, so nothing on the path depends on them). */
+HX_API hx_status hx_tensor_cast(const hx_tensor *a, int32_t dtype, hx_tensor **out);
+/* TensorOps::to_scalar (tensor.rs:133): a one-element tensor, else HX_ERR_INVALID_INPUT.  Synchronises. */
+HX_API hx_status hx_tensor_to_scalar(const hx_tensor *a, float *value);
+/* TensorOps::from_scalar, TensorRandom::{zeros, ones} = hx_tensor_full; TensorRandom::{eye, arange}
+ * (tensor.rs:118,223-232; lib.rs:901-911,1272-1349): arange adds `step` in fp32 while the value is below `end`. */
+HX_API hx_status hx_tensor_full(float value, const int64_t *dims, int32_t ndim, int32_t dtype, int32_t device_id,
+                         hx_tensor **out);
+HX_API hx_status hx_tensor_eye(int64_t n, int32_t dtype, int32_t device_id, hx_tensor **out);
+HX_API hx_status hx_tensor_arange(float start, float end, float step, int32_t dtype, int32_t device_id, hx_tensor **out);
+/* TensorRandom::{random_normal(mean p0, std p1), random_uniform(min p0, max p1), random_bernoulli(p p0)}
+ * (tensor.rs:214-220; lib.rs:1203-1270): F32, drawn from the stream hx_manual_seed seeds. */
+typedef enum hx_random_kind { HX_RANDOM_NORMAL = 0, HX_RANDOM_UNIFORM = 1, HX_RANDOM_BERNOULLI = 2 } hx_random_kind;
+HX_API hx_status hx_tensor_random(int32_t kind, const int64_t *dims, int32_t ndim, float p0, float p1, int32_t device_id,
+                           hx_tensor **out);
 
 HX_API hx_status hx_mamba_block_new(int64_t d_model, int64_t d_state, int64_t d_conv, int64_t expand, int32_t dtype,
                              int32_t device_id, hx_module **out);

@@ -125,3 +125,97 @@ def mamba_block(x, w, d_state, d_conv):
     Cm = dbc[:, R + d_state:].reshape(B, L, d_state)
     y = selective_scan(u, dtl, w["A"], Bm, Cm, D=w["D"], z=z, dt_bias=w["b_dt"], dt_softplus=True)
     return linear(y.reshape(B * L, E), w["W_out"]).reshape(B, L, M)
+
+
+# ---------------------------------------------------------------- tensor primitives (Oracle-R)
+# CpuTensor's own arithmetic, crates/backend-cpu/src/lib.rs.  Element-wise work goes through ndarray, i.e. plain
+# IEEE f32 operations, which numpy's float32 arrays reproduce bit for bit.
+
+def t_binary(name, a, b):
+    """add/sub/mul/div (:570-632), max/min (:852-899), gt (:951-975): identical shapes, else ShapeMismatch."""
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    if a.shape != b.shape:
+        raise ValueError("ShapeMismatch")
+    with np.errstate(all="ignore"):
+        return {"add": lambda: a + b, "sub": lambda: a - b, "mul": lambda: a * b, "div": lambda: a / b,
+                "max": lambda: np.fmax(a, b), "min": lambda: np.fmin(a, b),
+                "gt": lambda: (a > b).astype(np.float32)}[name]().astype(np.float32)
+
+
+def t_unary(name, x, p0=0.0, p1=0.0):
+    """pow .. neg (:759-899), scalar ops (:913-949), activations (:1100-1198).  Evaluated in float64 and rounded,
+    which stands in for Rust's f32 libm to within 1 ulp."""
+    x32 = np.asarray(x, np.float32)
+    x = x32.astype(np.float64)
+    p0f, p1f = np.float32(p0), np.float32(p1)
+    with np.errstate(all="ignore"):
+        if name == "sign":  # f32::signum: 1.0 for +0.0, -1.0 for -0.0, NaN for NaN
+            r = np.where(np.isnan(x32), x32, np.copysign(np.float32(1), x32))
+        elif name == "gelu":
+            c = np.float32(np.sqrt(np.float32(2.0) / np.float32(np.pi)))
+            r = 0.5 * x * (1.0 + np.tanh(float(c) * (x + 0.044715 * x ** 3)))
+        else:
+            r = {"sqrt": lambda: np.sqrt(x), "exp": lambda: np.exp(x), "log": lambda: np.log(x), "sin": lambda: np.sin(x),
+                 "cos": lambda: np.cos(x), "tan": lambda: np.tan(x), "abs": lambda: np.abs(x), "neg": lambda: -x,
+                 "relu": lambda: np.maximum(x, 0.0), "silu": lambda: x / (1.0 + np.exp(-x)),
+                 "sigmoid": lambda: 1.0 / (1.0 + np.exp(-x)), "tanh": lambda: np.tanh(x),
+                 "pow": lambda: np.power(x, float(p0f)), "clamp": lambda: np.minimum(np.maximum(x32, p0f), p1f),
+                 "add_scalar": lambda: x32 + p0f, "mul_scalar": lambda: x32 * p0f,
+                 "gt_scalar": lambda: (x32 > p0f).astype(np.float32),
+                 "leaky_relu": lambda: np.where(x32 >= 0, x32, p0f * x32)}[name]()
+    return np.asarray(r).astype(np.float32)
+
+
+def t_matmul(a, b):
+    """(2,2), (1,2), (2,1) products, k ascending into one f32 accumulator, product and sum rounded separately
+    (:634-757).  Other ranks: UnsupportedOperation."""
+    a, b = np.asarray(a, np.float32), np.asarray(b, np.float32)
+    if (a.ndim, b.ndim) not in ((2, 2), (1, 2), (2, 1)):
+        raise ValueError("UnsupportedOperation")
+    A = a.reshape(1, -1) if a.ndim == 1 else a
+    Bm = b.reshape(-1, 1) if b.ndim == 1 else b
+    if A.shape[1] != Bm.shape[0]:
+        raise ValueError("ShapeMismatch")
+    out = np.zeros((A.shape[0], Bm.shape[1]), np.float32)
+    for k in range(A.shape[1]):
+        out = (out + (A[:, k:k + 1] * Bm[k:k + 1, :]).astype(np.float32)).astype(np.float32)
+    return out.reshape(-1) if (a.ndim == 1 or b.ndim == 1) else out
+
+
+def t_transpose(a, d0, d1):
+    """permuted_axes(...).to_owned() (:115-137)."""
+    return np.ascontiguousarray(np.swapaxes(np.asarray(a), d0, d1))
+
+
+def t_slice(a, start, end):
+    """2-D only (:139-183)."""
+    a = np.asarray(a)
+    if len(start) != a.ndim or len(end) != a.ndim:
+        raise ValueError("ShapeMismatch")
+    for i in range(a.ndim):
+        if start[i] >= a.shape[i] or end[i] > a.shape[i] or start[i] >= end[i]:
+            raise ValueError("InvalidDimension")
+    if a.ndim != 2:
+        raise ValueError("UnsupportedOperation")
+    return np.ascontiguousarray(a[start[0]:end[0], start[1]:end[1]])
+
+
+def t_cat(ts, dim):
+    """1-D only (:184-252)."""
+    if ts[0].ndim != 1:
+        raise ValueError("UnsupportedOperation")
+    return np.concatenate(ts)
+
+
+def t_stack(ts, dim):
+    """The buffer is the operands one after the other, [count, operand shape...], whatever `dim`; the shape LABEL
+    has the new axis inserted at `dim` (:254-335).  Returns (buffer, label)."""
+    buf = np.stack([np.asarray(t) for t in ts], axis=0)
+    label = list(ts[0].shape)
+    label.insert(dim, len(ts))
+    return buf, tuple(label)
+
+
+def t_broadcast_to(a, shape):
+    """Trailing axes aligned, axes of size 1 repeated (:1352-1518)."""
+    return np.ascontiguousarray(np.broadcast_to(np.asarray(a), shape))

@@ -76,7 +76,8 @@ def test_round_trip_and_foreign_device_labels(tmp_path):
     assert np.array_equal(back[0], a)
 
 
-@pytest.mark.parametrize("damage", ["truncate_header", "truncate_body", "trailing", "bad_version", "count_mismatch", "missing"])
+@pytest.mark.parametrize("damage", ["truncate_header", "truncate_body", "trailing", "bad_version", "count_mismatch", "missing",
+                                    "huge_count", "wrapping_shape"])
 def test_malformed_files_are_refused(tmp_path, damage):
     p = str(tmp_path / "c.pt")
     checkpoint.write(p, [np.arange(6, dtype=np.float32).reshape(2, 3)], epoch=1)
@@ -92,6 +93,13 @@ def test_malformed_files_are_refused(tmp_path, damage):
         raw = raw[:4 + jl + 8] + b"\x02" + raw[4 + jl + 9:]
     elif damage == "count_mismatch":
         raw = raw.replace(b'"model_params_count":1', b'"model_params_count":2')
+    elif damage in ("huge_count", "wrapping_shape"):
+        # after the JSON: u64 tensor count, u8 version, u64 ndim, the dims, u64 element count, the elements.
+        # Sizes come from the file: an element count whose byte size wraps around 2^64, or a shape whose product
+        # does, must be refused with a status, not reach an allocation.
+        o = 4 + jl + 8 + 1 + 8
+        d0, d1, cnt = ((1 << 62), 1, (1 << 62)) if damage == "huge_count" else ((1 << 62), 4, 0)
+        raw = raw[:o] + struct.pack("<QQQ", d0, d1, cnt) + raw[o + 24:]
     if damage == "missing":
         os.remove(p)
     else:
