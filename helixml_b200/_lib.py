@@ -99,6 +99,8 @@ _PROTOS = {
     "hx_selective_scan_fwd_noalloc": (C.c_int, [C.POINTER(ScanArgs), C.c_void_p]),
     "hx_scan_check_geometric": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int32)]),
     "hx_device_status": (C.c_int, [C.POINTER(C.c_int32), C.c_int32]),
+    "hx_device_check": (C.c_int, []),
+    "hx_debug_scan_orphan_segment": (C.c_int, [C.POINTER(ScanArgs), C.c_int32, C.c_void_p]),
     "hx_probe_pipe": (C.c_int, [C.c_int32, C.c_void_p, C.c_size_t, C.POINTER(C.c_double), C.c_void_p]),
     "hx_conv1d_silu_fwd": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                      C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
@@ -217,6 +219,11 @@ def exported_symbols():
 def check(status: int) -> None:
     if status != HX_OK:
         raise HxError(status, lib().hx_last_error().decode())
+
+
+def check_device() -> None:
+    """Raises HxError (BackendError) when a bounded device-side wait ran out since the last check."""
+    check(lib().hx_device_check())
 
 
 def device_status(clear: bool = True) -> int:

@@ -558,12 +558,14 @@ ByteLM::~ByteLM() {
 }
 
 Result<Unit> ByteLM::set_profile(bool enable) {
+    std::lock_guard<std::recursive_mutex> lock(mu_);
     delete prof_;
     prof_ = enable ? new Profile() : nullptr;
     return Unit{};
 }
 
 Result<Unit> ByteLM::read_profile(float *ms9, int *forwards) {
+    std::lock_guard<std::recursive_mutex> lock(mu_);
     if (!ms9 || !forwards) return err(HX_ERR_INVALID_INPUT, "read_profile: NULL argument");
     for (int i = 0; i < 9; ++i) ms9[i] = 0.f;
     *forwards = 0;
@@ -630,6 +632,7 @@ Result<Unit> ByteLM::ensure_buffers(int64_t batch, int64_t seq_len) {
 }
 
 int64_t ByteLM::launches_per_forward() const {
+    std::lock_guard<std::recursive_mutex> lock(mu_);
     // embedding + per layer (norm + the block's 5 or 6 kernels) + final norm + logits GEMM
     int32_t per_block = 6;
     if (buf_ && buf_->batch > 0 && !blocks.empty()) {
@@ -694,6 +697,7 @@ Result<Unit> ByteLM::enqueue_step(void *stream) {
 }
 
 int64_t ByteLM::launches_per_decode_step() const {
+    std::lock_guard<std::recursive_mutex> lock(mu_);
     // embedding + per layer (fused: in_proj with norm and conv step, x_proj, state step, out_proj with the add;
     // otherwise: norm, in_proj, conv step, x_proj, state step, out_proj, residual add) + final norm + head
     const int64_t batch = dec_ ? dec_->batch : 1;
@@ -702,6 +706,7 @@ int64_t ByteLM::launches_per_decode_step() const {
 }
 
 Result<Unit> ByteLM::decode_step_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, void *stream) {
+    std::lock_guard<std::recursive_mutex> lock(mu_);
     if (!tokens_dev || !logits_dev) return err(HX_ERR_INVALID_INPUT, "ByteLM::decode_step_device: NULL buffer");
     if (!dec_ || dec_->batch != batch)
         return err(HX_ERR_INVALID_INPUT, "ByteLM::decode_step_device: no prefill state for batch " + std::to_string(batch));
@@ -745,6 +750,7 @@ Result<Unit> ByteLM::decode_step_device(const uint8_t *tokens_dev, void *logits_
 
 Result<Unit> ByteLM::run_layers(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream,
                                 bool keep_state) {
+    std::lock_guard<std::recursive_mutex> lock(mu_);
     if (batch <= 0 || seq_len <= 0) return err(HX_ERR_INVALID_DIMENSION, "ByteLM: batch and seq_len must be positive");
     HELIX_TRY(use_device(device_));
     HELIX_TRY(ensure_buffers(batch, seq_len));
@@ -802,6 +808,7 @@ Result<Unit> ByteLM::run_layers(const uint8_t *tokens_dev, void *logits_dev, int
 }
 
 Result<Unit> ByteLM::forward_host(const uint8_t *tokens_host, void *logits_host, int64_t batch, int64_t seq_len, void *stream) {
+    std::lock_guard<std::recursive_mutex> lock(mu_);
     if (!tokens_host || !logits_host) return err(HX_ERR_INVALID_INPUT, "ByteLM::forward_host: NULL buffer");
     HELIX_TRY(use_device(device_));
     HELIX_TRY(ensure_buffers(batch, seq_len));
@@ -813,6 +820,7 @@ Result<Unit> ByteLM::forward_host(const uint8_t *tokens_host, void *logits_host,
 }
 
 Result<DeviceTensor> ByteLM::forward(const DeviceTensor &tokens) const {
+    std::lock_guard<std::recursive_mutex> lock(mu_);
     if (tokens.dtype() != DType::U8) return err(HX_ERR_DTYPE_MISMATCH, "ByteLM: tokens must be U8");
     if (tokens.ndim() != 2) return err(HX_ERR_SHAPE_MISMATCH, "ByteLM: expected tokens [batch, seq_len], got " + shape_str(tokens.shape()));
     const int64_t B = tokens.shape().dim(0), L = tokens.shape().dim(1);
@@ -821,7 +829,7 @@ Result<DeviceTensor> ByteLM::forward(const DeviceTensor &tokens) const {
     if (B * L == 0) return logits;
     // forward() is const in the interface; the activation buffers are a cache
     HELIX_TRY(const_cast<ByteLM *>(this)->forward_device(static_cast<const uint8_t *>(tokens.data()), logits.data(), B, L, nullptr));
-    HELIX_TRY_ABI(hx_stream_synchronize(nullptr));
+    HELIX_TRY_ABI(hx_device_check());  // synchronises; a device-side wait that ran out is a BackendError
     return logits;
 }
 

@@ -20,6 +20,7 @@
 #pragma once
 
 #include <memory>
+#include <mutex>
 #include <string>
 #include <utility>
 #include <vector>
@@ -277,6 +278,11 @@ class ByteLM : public Module {
     bool decode_graph_ = true;
     struct Profile;
     Profile *prof_ = nullptr;
+    // The activation buffers, the decode state and the profile belong to the module: every call that touches them
+    // holds this lock while it queues its work (forward() until its result is complete), so threads that share one
+    // handle are serialised.  Their work must go to ONE stream: stream order is what keeps a later call from
+    // overwriting buffers an earlier one still reads.
+    mutable std::recursive_mutex mu_;
 };
 
 // Seed of the parameter initialisers (the reference draws from an unseeded thread_rng,

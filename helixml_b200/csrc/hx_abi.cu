@@ -136,6 +136,17 @@ hx_status hx_device_status(int32_t *status, int32_t clear) {
     return HX_OK;
 }
 
+hx_status hx_device_check(void) {
+    int32_t st = 0;
+    hx_status s = hx_device_status(&st, 1);
+    if (s != HX_OK) return s;
+    if (st == 0) return HX_OK;
+    return hx::fail(HX_ERR_BACKEND,
+                    "a bounded device-side wait ran out (status 0x%x:%s%s%s%s%s%s); outputs since the last check are not valid", st,
+                    (st & 1) ? " tile load" : "", (st & 2) ? " stage release" : "", (st & 4) ? " output tile" : "",
+                    (st & 8) ? " output release" : "", (st & 16) ? " segment carry" : "", (st & 32) ? " GEMM pipeline" : "");
+}
+
 hx_status hx_stream_synchronize(void *stream) {
     HX_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
     return HX_OK;

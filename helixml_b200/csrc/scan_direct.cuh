@@ -123,7 +123,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     constexpr int OFF_Z = Cfg::X_BYTES, OFF_DTT = Cfg::X_BYTES + Cfg::ROW_BYTES;  // inside a box: x, z, dt
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x, b = blockIdx.y, seg = blockIdx.z;
+    const int tile = blockIdx.x, b = blockIdx.y, seg = blockIdx.z + p.seg_base;
     const int d0 = tile * Cfg::DT;
     const int t_seg0 = seg * p.seg_len;
     const int t_seg1 = min(p.L, t_seg0 + p.seg_len);
@@ -456,7 +456,8 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     if (MODE == 0 && p.n_segments > 1 && seg > 0) {
         const int fidx = (((seg - 1) * p.B + b) * gridDim.x + tile) * 8 + warp;
         bool ok = false;
-        for (int it = 0; it < (1 << 22); ++it) {
+        const int poll_limit = g_carry_polls;
+        for (int it = 0; it < poll_limit; ++it) {
             int v;
             asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.flags + fidx) : "memory");
             if (v == p.epoch) { ok = true; break; }

@@ -33,6 +33,10 @@ namespace scan {
 // Per-device status word: a bounded wait that ran out ORs its code in here.
 __device__ int g_wait_status = 0;
 enum : int { kWaitFull = 1, kWaitEmpty = 2, kWaitOutFull = 4, kWaitOutEmpty = 8, kWaitCarry = 16 };
+// Polls (40 ns apart) a segment spends on its predecessor's carry flag before it gives up, records kWaitCarry and
+// carries on from a zero state.  The default is about 0.2 s; hx_debug_scan_orphan_segment lowers it for one launch.
+constexpr int kCarryPollsDefault = 1 << 22;
+__device__ int g_carry_polls = kCarryPollsDefault;
 
 // ------------------------------------------------------------------------------------------
 // simple kernel
@@ -131,6 +135,8 @@ struct TiledParams {
     int *flags;       // [n_segments-1, B, tiles, 8] one per consumer warp, set to `epoch` once its carry is written
     int epoch;
     int dt_rank;      // > 0: dt is produced in the kernel from dt_low and W_dt (direct kernel only)
+    int seg_base;     // segment index of grid.z == 0 (0 except in hx_debug_scan_orphan_segment, which launches a
+                      // segment without its predecessor)
     float *sdt;       // look-back form: [n_segments-1, B, D] sum of dt over each segment (its aggregate decay is
                       // exp(A * sdt)); `carry` then holds the segments' end states from a zero state
 };
@@ -225,7 +231,7 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
                   OFF_C = OFF_B + Cfg::BC_BYTES, OFF_BF = OFF_C + Cfg::BC_BYTES, OFF_CF = OFF_BF + Cfg::BCF_BYTES;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x, b = blockIdx.y, seg = blockIdx.z;
+    const int tile = blockIdx.x, b = blockIdx.y, seg = blockIdx.z + p.seg_base;
     const int d0 = tile * DT;
     const int t_seg0 = seg * p.seg_len;
     const int t_seg1 = min(p.L, t_seg0 + p.seg_len);
@@ -413,7 +419,8 @@ scan_tiled_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constan
         // the same warp index of the previous segment's CTA owns the same channels
         const int fidx = (((seg - 1) * p.B + b) * gridDim.x + tile) * 8 + warp;
         bool ok = false;
-        for (int it = 0; it < (1 << 22); ++it) {
+        const int poll_limit = g_carry_polls;
+        for (int it = 0; it < poll_limit; ++it) {
             int v;
             asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p.flags + fidx) : "memory");
             if (v == p.epoch) { ok = true; break; }
@@ -832,7 +839,7 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
     p.n_segments = n_seg; p.seg_len = seg_len;
     p.A = a->A; p.Dskip = a->Dskip; p.conv_w = a->conv_w; p.conv_b = a->conv_b; p.dt_bias = a->dt_bias;
     p.h_last = a->h_last;
-    p.carry = nullptr; p.flags = nullptr; p.epoch = 1; p.dt_rank = 0; p.sdt = nullptr;
+    p.carry = nullptr; p.flags = nullptr; p.epoch = 1; p.dt_rank = 0; p.sdt = nullptr; p.seg_base = 0;
     if (n_seg > 1) {
         const WsLayout wl = ws_layout(a, n_seg);
         HX_REQUIRE(a->workspace && a->workspace_bytes >= wl.total, HX_ERR_INVALID_INPUT,
@@ -965,6 +972,9 @@ static bool lookback_ok(const hx_scan_args *a) {
     return true;
 }
 
+// hx_debug_scan_orphan_segment: first segment the calling thread's next chained launch starts (0 = all of them)
+static thread_local int t_orphan_from = 0;
+
 // form: 0 = one pass (segments, if any, chained through carries), 1 = look-back (aggregate pass + output pass)
 static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t st, int form = 0) {
     HX_REQUIRE(a->d_state == 16, HX_ERR_UNSUPPORTED_OPERATION, "the direct scan needs d_state == 16 (got %d)", a->d_state);
@@ -991,6 +1001,7 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
     p.h_last = a->h_last;
     p.carry = nullptr; p.flags = nullptr; p.epoch = 1; p.sdt = nullptr;
     p.dt_rank = a->W_dt ? a->dt_rank : 0;
+    p.seg_base = t_orphan_from;
     if (n_seg > 1) {
         const WsLayout wl = ws_layout(a, n_seg);
         HX_REQUIRE(a->workspace && a->workspace_bytes >= wl.total, HX_ERR_INVALID_INPUT,
@@ -1050,7 +1061,7 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
 
     HX_REQUIRE(a->batch <= 65535 && n_seg <= 65535, HX_ERR_INVALID_DIMENSION, "batch %d or segments %d exceed the grid limit",
                a->batch, n_seg);
-    dim3 grid(tiles, a->batch, n_seg);
+    dim3 grid(tiles, a->batch, n_seg - p.seg_base);
     const bool geom = a->a_geometric != 0;
     const bool stdp = a->conv_w != nullptr && a->z != nullptr && a->dt_softplus != 0;
     // the block's own call: u already convolved, gate and softplus present, geometric A
@@ -1330,6 +1341,22 @@ hx_status hx_selective_scan_fwd_noalloc(const hx_scan_args *a, void *stream) {
     // launch_tiled clears the carry flags with a memset on `stream` before the kernel, so nothing is
     // inherited from the previous call; the carry states themselves are always written before they are read.
     return hx::scan::launch_tiled(&b, true, (cudaStream_t)stream);
+}
+
+hx_status hx_debug_scan_orphan_segment(const hx_scan_args *a, int32_t polls, void *stream) {
+    hx_status s = hx::scan::validate(a);
+    if (s != HX_OK) return s;
+    HX_REQUIRE(polls >= 1 && polls <= hx::scan::kCarryPollsDefault, HX_ERR_INVALID_INPUT, "polls %d outside [1, 2^22]", polls);
+    HX_REQUIRE(a->d_state == 16 && a->seq_splits == 2 && a->seq_len > 2 * hx::scan::kPlanChunk, HX_ERR_INVALID_INPUT,
+               "hx_debug_scan_orphan_segment: d_state 16, seq_splits 2 and more than 64 steps");
+    cudaStream_t st = (cudaStream_t)stream;
+    HX_CUDA(cudaMemcpyToSymbolAsync(hx::scan::g_carry_polls, &polls, sizeof(int), 0, cudaMemcpyHostToDevice, st));
+    hx::scan::t_orphan_from = 1;  // segment 1 alone: nobody publishes the flag it waits for
+    s = hx::scan::launch_direct(a, true, st);
+    hx::scan::t_orphan_from = 0;
+    const int def = hx::scan::kCarryPollsDefault;
+    cudaMemcpyToSymbolAsync(hx::scan::g_carry_polls, &def, sizeof(int), 0, cudaMemcpyHostToDevice, st);
+    return s;
 }
 
 hx_status hx_scan_check_geometric(const float *A, int32_t d_inner, int32_t d_state, int32_t *is_geometric) {

@@ -18,7 +18,10 @@
  *  - Every entry point returns an hx_status whose values map one to one onto the
  *    reference's TensorError variants (crates/tensor-core/src/error.rs:7-37); bad input is
  *    reported, never trapped.  hx_last_error() gives the calling thread's last message.
- *  - All entry points are re-entrant and thread-safe.
+ *  - All entry points are re-entrant and thread-safe: the kernel-level ones keep no state between calls, and a
+ *    module handle serialises the calls threads make on it with a lock.  The byte LM keeps its activation buffers
+ *    and its decode state inside the module, so all serving calls on ONE handle must be queued on one stream
+ *    (stream order keeps a later call from overwriting what an earlier one still reads); use one handle per stream.
  *  - Strides are in ELEMENTS of the tensor's dtype.  The innermost (channel) stride is 1.
  */
 #ifndef HELIX_B200_H
@@ -200,6 +203,15 @@ HX_API hx_status hx_scan_check_geometric(const float *A, int32_t d_inner, int32_
  * clears it when `clear` is non-zero.  A non-zero word means the outputs of the launches since the last
  * clear are not valid; map it to TensorError::BackendError. */
 HX_API hx_status hx_device_status(int32_t *status, int32_t clear);
+/* The same as a Result: synchronises, clears the word, and returns HX_ERR_BACKEND (TensorError::BackendError) with
+ * a message naming the waits that ran out when it was non-zero, HX_OK otherwise. */
+HX_API hx_status hx_device_check(void);
+/* Test aid for the path above (no counterpart in the reference): launches the chained two-segment direct scan for
+ * `args` (d_state 16, seq_splits 2, workspace given) WITHOUT its first segment and with the carry wait limited to
+ * `polls` polls of 40 ns, so that segment 1's wait for a flag nobody publishes runs out after polls * 40 ns: the
+ * kernel records the event in the status word, scans on from a zero state and returns normally.  y is not valid
+ * afterwards; hx_device_check() reports the event.  The default limit (2^22 polls) is restored on `stream`. */
+HX_API hx_status hx_debug_scan_orphan_segment(const hx_scan_args *args, int32_t polls, void *stream);
 
 /* Measures, on the current device, how many results per second one arithmetic pipe retires: fp32
  * fused multiply-adds (scalar, or the packed two-wide form, counted per lane) or special-function

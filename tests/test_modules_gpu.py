@@ -1,9 +1,11 @@
 """GPU tests of the module-level API (the reference's constructors and forward): same names, same argument
 meaning, same error behaviour, outputs checked against the oracle on injected weights."""
+import ctypes as C
+
 import numpy as np
 import pytest
 
-from conftest import BF16_TOL, FP32_TOL, fp32_tol_err, rel_l2
+from conftest import BF16_TOL, FP32_TOL, fp32_tol_err, rel_l2, to_dev
 from helixml_b200 import synth
 from oracle import cbind
 
@@ -252,3 +254,116 @@ def test_byte_lm_checkpoint_round_trip(tmp_path):
     meta = b.load_checkpoint(p)
     assert meta["epoch"] == 1 and meta["step"] == 10
     assert np.array_equal(b.forward(nn.Tensor.from_numpy(tok)).numpy(), la)
+
+
+def _per_position_worst(got, ref):
+    """Largest relative L2 error over single positions (one token's output vector each)."""
+    g, r = got.reshape(-1, got.shape[-1]).astype(np.float64), ref.reshape(-1, ref.shape[-1]).astype(np.float64)
+    return float(np.max(np.linalg.norm(g - r, axis=1) / np.maximum(np.linalg.norm(r, axis=1), 1e-30)))
+
+
+def test_mamba_block_full_size_config3_shape_sampled_rows():
+    """One block at the benchmark's shape, [32, 2048, 768] bf16: the path the byte LM times (tensor-core GEMMs, the
+    one-lane-per-channel scan with the dt projection inside and chained sequence segments).  Batch rows are
+    independent, so the oracle runs on the first and the last row; the gate is applied to the rows as a whole and
+    to every position by itself (a lost carry would spoil the positions after one segment boundary)."""
+    import torch
+    from helixml_b200 import _lib, ops
+    B, L, M = 32, 2048, 768
+    w = synth.mamba_block_weights(3, M, 16, 4, 2, init="0.02")
+    big = ("W_in", "W_x", "W_dt", "W_out")
+    wq = {k: (synth.round_bf16(v) if k in big else v) for k, v in w.items()}
+    x = synth.round_bf16(synth.normal(3, "xfull", (B, L, M)))
+    dev = {k: to_dev(v, "bf16" if k in big else None) for k, v in wq.items()}
+    got = ops.mamba_block(to_dev(x, "bf16"), dev, 16, 4)
+    _lib.check_device()
+    a = _lib.MambaBlockArgs()
+    a.batch, a.seq_len, a.d_model, a.d_inner, a.d_state, a.d_conv, a.dt_rank = B, L, M, 2 * M, 16, 4, 48
+    a.io_dtype, a.scan_variant, a.a_geometric = _lib.HX_BF16, _lib.SCAN_AUTO, 1
+    a.W_dt = dev["W_dt"].data_ptr()
+    n = C.c_int32(0)
+    _lib.check(_lib.lib().hx_mamba_block_kernel_launches(C.byref(a), C.byref(n)))
+    assert n.value == 5  # in_proj, conv, x_proj, scan with the dt projection inside, out_proj
+    rows = [0, B - 1]
+    ref = cbind.mamba_block(x[rows], wq, 16, 4)
+    g = got[rows].float().cpu().numpy()
+    assert rel_l2(g, ref) <= BF16_TOL
+    assert _per_position_worst(g, ref) <= 3 * BF16_TOL
+
+
+def test_byte_lm_full_size_config3_sampled_sequences():
+    """Benchmark configuration 3 at full size: 24 blocks, d_model 768, batch 32 x 2048 bytes, bf16 -- the very call
+    bench.py times.  The logits of the first and the last sequence are compared with the CPU oracle of the whole
+    model (rows are independent); the launch count shows that every block ran the fused-dt scan."""
+    import torch
+    from helixml_b200 import _lib, nn
+    nl, M, B, L = 24, 768, 32, 2048
+    emb, layers, normf = _lm_weights(3, nl, M)
+    big = ("W_in", "W_x", "W_dt", "W_out")
+    layers_q = [{k: (synth.round_bf16(v) if k in big else v) for k, v in l.items()} for l in layers]
+    emb_q = synth.round_bf16(emb)
+    tok = synth.random_bytes(3, "tokfull", (B, L))
+    lm = nn.ByteLM(nl, M, dtype=nn.BF16)
+    lm.load_weights(emb_q, layers_q, normf)
+    tok_d = torch.from_numpy(tok).cuda()
+    logits = torch.empty((B, L, 256), dtype=torch.bfloat16, device="cuda")
+    lm.forward_device(tok_d.data_ptr(), logits.data_ptr(), B, L, torch.cuda.current_stream().cuda_stream)
+    _lib.check_device()
+    assert lm.launches_per_forward == 1 + nl * 6 + 2  # norm + 5 kernels per block: the dt projection is in the scan
+    rows = [0, B - 1]
+    ref = cbind.byte_lm(tok[rows], emb_q, layers_q, normf, 16, 4)
+    g = logits[rows].float().cpu().numpy()
+    assert rel_l2(g, ref) <= BF16_TOL
+    assert _per_position_worst(g, ref) <= 3 * BF16_TOL
+
+
+def test_byte_lm_small_batch_runs_the_lookback_scan():
+    """Four sequences per GPU is what one of eight GPUs gets of configuration 3's batch: too few chains for one pass,
+    so the blocks run the look-back form of the scan (two launches), still with the dt projection inside."""
+    import torch
+    from helixml_b200 import _lib, nn
+    nl, M, B, L = 3, 768, 4, 1024
+    emb, layers, normf = _lm_weights(11, nl, M)
+    big = ("W_in", "W_x", "W_dt", "W_out")
+    layers_q = [{k: (synth.round_bf16(v) if k in big else v) for k, v in l.items()} for l in layers]
+    emb_q = synth.round_bf16(emb)
+    tok = synth.random_bytes(11, "tok", (B, L))
+    lm = nn.ByteLM(nl, M, dtype=nn.BF16)
+    lm.load_weights(emb_q, layers_q, normf)
+    tok_d = torch.from_numpy(tok).cuda()
+    logits = torch.empty((B, L, 256), dtype=torch.bfloat16, device="cuda")
+    lm.forward_device(tok_d.data_ptr(), logits.data_ptr(), B, L, torch.cuda.current_stream().cuda_stream)
+    _lib.check_device()
+    assert lm.launches_per_forward == 1 + nl * 7 + 2  # norm, in_proj, conv, x_proj, aggregate pass, output pass, out_proj
+    ref = cbind.byte_lm(tok, emb_q, layers_q, normf, 16, 4)
+    g = logits.float().cpu().numpy()
+    assert rel_l2(g, ref) <= BF16_TOL
+    assert _per_position_worst(g, ref) <= 3 * BF16_TOL
+
+
+def test_byte_lm_handle_shared_by_two_threads():
+    """Two threads call forward on ONE byte-LM handle (default stream): the module serialises them, and each gets
+    the logits of its own tokens."""
+    import threading
+    from helixml_b200 import nn
+    emb, layers, normf = _lm_weights(12, 2, 64)
+    lm = nn.ByteLM(2, 64, dtype=nn.F32)
+    lm.load_weights(emb, layers, normf)
+    toks = [synth.random_bytes(12, f"t{i}", (2, 70)) for i in range(2)]
+    want = [lm.forward(nn.Tensor.from_numpy(t)).numpy() for t in toks]
+    got, errors = [None, None], []
+
+    def run(i):
+        try:
+            for _ in range(5):
+                got[i] = lm.forward(nn.Tensor.from_numpy(toks[i])).numpy()
+        except Exception as e:  # noqa: BLE001
+            errors.append(repr(e))
+
+    th = [threading.Thread(target=run, args=(i,)) for i in range(2)]
+    for t in th:
+        t.start()
+    for t in th:
+        t.join()
+    assert not errors, errors
+    assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1])

@@ -452,3 +452,43 @@ def test_config4_shard_long_sequences_sampled_chains():
                                to_np(Cm[rows]), D=to_np(Dk[sl]), z=to_np(z[rows][:, :, sl]), conv_w=to_np(cw[sl]))
     for name, (y, _) in outs.items():
         assert rel_l2(to_np(y[rows][:, :, sl]), ref) <= BF16_TOL, name
+
+
+def test_carry_wait_that_runs_out_is_reported_not_trapped():
+    """A chained segment whose predecessor never publishes its carry: the bounded wait gives up (here after 2000
+    polls, about 0.1 ms), the kernel records the event and returns, the host sees TensorError::BackendError through
+    hx_device_check, and the next launch on the same context is clean.  The predecessor is simply not launched
+    (hx_debug_scan_orphan_segment); nothing traps, faults or waits without a limit."""
+    import ctypes as C
+    import torch
+    from helixml_b200 import _lib, ops
+    inp = synth.scan_inputs(52, 1, 256, 128, 16, 4, bf16=True)
+    dev = {k: to_dev(v, "bf16" if k in ("x", "dt", "z", "B", "C") else None) for k, v in inp.items()}
+    y = torch.empty_like(dev["x"])
+    a = _lib.ScanArgs()
+    a.batch, a.seq_len, a.d_inner, a.d_state, a.d_conv = 1, 256, 128, 16, 4
+    a.io_dtype, a.dt_softplus, a.variant, a.seq_splits, a.a_geometric = _lib.HX_BF16, 1, _lib.SCAN_DIRECT, 2, 1
+    for name, t in (("x", dev["x"]), ("dt", dev["dt"]), ("z", dev["z"]), ("y", y)):
+        setattr(a, name, t.data_ptr())
+        setattr(a, f"{name}_batch_stride", t.stride(0))
+        setattr(a, f"{name}_row_stride", t.stride(1))
+    for name, f, t in (("Bm", "B", dev["B"]), ("Cm", "C", dev["C"])):
+        setattr(a, name, t.data_ptr())
+        setattr(a, f"{f}_batch_stride", t.stride(0))
+        setattr(a, f"{f}_row_stride", t.stride(1))
+    a.A, a.Dskip, a.conv_w = dev["A"].data_ptr(), dev["D"].data_ptr(), dev["conv_w"].data_ptr()
+    ws = torch.empty(ops.scan_workspace_bytes(1, 256, 128, torch.bfloat16, 2), dtype=torch.uint8, device="cuda")
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert _lib.device_status() == 0
+    _lib.check(_lib.lib().hx_debug_scan_orphan_segment(C.byref(a), 2000, st))
+    with pytest.raises(_lib.HxError) as e:
+        _lib.check_device()
+    assert e.value.variant == "BackendError" and "segment carry" in str(e.value)
+    assert _lib.device_status() == 0  # the check cleared the word
+    # the context is intact and the default limit is back: the complete two-segment scan is right
+    got = run_gpu(inp, "bf16", variant=DIRECT, seq_splits=2, geom=True)
+    check(got, run_ref(inp), "bf16")
+    # argument checks of the test aid itself
+    a.seq_splits = 3
+    assert _lib.lib().hx_debug_scan_orphan_segment(C.byref(a), 2000, st) == 10

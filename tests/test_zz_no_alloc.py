@@ -4,14 +4,17 @@ It exists for callers that may not allocate device memory when they run the scan
 their own pool, or a thread that must stay out of the CUDA allocator).  The carries between sequence
 segments live in an array inside the library instead of a caller workspace, so the output must equal what
 hx_selective_scan_fwd(variant = SEQSPLIT) produces with a caller workspace -- the same kernel on the same
-inputs -- and must stay equal on a second call, which reuses the array with the first call's contents in it."""
+inputs -- and must stay equal on a second call, which reuses the array with the first call's contents in it.
+Because the two share a kernel, the output is also held against the CPU oracle, and the driver's count of free
+device memory must not move across the call."""
 import ctypes as C
 
 import numpy as np
 import pytest
 
-from conftest import to_dev
+from conftest import BF16_TOL, FP32_TOL, fp32_tol_err, rel_l2, to_dev
 from helixml_b200 import synth
+from oracle import cbind
 
 pytestmark = pytest.mark.gpu
 
@@ -50,9 +53,15 @@ def test_noalloc_matches_workspace_variant_twice(dtype):
                                   conv_w=dev["conv_w"], variant=L.SCAN_SEQSPLIT, seq_splits=4, a_geometric=True)
         got = torch.full_like(want, float("nan"))
         a = _args(L, dev, got, code, 4)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         L.check(lib.hx_selective_scan_fwd_noalloc(C.byref(a), stream))
         torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the amount of free device memory"
         assert L.device_status() == 0
+        ref = cbind.selective_scan(inp["x"], inp["dt"], inp["A"], inp["B"], inp["C"], D=inp["D"], z=inp["z"], conv_w=inp["conv_w"])
+        g = got.float().cpu().numpy()
+        assert (rel_l2(g, ref) <= BF16_TOL) if dtype == "bf16" else (fp32_tol_err(g, ref) <= FP32_TOL)
         # same kernel, same inputs: the tests' tolerance for two runs of one kernel is exact equality
         assert torch.equal(got, want), f"call {call}: max diff {(got.float() - want.float()).abs().max().item()}"
 
