@@ -1,13 +1,16 @@
 """Benchmark of the state-space hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload scan_cfg2|scan_cfg4|lm_cfg3] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload lm_cfg3|scan_cfg2|scan_cfg4|...] [--impl reference]
 
 Prints ONE JSON line.  A step is one pass of the hot path over one batch of seeded synthetic input
 (inputs far larger than L2, so no flush between steps is needed).  `value` is whole-job tokens/s with
 inputs resident in HBM; `e2e` is the same metric through the host-buffer C-ABI call, host<->device
-copies inside the timed region.  With N > 1 (torchrun, one rank per GPU) every rank runs the full
-per-GPU workload on its own shard (weak scaling, no collective on the path) and the time is the max
-over ranks.  `--impl reference` times the CPU oracle port of the same path on the host cores."""
+copies inside the timed region.  With N > 1 (torchrun, one rank per GPU) the default workload, the byte-LM
+prefill of one batch of 32 sequences, is sharded by batch rows (32 -> 16 / 8 / 4 rows per GPU, a weight replica per
+rank, no collective on the path: strong scaling); `--scaling weak` gives every rank the whole batch instead.  The
+time is the max over ranks.  `--impl reference` times the CPU oracle port of the same path on the host cores.
+The `kernels_*`, `s4_cfg1`, `decode_cfg3` and `ref_benches` workloads time single kernels / calls of the path
+(one JSON line per case); the ncu summaries under profiles/ were captured on them."""
 from __future__ import annotations
 
 import argparse
@@ -37,6 +40,12 @@ WORKLOADS = {
     # the scan of one block of configuration 3 (batch 32 x 2048, d_inner 1536)
     "scan_cfg3": dict(kind="scan", batch=32, seq_len=2048, d_inner=1536, d_state=16, d_conv=4, seed=3),
     "lm_cfg3": dict(kind="lm", n_layer=24, d_model=768, d_state=16, d_conv=4, expand=2, batch=32, seq_len=2048, seed=3),
+    # what one GPU of eight gets of configuration 3 (4 sequences): the few-chains case of the scan
+    "lm_cfg3_rows4": dict(kind="lm", n_layer=24, d_model=768, d_state=16, d_conv=4, expand=2, batch=4, seq_len=2048, seed=3),
+    "scan_cfg3_rows4": dict(kind="scan", batch=4, seq_len=2048, d_inner=1536, d_state=16, d_conv=4, seed=3),
+    # single kernels / calls of the path at the shapes of configuration 3 (and 1): one JSON line per case
+    "kernels_gemm": dict(kind="kernels"), "kernels_conv": dict(kind="kernels"), "kernels_norm": dict(kind="kernels"),
+    "s4_cfg1": dict(kind="kernels"), "decode_cfg3": dict(kind="kernels"), "ref_benches": dict(kind="kernels"),
 }
 
 STAGE_NAMES = ["embedding", "rmsnorm", "in_proj", "conv_silu", "x_proj", "dt_proj", "scan", "out_proj", "lm_head"]
@@ -52,22 +61,34 @@ def measured_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
-# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel, from the ncu
-# captures summarised under profiles/ (same workload as the benchmark, one launch each).
-NCU_TRAFFIC_BYTES = {
-    "lm_cfg3": 608_549_120,    # profiles/scan_direct_kernel_lm_cfg3.md: 413.6 MB + 194.9 MB
-    "scan_cfg2": 791_900_000,  # profiles/scan_tiled_kernel_cfg2.md: 608.9 MB + 182.9 MB
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the dominant kernel, from an ncu
+# capture of this workload.  A figure is reported only while the kernel that ran is the kernel that was captured;
+# otherwise `traffic` is null (a run cannot measure it: ncu is not part of a timed run).
+NCU_TRAFFIC = {
+    ("lm_cfg3", "scan_direct_kernel (chained segments, dt projection inside)"):
+        {"bytes": 608_549_120, "capture": "ncu --set full, one launch inside the 24-block step: 413.6 MB read + 194.9 MB written"},
+    ("scan_cfg2", "scan_tiled_kernel"):
+        {"bytes": 791_900_000, "capture": "ncu --set full, one launch: 608.9 MB read + 182.9 MB written"},
 }
 
 
-def scan_kernel_name(variant, cfg):
+def ncu_traffic(workload, kernel):
+    t = NCU_TRAFFIC.get((workload, kernel))
+    return (t["bytes"], t["capture"]) if t else (None, "no ncu capture of this kernel on this workload")
+
+
+def scan_kernel_name(variant, cfg, splits=0):
     """The kernel hx_selective_scan_fwd runs for this variant (HX_SCAN_AUTO: one lane per channel when there are at
     least 8 warps of chains per SM, the lane-split kernel otherwise)."""
     if variant == "auto":
         import torch
         sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
-        variant = "direct" if cfg["batch"] * cfg["d_inner"] / 32.0 >= 8.0 * sms else "tiled"
-    return {"direct": "scan_direct_kernel", "simple": "scan_simple_kernel"}.get(variant, "scan_tiled_kernel")
+        if cfg["batch"] * cfg["d_inner"] / 32.0 >= 8.0 * sms:
+            variant = "direct"
+        else:
+            variant = "lookback" if splits > 1 else "tiled"
+    return {"direct": "scan_direct_kernel", "simple": "scan_simple_kernel",
+            "lookback": "scan_direct_kernel (look-back: aggregate pass + output pass)"}.get(variant, "scan_tiled_kernel")
 
 
 def scan_algorithmic_bytes(batch, seq_len, d_inner, d_state, d_conv, es=2):
@@ -246,7 +267,8 @@ def run_scan(args, cfg, name):
     t = gpu_inputs(torch, cfg, device, seed_offset=rank)
     y = torch.empty_like(t["x"])
     ws = torch.empty(64 << 20, dtype=torch.uint8, device=device) if args.splits > 1 else None
-    variant = {"auto": _lib.SCAN_AUTO, "tiled": _lib.SCAN_TILED, "simple": _lib.SCAN_SIMPLE, "direct": _lib.SCAN_DIRECT}[args.variant]
+    variant = {"auto": _lib.SCAN_AUTO, "tiled": _lib.SCAN_TILED, "simple": _lib.SCAN_SIMPLE, "direct": _lib.SCAN_DIRECT,
+               "lookback": _lib.SCAN_LOOKBACK}[args.variant]
 
     def step():
         ops.selective_scan(t["x"], t["dt"], t["A"], t["B"], t["C"], D=t["D"], z=t["z"], conv_w=t["conv_w"], variant=variant,
@@ -338,13 +360,16 @@ def run_scan(args, cfg, name):
                        "per_gpu": ("channel shard of %d channels, B and C replicated" % cfg["d_inner"]) if args.shard == "channels"
                        else "full workload on every rank", "l2": "inputs (0.8 GB+) exceed the 126 MB L2, no flush",
                        "variant": args.variant, "lanes_per_channel": args.lpc, "tune": args.tune, "seq_splits": args.splits},
-            "roofline": {"bound": "hbm", "kernel": scan_kernel_name(args.variant, cfg), "achieved": achieved, "peak": peaks["hbm_gbs"],
+            "roofline": {"bound": "hbm", "kernel": scan_kernel_name(args.variant, cfg, args.splits), "achieved": achieved, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "algorithmic_bytes_per_launch": alg,
-                         "traffic": NCU_TRAFFIC_BYTES.get(name) if (args.variant == "auto" and world == 1) else None},
+                         "traffic": ncu_traffic(name, scan_kernel_name(args.variant, cfg, args.splits))[0] if world == 1 else None,
+                         "traffic_source": ncu_traffic(name, scan_kernel_name(args.variant, cfg, args.splits))[1]},
             "compute_roof": scan_compute_roof(cfg["batch"] * cfg["seq_len"] * cfg["d_inner"], cfg["d_state"], cfg["d_conv"], alg,
                                               peaks["hbm_gbs"], pipe_rates(), ms_step),
-            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps, "clocks": clocks, "device_status": status,
+            "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": args.steps * (2 if "look-back" in scan_kernel_name(args.variant, cfg, args.splits) else 1),
+            "clocks": clocks, "device_status": status,
         }
         print(json.dumps(line))
     if world > 1:
@@ -358,42 +383,80 @@ def lm_flops_per_token(cfg):
     return cfg["n_layer"] * per_block + 2 * M * 256
 
 
-def cpu_baseline_lm(cfg, seconds_hint=15.0, max_layers=None):
-    """Times the CPU oracle port of the byte LM (naive i-j-k GEMMs as the reference's, rows spread over all
-    host threads with OpenMP) on a bounded sample: ONE sequence of a few hundred tokens through all layers."""
+def _lm_oracle_weights(cfg):
     import numpy as np
     from helixml_b200 import synth
-    from oracle import cbind
-    _use_all_host_threads()
     M, nl = cfg["d_model"], cfg["n_layer"]
     layers = []
     for l in range(nl):
         w = synth.mamba_block_weights(cfg["seed"], M, cfg["d_state"], cfg["d_conv"], cfg["expand"], init="0.02", prefix=f"l{l}.")
         w["norm_w"] = np.ones(M, np.float32)
         layers.append(w)
-    emb = synth.normal(cfg["seed"], "emb", (256, M), 0, 0.02)
-    normf = np.ones(M, np.float32)
-    L = 64
+    return synth.normal(cfg["seed"], "emb", (256, M), 0, 0.02), layers, np.ones(M, np.float32)
+
+
+def cpu_baseline_lm(cfg, seconds_hint=15.0, threads=None):
+    """Times the CPU oracle port of the byte LM (naive i-j-k GEMMs as the reference's, rows spread over the host
+    threads with OpenMP) on a bounded sample: ONE sequence of a few hundred tokens through all layers.
+    threads = 1 is the reference-faithful leg: the reference's CPU backend is single-threaded."""
+    from helixml_b200 import synth
+    from oracle import cbind
+    if threads is None:
+        _use_all_host_threads()
+    else:
+        cbind.set_num_threads(threads)
+    nl = cfg["n_layer"]
+    emb, layers, normf = _lm_oracle_weights(cfg)
+    L = 32 if threads == 1 else 64
     tok = synth.random_bytes(cfg["seed"], "tok", (1, L))
     t0 = time.perf_counter()
     cbind.byte_lm(tok, emb, layers, normf, cfg["d_state"], cfg["d_conv"])
     dt1 = time.perf_counter() - t0
     # grow the sample until it is worth ~seconds_hint of CPU time (cost is linear in tokens)
     L2 = int(min(cfg["seq_len"], max(L, L * seconds_hint / max(dt1, 1e-3))))
-    L2 = max(64, (L2 // 64) * 64)
+    L2 = max(L, (L2 // L) * L)
     tok = synth.random_bytes(cfg["seed"], "tok", (1, L2))
     t0 = time.perf_counter()
     cbind.byte_lm(tok, emb, layers, normf, cfg["d_state"], cfg["d_conv"])
     dt = time.perf_counter() - t0
+    how = "one thread, as the reference's single-threaded CPU backend" if threads == 1 else "OpenMP over rows"
     return {"value": L2 / dt, "unit": "tokens/s", "cores": cbind.num_threads(), "kind": "port",
-            "sample": f"1 sequence x {L2} tokens through all {nl} blocks + head (f32 oracle, naive GEMMs, OpenMP over rows)"}
+            "sample": f"1 sequence x {L2} tokens through all {nl} blocks + head (f32 oracle, naive GEMMs, {how})"}
+
+
+def lm_parity_check(lm, cfg, tok_row, logits_row):
+    """The logits the timed path produced for one sequence against the CPU oracle of the whole model, with the
+    model's own weights read back from the device: rel. L2 (gate 2e-2 for bf16) and the worst single position."""
+    import numpy as np
+    from oracle import cbind
+    _use_all_host_threads()
+    emb, layers, normf = lm.weights_numpy()
+    t0 = time.perf_counter()
+    ref = cbind.byte_lm(tok_row[None, :], emb, layers, normf, cfg["d_state"], cfg["d_conv"])[0].astype(np.float64)
+    got = logits_row.astype(np.float64)
+    rel = float(np.linalg.norm(got - ref) / max(np.linalg.norm(ref), 1e-30))
+    pos = float(np.max(np.linalg.norm(got - ref, axis=1) / np.maximum(np.linalg.norm(ref, axis=1), 1e-30)))
+    return {"against": "CPU oracle (f32) of the whole model on one sequence of this run's batch", "tokens": int(tok_row.shape[0]),
+            "rel_l2": rel, "worst_position_rel_l2": pos, "gate_rel_l2": 2e-2, "ok": bool(rel <= 2e-2),
+            "oracle_seconds": time.perf_counter() - t0}
+
+
+def lm_config(cfg, name, world, strong):
+    """The `config` object of an lm line: the same for this arm and for the reference arm."""
+    GB, L = cfg["batch"], cfg["seq_len"]
+    per_gpu = (f"{GB} / {world} rows of ONE batch of {GB} sequences per GPU (contiguous blocks, first ranks take the remainder), "
+               "weight replica per rank") if strong else f"batch {GB} x {L} on every rank (independent replicas)"
+    return {"workload": name, **{k: cfg[k] for k in ("n_layer", "d_model", "d_state", "d_conv", "expand", "batch", "seq_len")},
+            "vocab": 256, "global_batch": GB if strong else GB * world, "per_gpu": per_gpu,
+            "l2": "per-layer activations exceed the 126 MB L2 at 32 rows; at fewer rows the layers' weights and "
+                  "activations rotate through it (24 layers x 0.1-0.4 GB per step), no flush"}
 
 
 def run_lm(args, cfg, name):
     import numpy as np
     import torch
     import torch.distributed as dist
-    from helixml_b200 import _lib, nn, synth
+    from helixml_b200 import _lib, nn, shard, synth
     import ctypes as C
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -405,11 +468,19 @@ def run_lm(args, cfg, name):
         dist.init_process_group("nccl", device_id=device)
     _lib.lib()
 
-    B, L = cfg["batch"], cfg["seq_len"]
+    GB, L = cfg["batch"], cfg["seq_len"]
+    strong = args.scaling == "strong"
     nn.manual_seed(cfg["seed"])          # same weights on every rank: a replica per GPU
     lm = nn.ByteLM(cfg["n_layer"], cfg["d_model"], cfg["d_state"], cfg["d_conv"], cfg["expand"], nn.Device.cuda(local), nn.BF16)
-    # each rank prefill its own batch of sequences (batch shard, no collective on the path)
-    tok_np = synth.random_bytes(cfg["seed"] + 1000 * rank, "tok", (B, L))
+    if strong:
+        # ONE batch of GB sequences, rank r prefills its contiguous block of rows (no collective on the path)
+        r0, r1 = shard.batch_shard(GB, world, rank)
+        tok_np = np.ascontiguousarray(synth.random_bytes(cfg["seed"], "tok", (GB, L))[r0:r1])
+    else:
+        tok_np = synth.random_bytes(cfg["seed"] + 1000 * rank, "tok", (GB, L))
+    B = tok_np.shape[0]
+    if B == 0:
+        raise SystemExit(f"rank {rank} has no batch rows: more ranks than sequences")
     tok_host = torch.from_numpy(tok_np).pin_memory()
     tok_dev = tok_host.to(device)
     logits_dev = torch.empty((B, L, 256), dtype=torch.bfloat16, device=device)
@@ -451,7 +522,7 @@ def run_lm(args, cfg, name):
         time.sleep(0.3)
     ms_step = timed(step, args.steps)
     clocks = sampler.stop() if rank == 0 else None
-    tokens_step = B * L * world
+    tokens_step = GB * L if strong else GB * L * world
     value = tokens_step / (ms_step * 1e-3)
 
     for _ in range(2):
@@ -459,7 +530,7 @@ def run_lm(args, cfg, name):
     e_steps = max(1, min(args.steps, 10))
     ems = timed(step_host, e_steps)
     e2e = {"value": tokens_step / (ems * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": B * L, "d2h_bytes_per_step": B * L * 256 * 2,
-           "steps": e_steps}
+           "steps": e_steps, "bytes_are": "per rank"}
 
     # per-stage breakdown with CUDA events on the launching stream (a second pass over the same steps, so the
     # event records do not sit inside the region `value` is taken from)
@@ -473,11 +544,12 @@ def run_lm(args, cfg, name):
     _lib.check(L_.hx_byte_lm_profile(lm._h, 0))
     stage_ms = {n: float(ms9[i]) / max(nf.value, 1) for i, n in enumerate(STAGE_NAMES)}
     status = _lib.device_status()
+    launches = lm.launches_per_forward
 
     if rank == 0:
         peaks = measured_peaks()
         E, N = cfg["d_model"] * cfg["expand"], cfg["d_state"]
-        # algorithmic bytes of one selective scan of this shape: u, dt, z read, y written, B and C read once
+        # algorithmic bytes of one selective scan of this rank's shape: u, dt, z read, y written, B and C read once
         # (12 354 bytes per token at d_inner 1536).  The block's kernel computes dt from the low-rank x_proj
         # output instead of reading it, so its DRAM traffic is lower than this figure; the figure stays that of
         # the operation so that fused and unfused kernels are compared on the same basis.
@@ -486,33 +558,49 @@ def run_lm(args, cfg, name):
         scan_gbs = scan_bytes / (scan_ms * 1e-3) / 1e9
         gemm_ms = sum(stage_ms[k] for k in ("in_proj", "x_proj", "dt_proj", "out_proj", "lm_head"))
         gemm_tflops = lm_flops_per_token(cfg) * B * L / (gemm_ms * 1e-3) / 1e12
+        # launches per block beyond norm + in_proj + conv + x_proj + out_proj: 1 = one-pass scan with the dt
+        # projection inside, 2 = look-back scan (aggregate pass + output pass), or dt_proj GEMM + scan
+        per_block = (launches - 3) // cfg["n_layer"]
+        fused = stage_ms["dt_proj"] < 1e-3
+        if fused and per_block == 6:
+            scan_kernel = "scan_direct_kernel (chained segments, dt projection inside)"
+        elif fused:
+            scan_kernel = "scan_direct_kernel (look-back: aggregate pass + output pass, dt projection inside)"
+        else:
+            scan_kernel = "selective scan with a dt_proj GEMM of its own"
+        traffic, traffic_src = ncu_traffic(name, scan_kernel) if world == 1 else (None, "single-GPU captures only")
         # the scan is the largest single stage (and the top entry of the ncu launch list); the GEMMs, five
         # shapes of one kernel, are reported beside it under "gemm"
         dominant_scan = stage_ms["scan"] >= max(stage_ms[k] for k in ("in_proj", "x_proj", "dt_proj", "out_proj", "lm_head"))
         if dominant_scan:
-            roof = {"bound": "hbm", "kernel": "scan_direct_kernel", "achieved": scan_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            roof = {"bound": "hbm", "kernel": scan_kernel, "achieved": scan_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": scan_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
-                    "algorithmic_bytes_per_launch": scan_bytes, "launch_ms": scan_ms, "traffic": NCU_TRAFFIC_BYTES.get(name),
-                    "note": "dt projection fused into this kernel: it reads u, z, B, C and the rank-48 dt input, writes y"}
+                    "algorithmic_bytes_per_launch": scan_bytes, "launch_ms": scan_ms, "traffic": traffic, "traffic_source": traffic_src,
+                    "note": "per call of the scan stage (all its launches); algorithmic bytes are those of the unfused operation"}
         else:
             roof = {"bound": "tensor", "kernel": "gemm_tc_kernel (all projections)", "achieved": gemm_tflops,
                     "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": gemm_tflops / peaks["bf16_tflops_sustained"],
                     "peak_source": peaks["source"] + " (sustained)", "traffic": None}
-        cpu = None if (args.no_cpu or world > 1) else cpu_baseline_lm(cfg)  # the CPU leg is timed at N = 1 only
+        parity = None
+        if not args.no_parity:
+            parity = lm_parity_check(lm, cfg, tok_np[0], logits_dev[0].float().cpu().numpy())
+        cpu = cpu1 = None
+        if not (args.no_cpu or world > 1):  # the CPU legs are timed at N = 1 only
+            cpu = cpu_baseline_lm(cfg)
+            cpu1 = cpu_baseline_lm(cfg, seconds_hint=6.0, threads=1)
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic",
-            "config": {"workload": name, **{k: cfg[k] for k in ("n_layer", "d_model", "d_state", "d_conv", "expand", "batch", "seq_len")},
-                       "vocab": 256, "per_gpu": "batch 32 x 2048 on every rank (batch shard, weight replica per rank)",
-                       "l2": "per-layer activations (0.2-0.4 GB each) exceed the 126 MB L2, no flush"},
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": lm_config(cfg, name, world, strong),
             "roofline": roof,
             "stages_ms": stage_ms,
             "scan": {"gbs": scan_gbs, "frac_of_hbm_peak": scan_gbs / peaks["hbm_gbs"], "ms_per_launch": scan_ms,
                      "compute_roof": scan_compute_roof(B * L * E, N, 0, scan_bytes, peaks["hbm_gbs"], pipe_rates(),
                                                        scan_ms)},
             "gemm": {"tflops": gemm_tflops, "frac_of_sustained_peak": gemm_tflops / peaks["bf16_tflops_sustained"], "ms_total": gemm_ms},
-            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": args.steps * lm.launches_per_forward, "clocks": clocks,
+            "parity_checked": parity,
+            "cpu_baseline": cpu, "cpu_baseline_1core": cpu1, "e2e": e2e, "gpu_launches": args.steps * launches, "clocks": clocks,
             "device_status": status,
         }
         print(json.dumps(line))
@@ -531,13 +619,119 @@ def run_reference_lm(args, cfg, name):
             vals.append(base["value"])
     v = sum(vals) / len(vals)
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": name, **{k: cfg[k] for k in ("n_layer", "d_model", "d_state", "d_conv", "expand", "batch", "seq_len")}},
+            "warmup": args.warmup, "ms_per_step": 1e3 * cfg["batch"] * cfg["seq_len"] / v, "higher_is_better": True,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": lm_config(cfg, name, int(os.environ.get("WORLD_SIZE", "1")), args.scaling == "strong"),
             "cpu_baseline": {**base, "value": v},
             "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0,
             "note": "the reference is Rust and cannot be built here (no toolchain): this arm is the CPU oracle port of the same path"}
     print(json.dumps(line))
+
+
+GEMM_SHAPES = {"in_proj": (65536, 3072, 768), "out_proj": (65536, 768, 1536), "x_proj": (65536, 80, 1536),
+               "dt_proj": (65536, 1536, 48), "lm_head": (65536, 256, 768)}
+
+
+def run_kernels(args, name):
+    """Single kernels / calls of the path, timed alone with CUDA events on torch's current stream: `warmup` untimed
+    calls, then `steps` calls between two events, queued behind a ~2 ms spin so that the host's launch rate does not
+    limit a kernel of a few tens of microseconds.  One JSON line per case."""
+    import torch
+    from helixml_b200 import _lib, nn, ops, synth
+    torch.cuda.set_device(0)
+    _lib.lib()
+    reps, warm = max(1, args.steps), max(3, args.warmup)
+
+    def timed(fn):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda._sleep(4_000_000)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps
+
+    def emit(case, ms, **kw):
+        print(json.dumps({"workload": name, "case": case, "us": ms * 1e3, "steps": reps, "warmup": warm, **kw}))
+
+    peaks = measured_peaks()
+    if name == "kernels_gemm":
+        for case in args.cases or list(GEMM_SHAPES):
+            M, N, K = GEMM_SHAPES[case]
+            a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
+            w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
+            c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            ms = timed(lambda: ops.gemm(a, w, out=c))
+            err = (c[:256].float() - a[:256].float() @ w.float().t()).abs().max().item()
+            tf = 2 * M * N * K / ms / 1e9
+            emit(case, ms, M=M, N=N, K=K, tflops=tf, frac_of_burst_peak=tf / peaks["bf16_tflops"], max_abs_err_256_rows=err)
+    elif name == "kernels_conv":
+        B, L, E = 32, 2048, 1536
+        xz = torch.randn(B, L, 2 * E, device="cuda").to(torch.bfloat16)
+        w = torch.rand(E, 4, device="cuda") - 0.5
+        b = torch.zeros(E, device="cuda")
+        u = torch.empty(B, L, E, device="cuda", dtype=torch.bfloat16)
+        ms = timed(lambda: ops.conv1d_silu(xz[:, :, :E], w, b, out=u))
+        gbs = B * L * E * 2 * 2 / ms / 1e6
+        emit("conv_silu [32, 2048, 1536] bf16, x a strided half of [B, L, 2E]", ms, gbs=gbs, frac_of_hbm_peak=gbs / peaks["hbm_gbs"])
+    elif name == "kernels_norm":
+        T, M = 65536, 768
+        x = torch.randn(T, M, device="cuda").to(torch.bfloat16)
+        r = torch.randn(T, M, device="cuda")
+        w = torch.ones(M, device="cuda")
+        ms = timed(lambda: ops.rmsnorm(x, w, 1e-5, residual=r, out_dtype=torch.bfloat16))
+        gbs = T * M * (2 + 4 + 4 + 2) / ms / 1e6
+        emit("rmsnorm + residual add [65536, 768]", ms, gbs=gbs, frac_of_hbm_peak=gbs / peaks["hbm_gbs"])
+    elif name == "s4_cfg1":
+        # benchmark configuration 1: diagonal S4, f32, batch 8, L 2048, d_model 256, d_state 64
+        inp = synth.s4_inputs(1, 8, 2048, 256, 64)
+        dev = {k: torch.from_numpy(v).cuda() for k, v in inp.items()}
+        ms = timed(lambda: ops.s4_diag(dev["u"], dev["A"], dev["B"], dev["C"], dev["delta"], dev["D"]))
+        emit("s4_diag [8, 2048, 256] N 64 f32", ms, gbs=2 * 8 * 2048 * 256 * 4 / ms / 1e6, g_state_updates_per_s=8 * 2048 * 256 * 64 / ms / 1e6)
+        M, L, N = 256, 2048, 64
+        r = {"u": torch.randn(M, L, device="cuda"), "Ar": -torch.rand(N, device="cuda"), "Ai": torch.randn(N, device="cuda"),
+             "B": torch.randn(N, M, device="cuda") * 0.1, "C": torch.randn(M, N, device="cuda") * 0.1, "D": torch.randn(M, device="cuda")}
+        ms = timed(lambda: ops.s4_ref_forward_ssm(r["u"], r["Ar"], r["Ai"], r["B"], r["C"], r["D"]))
+        emit("reference-literal S4Block::forward_ssm [256, 2048] N 64 f32", ms)
+    elif name == "decode_cfg3":
+        # byte LM of configuration 3: prefill 32 x 2048, then single-token steps, plain launches and CUDA-graph replays
+        B, L0 = 32, 2048
+        nn.manual_seed(3)
+        lm = nn.ByteLM(24, 768, dtype=nn.BF16)
+        tok = torch.randint(0, 256, (B, L0), device="cuda", dtype=torch.uint8)
+        pre = torch.empty(B, L0, 256, device="cuda", dtype=torch.bfloat16)
+        nxt = torch.randint(0, 256, (B,), device="cuda", dtype=torch.uint8)
+        lg = torch.empty(B, 256, device="cuda", dtype=torch.bfloat16)
+        for graph in (False, True):
+            lm.decode_graph(graph)
+            lm.prefill_device(tok.data_ptr(), pre.data_ptr(), B, L0)
+            for _ in range(4):  # the first step is plain, the second captures
+                lm.decode_step_device(nxt.data_ptr(), lg.data_ptr(), B)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(64):
+                lm.decode_step_device(nxt.data_ptr(), lg.data_ptr(), B)
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / 64
+            emit(f"decode step, batch 32, 24 blocks, {'CUDA graph' if graph else 'plain launches'}", ms,
+                 kernels=lm.launches_per_decode_step, tokens_per_s=B / ms * 1e3)
+    elif name == "ref_benches":
+        # the reference's own criterion shapes (benches/src/neural_networks.rs:11-51): S4Block::new(512, 64) and
+        # MambaBlock::new(512, 64, 4, 2) forward on [seq, 512], seq 64 / 128 / 256, f32.  There the S4 forward is
+        # input.clone() and the Mamba forward out_proj(silu(gate(x))); here they are the real recurrences.
+        for seq in (64, 128, 256):
+            x = nn.Tensor.from_numpy(synth.normal(1, f"x{seq}", (seq, 512)))
+            s4 = nn.S4Block(512, 64)
+            mb = nn.MambaBlock(512, 64, 4, 2, nn.Device.cuda(0))
+            emit(f"S4Block(512, 64).forward [{seq}, 512]", timed(lambda: s4.forward(x)))
+            emit(f"MambaBlock(512, 64, 4, 2).forward [{seq}, 512]", timed(lambda: mb.forward(x)))
+    assert _lib.device_status() == 0
 
 
 def main():
@@ -547,7 +741,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="lm_cfg3", choices=sorted(WORKLOADS))
-    ap.add_argument("--variant", default="auto", choices=["auto", "tiled", "simple", "direct"])
+    ap.add_argument("--variant", default="auto", choices=["auto", "tiled", "simple", "direct", "lookback"])
     ap.add_argument("--lpc", type=int, default=0)
     ap.add_argument("--tune", type=int, default=0)
     ap.add_argument("--splits", type=int, default=0)
@@ -555,6 +749,10 @@ def main():
     ap.add_argument("--gather", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of one sequence of the timed path")
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
+                    help="lm workloads at N > 1: one batch sharded by rows (strong) or the whole batch on every rank (weak)")
+    ap.add_argument("cases", nargs="*", help="kernels_gemm: shapes to time (default all)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     if args.impl == "reference":
@@ -562,6 +760,8 @@ def main():
         return
     if cfg["kind"] == "scan":
         run_scan(args, cfg, args.workload)
+    elif cfg["kind"] == "kernels":
+        run_kernels(args, args.workload)
     else:
         run_lm(args, cfg, args.workload)
 

@@ -359,6 +359,19 @@ class ByteLM(Module):
         arrays.append(norm_f)
         self.load_parameters(arrays)
 
+    def weights_numpy(self):
+        """(emb, layers, norm_f) as fp32 numpy arrays in the layout load_weights takes: what a CPU check of the
+        model's output needs."""
+        ps = [p.numpy() for p in self.parameters()]
+        per = 1 + len(MambaBlock.PARAMS)
+        layers = []
+        for l in range(self.n_layer):
+            blk = ps[1 + l * per: 1 + (l + 1) * per]
+            d = {"norm_w": blk[0]}
+            d.update({k: v for k, v in zip(MambaBlock.PARAMS, blk[1:])})
+            layers.append(d)
+        return ps[0], layers, ps[-1]
+
     def forward_host(self, tokens_ptr: int, logits_ptr: int, batch: int, seq_len: int, stream: int = 0) -> None:
         L.check(L.lib().hx_byte_lm_forward_host(self._h, C.c_void_p(tokens_ptr), C.c_void_p(logits_ptr), batch, seq_len,
                                                 C.c_void_p(stream)))
