@@ -32,6 +32,8 @@ WORKLOADS = {
     "scan_cfg2": dict(kind="scan", batch=16, seq_len=4096, d_inner=1536, d_state=16, d_conv=4, seed=2),
     # benchmark configuration 4 per-GPU shard at 8 GPUs is [64, 16384, 640]; the full tensor is 43 GB
     "scan_cfg4": dict(kind="scan", batch=64, seq_len=16384, d_inner=5120, d_state=16, d_conv=4, seed=4),
+    # configuration 4 with fewer rows and steps, for trying the channel shard and its gather on two GPUs
+    "scan_cfg4_small": dict(kind="scan", batch=8, seq_len=4096, d_inner=5120, d_state=16, d_conv=4, seed=4),
     # the per-GPU shard of configuration 4 at 8 GPUs (channel shard): [64, 16384, 640]
     "scan_cfg4_shard8": dict(kind="scan", batch=64, seq_len=16384, d_inner=640, d_state=16, d_conv=4, seed=4),
     # benchmark configuration 3: byte-level Mamba LM prefill, 24 blocks, d_model 768, batch 32 x seq 2048, bf16
@@ -260,24 +262,44 @@ def run_scan(args, cfg, name):
     _lib.lib()  # fail loudly here if the CUDA library is missing
 
     full_cfg = cfg
-    if args.shard == "channels":
+    # configuration 4 shards by channels as soon as there is more than one GPU; everything else runs whole on every rank
+    by_channels = args.shard == "channels" or (args.shard == "auto" and world > 1 and name.startswith("scan_cfg4"))
+    c0 = 0
+    if by_channels:
         from helixml_b200 import shard as sh
         c0, c1 = sh.channel_shard(cfg["d_inner"], world, rank)
         cfg = dict(cfg, d_inner=c1 - c0)          # this rank's channels; B and C are replicated
     t = gpu_inputs(torch, cfg, device, seed_offset=rank)
     y = torch.empty_like(t["x"])
-    ws = torch.empty(64 << 20, dtype=torch.uint8, device=device) if args.splits > 1 else None
     variant = {"auto": _lib.SCAN_AUTO, "tiled": _lib.SCAN_TILED, "simple": _lib.SCAN_SIMPLE, "direct": _lib.SCAN_DIRECT,
                "lookback": _lib.SCAN_LOOKBACK}[args.variant]
+    splits = args.splits
+    if splits == 0 and args.variant == "auto":
+        # ask the library how to cut the sequence for this shape (chained segments to even out the load when chains
+        # are plentiful, parallel segments when they are few)
+        splits = ops.suggest_splits(cfg["batch"], cfg["seq_len"], cfg["d_inner"], torch.bfloat16, a_geometric=True)
+    ws = torch.empty(max(ops.scan_workspace_bytes(cfg["batch"], cfg["seq_len"], cfg["d_inner"], torch.bfloat16, splits), 256),
+                     dtype=torch.uint8, device=device) if splits > 1 else None
+
+    def scan_rows(r0, r1, out):
+        ops.selective_scan(t["x"][r0:r1], t["dt"][r0:r1], t["A"], t["B"][r0:r1], t["C"][r0:r1], D=t["D"], z=t["z"][r0:r1],
+                           conv_w=t["conv_w"], variant=variant, a_geometric=True, lanes_per_channel=args.lpc, out=out[r0:r1],
+                           tune=args.tune, seq_splits=splits, workspace=ws)
 
     def step():
-        ops.selective_scan(t["x"], t["dt"], t["A"], t["B"], t["C"], D=t["D"], z=t["z"], conv_w=t["conv_w"], variant=variant,
-                           a_geometric=True, lanes_per_channel=args.lpc, out=y, tune=args.tune, seq_splits=args.splits, workspace=ws)
+        scan_rows(0, cfg["batch"], y)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    def max_ranks(ms):
+        if world > 1:
+            tt = torch.tensor([ms], device=device)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            return float(tt.item())
+        return ms
 
     for _ in range(args.warmup):
         step()
@@ -296,33 +318,70 @@ def run_scan(args, cfg, name):
     ms = ev0.elapsed_time(ev1)
     clocks = sampler.stop() if rank == 0 else None
     status = _lib.device_status()
-    if world > 1:
-        tt = torch.tensor([ms], device=device)
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms = float(tt.item())
-    ms_step = ms / args.steps
-    if args.shard == "channels":
+    ms_step = max_ranks(ms) / args.steps
+    if by_channels:
         tokens_step = cfg["batch"] * cfg["seq_len"]   # every rank works on the same tokens (strong scaling)
     else:
         tokens_step = cfg["batch"] * cfg["seq_len"] * world
     value = tokens_step / (ms_step * 1e-3)
-    gather_ms = None
-    if args.shard == "channels" and world > 1 and args.gather:
-        # the one collective of the channel-sharded scan: all-gather of y over NVLink (NCCL), timed apart
+    gather = None
+    if by_channels and world > 1 and not args.no_gather:
+        # the one exchange of the channel-sharded scan: every rank pushes its y shard into every rank's full
+        # [B, L, D] buffer with peer stores (hx_allgather_y_push), rows in `gather_groups` groups so that a group's
+        # push runs on a second stream under the scan of the next group
         from helixml_b200 import shard as sh
+        pg = sh.PeerGather(cfg["batch"], cfg["seq_len"], full_cfg["d_inner"], torch.bfloat16, world, rank)
+        side = torch.cuda.Stream(device=device)
+        main = torch.cuda.current_stream()
+        groups = max(1, min(args.gather_groups, cfg["batch"]))
+        bounds = [cfg["batch"] * g // groups for g in range(groups + 1)]
+
+        def step_gather():
+            for g in range(groups):
+                scan_rows(bounds[g], bounds[g + 1], y)
+                e = torch.cuda.Event()
+                e.record(main)
+                side.wait_event(e)
+                pg.push(y, c0, bounds[g], bounds[g + 1], side.cuda_stream)
+            e = torch.cuda.Event()
+            e.record(side)
+            main.wait_event(e)
+
+        def timed(fn, steps):
+            barrier()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(steps):
+                fn()
+            a1.record()
+            barrier()
+            return max_ranks(a0.elapsed_time(a1)) / steps
+
         for _ in range(2):
-            sh.all_gather_channels(y, full_cfg["d_inner"], world)
-        barrier()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
-        sh.all_gather_channels(y, full_cfg["d_inner"], world)
-        g1.record()
-        barrier()
-        gather_ms = sh.max_over_ranks(g0.elapsed_time(g1), device)
+            step_gather()
+        both_ms = timed(step_gather, args.steps)
+        push_ms = timed(lambda: pg.push(y, c0, 0, cfg["batch"], main.cuda_stream), args.steps)
+        # check: column sums of every rank's shard, exchanged on the host side, against the same columns of the result
+        full = pg.tensor()
+        mine = y.float().sum(dim=(0, 1)).double().cpu()
+        sums = [None] * world
+        dist.all_gather_object(sums, (c0, mine))
+        ok = all(torch.allclose(full[:, :, cc:cc + sm.numel()].float().sum(dim=(0, 1)).double().cpu(), sm, rtol=1e-6, atol=1e-3)
+                 for cc, sm in sums)
+        okt = torch.tensor([1.0 if ok else 0.0], device=device)
+        dist.all_reduce(okt, op=dist.ReduceOp.MIN)
+        es = 2
+        out_bytes = cfg["batch"] * cfg["seq_len"] * cfg["d_inner"] * es * (world - 1)
+        gather = {"how": "peer stores (hx_allgather_y_push), one kernel per rank, result [B, L, D] on every rank",
+                  "row_groups": groups, "scan_plus_gather_ms": both_ms, "push_alone_ms": push_ms,
+                  "bytes_out_per_rank": out_bytes, "push_alone_gbs_out_per_rank": out_bytes / (push_ms * 1e-3) / 1e9,
+                  "link_peak_gbs": 770.0, "checked": bool(okt.item() == 1.0),
+                  "tokens_per_s_with_gather": tokens_step / (both_ms * 1e-3)}
+        pg.close()
 
     # end to end through the host-buffer entry point (pinned host activations in, y back to the host)
     e2e = None
-    if not args.no_e2e and args.shard != "channels":
+    if not args.no_e2e and not by_channels:
         hs = ops.HostScan(cfg["batch"], cfg["seq_len"], cfg["d_inner"], cfg["d_state"], torch.bfloat16, t["A"], D=t["D"],
                           conv_w=t["conv_w"], variant=variant, lanes_per_channel=args.lpc, device=device)
         for name_, src in (("x", t["x"]), ("dt", t["dt"]), ("z", t["z"]), ("Bm", t["B"]), ("Cm", t["C"])):
@@ -354,21 +413,21 @@ def run_scan(args, cfg, name):
         cpu = None if (args.no_cpu or world > 1) else cpu_baseline_scan(cfg)  # the CPU leg is timed at N = 1 only
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if args.shard == "channels" else "weak",
-            "vs_baseline": None, "dtype": "f32", "io_dtype": "bf16", "data": "synthetic", "allgather_y_ms": gather_ms,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if by_channels else "weak",
+            "vs_baseline": None, "dtype": "f32", "io_dtype": "bf16", "data": "synthetic", "allgather_y": gather,
             "config": {"workload": name, **{k: full_cfg[k] for k in ("batch", "seq_len", "d_inner", "d_state", "d_conv")},
-                       "per_gpu": ("channel shard of %d channels, B and C replicated" % cfg["d_inner"]) if args.shard == "channels"
+                       "per_gpu": ("channel shard of %d channels, B and C replicated" % cfg["d_inner"]) if by_channels
                        else "full workload on every rank", "l2": "inputs (0.8 GB+) exceed the 126 MB L2, no flush",
-                       "variant": args.variant, "lanes_per_channel": args.lpc, "tune": args.tune, "seq_splits": args.splits},
-            "roofline": {"bound": "hbm", "kernel": scan_kernel_name(args.variant, cfg, args.splits), "achieved": achieved, "peak": peaks["hbm_gbs"],
+                       "variant": args.variant, "lanes_per_channel": args.lpc, "tune": args.tune, "seq_splits": splits},
+            "roofline": {"bound": "hbm", "kernel": scan_kernel_name(args.variant, cfg, splits), "achieved": achieved, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "algorithmic_bytes_per_launch": alg,
-                         "traffic": ncu_traffic(name, scan_kernel_name(args.variant, cfg, args.splits))[0] if world == 1 else None,
-                         "traffic_source": ncu_traffic(name, scan_kernel_name(args.variant, cfg, args.splits))[1]},
+                         "traffic": ncu_traffic(name, scan_kernel_name(args.variant, cfg, splits))[0] if world == 1 else None,
+                         "traffic_source": ncu_traffic(name, scan_kernel_name(args.variant, cfg, splits))[1]},
             "compute_roof": scan_compute_roof(cfg["batch"] * cfg["seq_len"] * cfg["d_inner"], cfg["d_state"], cfg["d_conv"], alg,
                                               peaks["hbm_gbs"], pipe_rates(), ms_step),
             "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": args.steps * (2 if "look-back" in scan_kernel_name(args.variant, cfg, args.splits) else 1),
+            "gpu_launches": args.steps * (2 if "look-back" in scan_kernel_name(args.variant, cfg, splits) else 1),
             "clocks": clocks, "device_status": status,
         }
         print(json.dumps(line))
@@ -745,8 +804,10 @@ def main():
     ap.add_argument("--lpc", type=int, default=0)
     ap.add_argument("--tune", type=int, default=0)
     ap.add_argument("--splits", type=int, default=0)
-    ap.add_argument("--shard", default="none", choices=["none", "channels"])
-    ap.add_argument("--gather", action="store_true")
+    ap.add_argument("--shard", default="auto", choices=["auto", "none", "channels"],
+                    help="auto: configuration 4 is sharded by channels when N > 1")
+    ap.add_argument("--no-gather", action="store_true", help="channel shard: skip the all-gather of y")
+    ap.add_argument("--gather-groups", type=int, default=2, help="row groups whose pushes overlap the next group's scan")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of one sequence of the timed path")

@@ -77,6 +77,13 @@ class MambaStepArgs(C.Structure):
     ]
 
 
+class GatherArgs(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("batch", C.c_int32), ("seq_len", C.c_int32),
+                ("d_shard", C.c_int32), ("d_full", C.c_int32), ("col0", C.c_int32), ("io_dtype", C.c_int32),
+                ("y_local", C.c_void_p), ("dst", C.c_void_p * 8), ("row_begin", C.c_int32), ("row_end", C.c_int32),
+                ("max_ctas_per_sm", C.c_int32), ("reserved", C.c_int32)]
+
+
 _PROTOS = {
     "hx_version": (C.c_char_p, []),
     "hx_last_error": (C.c_char_p, []),
@@ -101,6 +108,10 @@ _PROTOS = {
     "hx_device_status": (C.c_int, [C.POINTER(C.c_int32), C.c_int32]),
     "hx_device_check": (C.c_int, []),
     "hx_debug_scan_orphan_segment": (C.c_int, [C.POINTER(ScanArgs), C.c_int32, C.c_void_p]),
+    "hx_ipc_export": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "hx_ipc_open": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    "hx_ipc_close": (C.c_int, [C.c_void_p]),
+    "hx_allgather_y_push": (C.c_int, [C.POINTER(GatherArgs), C.c_void_p]),
     "hx_probe_pipe": (C.c_int, [C.c_int32, C.c_void_p, C.c_size_t, C.POINTER(C.c_double), C.c_void_p]),
     "hx_conv1d_silu_fwd": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
                                      C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),

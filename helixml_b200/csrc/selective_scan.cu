@@ -929,10 +929,10 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
 
 
 template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2, bool FUSEDT = false, bool ZGATE = false, bool BLOCK = false,
-          int MODE = 0>
+          int MODE = 0, int XV = 0>
 static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *maps, dim3 grid, cudaStream_t st, void *y,
                                     int64_t y_bs, int64_t y_rs) {
-    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES, FUSEDT, ZGATE, BLOCK, MODE>;
+    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES, FUSEDT, ZGATE, BLOCK, MODE, XV>;
     auto kern = scan_direct_kernel<T, Cfg>;
     static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice is harmless
     int dev = 0;
@@ -1109,6 +1109,15 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
         if (geom) return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
         return launch_direct_inst<__nv_bfloat16, 1, false, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
     }
+    if (bf && geom && stdp && a->reserved / 100 >= 1 && form == 0) {  // experimental loop organisations
+        const int xv = a->reserved / 100;
+        if (cpl == 2) {
+            if (xv == 1) return launch_direct_inst<__nv_bfloat16, 2, true, true, 2, false, false, false, 0, 1>(p, maps, grid, st, yv, ybs, yrs);
+            return launch_direct_inst<__nv_bfloat16, 2, true, true, 2, false, false, false, 0, 2>(p, maps, grid, st, yv, ybs, yrs);
+        }
+        if (xv == 1) return launch_direct_inst<__nv_bfloat16, 1, true, true, 2, false, false, false, 0, 1>(p, maps, grid, st, yv, ybs, yrs);
+        return launch_direct_inst<__nv_bfloat16, 1, true, true, 2, false, false, false, 0, 2>(p, maps, grid, st, yv, ybs, yrs);
+    }
     if (bf && geom && stdp && a->reserved / 10 == 1) {  // tuning: three stages instead of two
         if (cpl == 2) return launch_direct_inst<__nv_bfloat16, 2, true, true, 3>(p, maps, grid, st, yv, ybs, yrs);
         return launch_direct_inst<__nv_bfloat16, 1, true, true, 3>(p, maps, grid, st, yv, ybs, yrs);
@@ -1189,10 +1198,12 @@ int32_t hx_selective_scan_suggest_splits(const hx_scan_args *a) {
     const double warps_per_sm = chains / 32.0 / hx::sm_count();
     const bool direct = warps_per_sm >= 8.0;
     if (!direct && a->a_geometric && !a->z_is_gate) {
-        // few chains, geometric A: the look-back form runs the segments of a chain at the same time, so split
-        // until there are about 16 one-lane-per-channel warps per SM, keeping segments of at least 64 steps
+        // few chains, geometric A: the look-back form runs the segments of a chain at the same time.  Its aggregate
+        // pass covers all segments but the last, so split until that pass alone has about 8 one-lane-per-channel
+        // warps per SM (measured: below that it is short of warps, beyond it the extra work of shorter segments
+        // buys nothing), keeping segments of at least 64 steps
         int splits = 1;
-        while (splits < 16 && splits * warps_per_sm < 16.0 && a->seq_len / (2 * splits) >= 64) splits *= 2;
+        while (splits < 16 && (splits - 1) * warps_per_sm < 8.0 && a->seq_len / (2 * splits) >= 64) splits *= 2;
         return splits;
     }
     // chained segments: CTAs of the kernel AUTO would pick, against the CTA slots of the device (about 3 per SM)

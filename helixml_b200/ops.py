@@ -71,6 +71,15 @@ def scan_workspace_bytes(batch, seq_len, d_inner, dtype, seq_splits=0) -> int:
     return n.value
 
 
+def suggest_splits(batch, seq_len, d_inner, dtype, a_geometric=True) -> int:
+    """hx_selective_scan_suggest_splits: sequence segments HX_SCAN_AUTO works best with for this shape."""
+    a = L.ScanArgs()
+    a.batch, a.seq_len, a.d_inner, a.d_state = batch, seq_len, d_inner, 16
+    a.io_dtype = L.HX_BF16 if dtype == torch.bfloat16 else L.HX_F32
+    a.a_geometric = 1 if a_geometric else 0
+    return int(L.lib().hx_selective_scan_suggest_splits(C.byref(a)))
+
+
 def selective_scan(x, dt, A, Bm, Cm, D=None, z=None, conv_w=None, conv_b=None, dt_bias=None, dt_softplus=True,
                    variant=L.SCAN_AUTO, a_geometric=None, lanes_per_channel=0, return_state=False, out=None,
                    workspace=None, seq_splits=0, tune=0, dt_low=None, W_dt=None, z_is_gate=False):
@@ -268,15 +277,16 @@ def mamba_block(x, w: dict, d_state: int, d_conv: int, workspace=None, scan_vari
     a.b_dt = _f32(w["b_dt"]).data_ptr()
     a.A = _f32(w["A"]).data_ptr()
     a.Dskip = _f32(w["D"]).data_ptr()
+    # the scan's plan (and with it the workspace size) depends on the variant and on whether A is geometric
+    a.scan_variant = scan_variant
+    if a_geometric is None:
+        a_geometric = check_geometric(w["A"])
+    a.a_geometric = 1 if a_geometric else 0
     n = C.c_size_t(0)
     L.check(L.lib().hx_mamba_block_workspace_bytes(C.byref(a), C.byref(n)))
     if workspace is None:
         workspace = torch.empty(n.value, dtype=torch.uint8, device=x.device)
     a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
-    a.scan_variant = scan_variant
-    if a_geometric is None:
-        a_geometric = check_geometric(w["A"])
-    a.a_geometric = 1 if a_geometric else 0
     if h_last is not None:
         a.h_last = h_last.data_ptr()
     if conv_state is not None:

@@ -213,6 +213,39 @@ HX_API hx_status hx_device_check(void);
  * afterwards; hx_device_check() reports the event.  The default limit (2^22 polls) is restored on `stream`. */
 HX_API hx_status hx_debug_scan_orphan_segment(const hx_scan_args *args, int32_t polls, void *stream);
 
+/* ---- the one exchange of the multi-GPU path: all-gather of a channel-sharded y over NVLink.
+ * The wide scan shards d_inner over the GPUs of one node (one process per GPU; B and C replicated; no collective
+ * inside the scan).  Afterwards every rank PUSHES its y[:, :, col0 : col0 + d_shard] into the full
+ * [batch, seq_len, d_full] buffer of every rank, its own included, with plain 16-byte stores through peer-mapped
+ * pointers: one kernel per rank, nothing is loaded from a peer, the result has the [B, L, D] layout directly.
+ * The reference has no distributed code (no counterpart); an NCCL all-gather would concatenate on the outermost
+ * axis instead.
+ *   hx_ipc_export / hx_ipc_open / hx_ipc_close: CUDA IPC plumbing for one process per GPU.  Export the base
+ *   pointer of an hx_alloc allocation into a 64-byte handle, send the handle to the peers by any host channel,
+ *   open it there (maps the allocation and enables peer access), close it before the owner frees it.
+ *   hx_allgather_y_push: queues this rank's push of batch rows [row_begin, row_end) on `stream` (so a caller can
+ *   scan rows in groups and push a finished group on a second stream under the scan of the next).  dst[g] is rank
+ *   g's full buffer as mapped in THIS process (dst[rank] is the local one).  Widths and col0 must be multiples of
+ *   16 bytes.  The buffers are complete everywhere once every rank has synchronised its stream and the ranks have
+ *   met at a host barrier. */
+#define HX_MAX_PEERS 8
+#define HX_IPC_HANDLE_BYTES 64
+typedef struct hx_gather_args {
+    int32_t world, rank;
+    int32_t batch, seq_len, d_shard, d_full;
+    int32_t col0;             /* first channel of this rank's shard in the full tensor */
+    int32_t io_dtype;
+    const void *y_local;      /* [batch, seq_len, d_shard] dense */
+    void *dst[HX_MAX_PEERS];  /* [batch, seq_len, d_full] dense, one per rank */
+    int32_t row_begin, row_end;
+    int32_t max_ctas_per_sm;  /* 0 = 4: the kernel is bound by the link and may share the GPU with a scan */
+    int32_t reserved;
+} hx_gather_args;
+HX_API hx_status hx_ipc_export(const void *dptr, void *handle64);
+HX_API hx_status hx_ipc_open(const void *handle64, void **dptr);
+HX_API hx_status hx_ipc_close(void *dptr);
+HX_API hx_status hx_allgather_y_push(const hx_gather_args *args, void *stream);
+
 /* Measures, on the current device, how many results per second one arithmetic pipe retires: fp32
  * fused multiply-adds (scalar, or the packed two-wide form, counted per lane) or special-function
  * ex2.approx results.  The scan is bound by these pipes rather than by HBM, so the benchmark reports it

@@ -218,3 +218,29 @@ def round_bf16(x):
     out = np.empty_like(x)
     lib().orc_round_bf16(_p(x), _p(out), _i(x.size))
     return out
+
+
+def byte_lm_bf16_storage(tokens, emb, layers: list, normf_w, d_state: int, d_conv: int, eps=1e-5):
+    """The byte LM of byte_lm() with every value rounded to bf16 at the points where a bf16 activation path has
+    to store it (the normed block input, the in_proj output, u, the x_proj output, the scan output, the logits),
+    f32 arithmetic everywhere else and an f32 residual stream.  This is not a second oracle: it measures how far
+    bf16 STORAGE alone moves the f32 result, i.e. the floor no bf16 implementation of the model can go below,
+    so that a test can tell rounding of the format from error of a kernel.  tokens [B, L] -> logits [B, L, 256]."""
+    rb = round_bf16
+    tokens = np.asarray(tokens)
+    out = []
+    for row in tokens:
+        h = np.asarray(emb, np.float32)[row].astype(np.float32)
+        for w in layers:
+            E, R = w["W_in"].shape[0] // 2, w["W_dt"].shape[1]
+            x = rb(rmsnorm(h, w["norm_w"], eps))
+            xz = rb(linear(x, w["W_in"]))
+            u = rb(conv_silu(np.ascontiguousarray(xz[:, :E])[None], w["conv_w"], w.get("conv_b"))[0])
+            dbc = rb(linear(u, w["W_x"]))
+            dt = linear(np.ascontiguousarray(dbc[:, :R]), w["W_dt"])
+            y = selective_scan(u[None], dt[None], w["A"], np.ascontiguousarray(dbc[None, :, R:R + d_state]),
+                               np.ascontiguousarray(dbc[None, :, R + d_state:]), D=w["D"], z=np.ascontiguousarray(xz[:, E:])[None],
+                               dt_bias=w["b_dt"])[0]
+            h = h + linear(rb(y), w["W_out"])
+        out.append(rb(linear(rb(rmsnorm(h, normf_w, eps)), emb)))
+    return np.stack(out)

@@ -492,3 +492,34 @@ def test_carry_wait_that_runs_out_is_reported_not_trapped():
     # argument checks of the test aid itself
     a.seq_splits = 3
     assert _lib.lib().hx_debug_scan_orphan_segment(C.byref(a), 2000, st) == 10
+
+
+def test_gather_push_places_shards_at_their_columns():
+    """hx_allgather_y_push on one GPU: two 'ranks' in one process, each with its own full buffer, both buffers local
+    (the kernel only sees pointers).  After both pushes both buffers hold the concatenation of the shards; a push
+    of a row range touches those rows only."""
+    import ctypes as C
+    import torch
+    from helixml_b200 import _lib
+    B, L, D = 3, 50, 192
+    widths = [(0, 128), (128, 192)]
+    full = torch.randn(B, L, D, device="cuda").to(torch.bfloat16)
+    bufs = [torch.zeros(B, L, D, dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for r, (c0, c1) in enumerate(widths):
+        shard = full[:, :, c0:c1].contiguous()
+        a = _lib.GatherArgs()
+        a.world, a.rank, a.batch, a.seq_len, a.d_shard, a.d_full, a.col0, a.io_dtype = 2, r, B, L, c1 - c0, D, c0, _lib.HX_BF16
+        a.y_local = shard.data_ptr()
+        a.dst[0], a.dst[1] = bufs[0].data_ptr(), bufs[1].data_ptr()
+        a.row_begin, a.row_end = (0, B) if r == 0 else (1, 3)
+        _lib.check(_lib.lib().hx_allgather_y_push(C.byref(a), st))
+    torch.cuda.synchronize()
+    for buf in bufs:
+        assert torch.equal(buf[:, :, :128], full[:, :, :128])
+        assert torch.equal(buf[1:, :, 128:], full[1:, :, 128:])
+        assert torch.count_nonzero(buf[0, :, 128:]) == 0  # row 0 of rank 1's shard was not pushed
+    a.col0 = 4  # 8 bytes: not a 16-byte multiple
+    assert _lib.lib().hx_allgather_y_push(C.byref(a), st) == 5
+    a.col0, a.world = 128, 9
+    assert _lib.lib().hx_allgather_y_push(C.byref(a), st) == 10
