@@ -620,13 +620,15 @@ def run_lm(args, cfg, name):
         # launches per block beyond norm + in_proj + conv + x_proj + out_proj: 1 = one-pass scan with the dt
         # projection inside, 2 = look-back scan (aggregate pass + output pass), or dt_proj GEMM + scan
         per_block = (launches - 3) // cfg["n_layer"]
-        fused = stage_ms["dt_proj"] < 1e-3
+        fused = stage_ms["dt_proj"] < 0.008 * cfg["n_layer"]   # only the event marks: no GEMM ran in that stage
         if fused and per_block == 6:
             scan_kernel = "scan_direct_kernel (chained segments, dt projection inside)"
         elif fused:
             scan_kernel = "scan_direct_kernel (look-back: aggregate pass + output pass, dt projection inside)"
+        elif per_block == 8:
+            scan_kernel = "scan_direct_kernel (look-back: aggregate pass + output pass), dt_proj GEMM before it"
         else:
-            scan_kernel = "selective scan with a dt_proj GEMM of its own"
+            scan_kernel = "selective scan (one launch), dt_proj GEMM before it"
         traffic, traffic_src = ncu_traffic(name, scan_kernel) if world == 1 else (None, "single-GPU captures only")
         # the scan is the largest single stage (and the top entry of the ncu launch list); the GEMMs, five
         # shapes of one kernel, are reported beside it under "gemm"
@@ -814,8 +816,11 @@ def main():
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="lm workloads at N > 1: one batch sharded by rows (strong) or the whole batch on every rank (weak)")
     ap.add_argument("cases", nargs="*", help="kernels_gemm: shapes to time (default all)")
+    ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (to look at one GPU's share of a sharded batch)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
+    if args.batch > 0 and "batch" in cfg:
+        cfg = dict(cfg, batch=args.batch)
     if args.impl == "reference":
         (run_reference_lm if cfg["kind"] == "lm" else run_reference)(args, cfg, args.workload)
         return

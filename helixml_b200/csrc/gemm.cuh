@@ -20,6 +20,11 @@ template <int EPI> __device__ __forceinline__ float apply_epilogue(float v) {
 hx_status launch_skinny(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias, void *C, int64_t ldc,
                         int c_dtype, int M, int N, int K, int epi, int epi_col0, cudaStream_t st);
 
+// The short-inner-dimension kernel (gemm_lowk.cu): K <= 64 and a multiple of 8, N a multiple of 8, bf16 C with a
+// 16-byte aligned base and row stride, no bias, no epilogue.
+hx_status launch_lowk(const void *A, int64_t lda, const void *W, int64_t ldw, void *C, int64_t ldc, int M, int N, int K,
+                      cudaStream_t st);
+
 hx_status validate_gemm(const void *A, int64_t lda, const void *W, int64_t ldw, void *C, int64_t ldc, int M, int N, int K);
 
 }  // namespace gemm

@@ -372,6 +372,11 @@ extern "C" hx_status hx_gemm_bf16_cols(const void *A, int64_t lda, const void *W
     // a handful of rows (a decode step): stream the weights through many small CTAs instead of one 128-row tile
     if (M <= 64 && K % 32 == 0 && (reinterpret_cast<uintptr_t>(A) & 15) == 0 && (reinterpret_cast<uintptr_t>(W) & 15) == 0)
         return launch_skinny(A, lda, W, ldw, bias, C, ldc, c_dtype, M, N, K, epilogue, epi_col0, st);
+    // a short inner dimension (dt_proj, K = dt_rank): bound by writing C, which a store-shaped kernel does at twice the
+    // rate of the tile kernel's epilogue
+    if (K <= 64 && M > 64 && N % 8 == 0 && N >= 64 && c_dtype == HX_BF16 && bias == nullptr && epilogue == kEpiNone &&
+        (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * 2) % 16 == 0)
+        return launch_lowk(A, lda, W, ldw, C, ldc, M, N, K, st);
     const int BN = N > 128 ? 256 : 128;
     CUtensorMap ma, mw;
     const uint64_t dims_a[2] = {(uint64_t)K, (uint64_t)M}, dims_w[2] = {(uint64_t)K, (uint64_t)N};

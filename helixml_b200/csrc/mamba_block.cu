@@ -79,7 +79,11 @@ static bool fuses_dt(const hx_mamba_block_args *a, int W, int splits) {
     if (a->scan_variant != HX_SCAN_AUTO) return false;
     hx_scan_args sa = scan_shape(a);
     sa.seq_splits = splits;
-    return hx::scan::auto_kind(&sa) != hx::scan::ScanKind::Tiled;
+    // AUTO fuses only into the one-pass kernel (there the fused form and a dt_proj kernel + unfused scan take the same
+    // time, 12.9 against 11.5 + 1.5 ms over 24 blocks at 32 x 2048 x 1536, and the fused form moves 0.4 GB less).  The look-back form has CTAs to spare and lives on occupancy: with
+    // the projection's weight and fp32 dt tiles in shared memory 3 CTAs fit an SM, without them 7, and measured at
+    // 4 to 16 rows of 2048 x 1536 the unfused form with a dt_proj GEMM of its own is the faster one.
+    return hx::scan::auto_kind(&sa) == hx::scan::ScanKind::Direct;
 }
 
 }  // namespace block

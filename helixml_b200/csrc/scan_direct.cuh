@@ -35,10 +35,8 @@ namespace hx {
 namespace scan {
 
 template <typename T, int CPL_, bool GEOM_, bool STD_, int STAGES_, bool FUSEDT_ = false, bool ZGATE_ = false,
-          bool BLOCK_ = false, int MODE_ = 0, int XV_ = 0>
+          bool BLOCK_ = false, int MODE_ = 0>
 struct DirectCfg {
-    static constexpr int XV = XV_;                     // experimental selector: unroll factor of the step loop
-    static constexpr int UNR = XV_ == 1 ? 4 : (XV_ == 2 ? 16 : 8);
     static constexpr int MODE = MODE_;                 // 0 chained segments, 1 aggregate pass, 2 output pass (see above)
     static constexpr bool BLOCK = BLOCK_;              // the Mamba block's call: no conv (u is given), gate and softplus
                                                        // present, all known at compile time
@@ -508,7 +506,8 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             }
         }
 
-#pragma unroll(Cfg::UNR)
+// unrolled by 8: 4 is 10 % slower, 16 no faster (measured at 49 152 chains)
+#pragma unroll 8
         for (int t = 0; t < steps; ++t) {
             float xc[CPL], dr[CPL], zr[CPL];
             if constexpr (CPL == 2) {

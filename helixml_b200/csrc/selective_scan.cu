@@ -929,10 +929,10 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
 
 
 template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2, bool FUSEDT = false, bool ZGATE = false, bool BLOCK = false,
-          int MODE = 0, int XV = 0>
+          int MODE = 0>
 static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *maps, dim3 grid, cudaStream_t st, void *y,
                                     int64_t y_bs, int64_t y_rs) {
-    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES, FUSEDT, ZGATE, BLOCK, MODE, XV>;
+    using Cfg = DirectCfg<T, CPL, GEOM, STD, STAGES, FUSEDT, ZGATE, BLOCK, MODE>;
     auto kern = scan_direct_kernel<T, Cfg>;
     static std::atomic<bool> attr_set[64];  // zero-initialised; setting the attribute twice is harmless
     int dev = 0;
@@ -1108,15 +1108,6 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
         }
         if (geom) return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
         return launch_direct_inst<__nv_bfloat16, 1, false, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
-    }
-    if (bf && geom && stdp && a->reserved / 100 >= 1 && form == 0) {  // experimental loop organisations
-        const int xv = a->reserved / 100;
-        if (cpl == 2) {
-            if (xv == 1) return launch_direct_inst<__nv_bfloat16, 2, true, true, 2, false, false, false, 0, 1>(p, maps, grid, st, yv, ybs, yrs);
-            return launch_direct_inst<__nv_bfloat16, 2, true, true, 2, false, false, false, 0, 2>(p, maps, grid, st, yv, ybs, yrs);
-        }
-        if (xv == 1) return launch_direct_inst<__nv_bfloat16, 1, true, true, 2, false, false, false, 0, 1>(p, maps, grid, st, yv, ybs, yrs);
-        return launch_direct_inst<__nv_bfloat16, 1, true, true, 2, false, false, false, 0, 2>(p, maps, grid, st, yv, ybs, yrs);
     }
     if (bf && geom && stdp && a->reserved / 10 == 1) {  // tuning: three stages instead of two
         if (cpl == 2) return launch_direct_inst<__nv_bfloat16, 2, true, true, 3>(p, maps, grid, st, yv, ybs, yrs);

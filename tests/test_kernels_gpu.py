@@ -138,6 +138,23 @@ def test_gemm_tcgen05_bf16(M, N, K):
     assert rel_l2(to_np(got16), ref) <= 5e-3
 
 
+@pytest.mark.parametrize("M,N,K,lda", [(500, 1536, 48, 80), (130, 200, 8, 8), (40000, 64, 64, 64), (100000, 72, 24, 40), (65, 1536, 48, 48),
+                                       (4097, 136, 56, 56)])
+def test_gemm_short_inner_dimension_bf16(M, N, K, lda):
+    """K <= 64 with a bf16 result goes to the store-shaped kernel (the dt_proj shape): A as a column slice of a wider
+    row (the x_proj output), ragged row and column counts, both CTA heights."""
+    from helixml_b200 import ops
+    wide = synth.round_bf16(synth.normal(65, "a", (M, lda)))
+    w = synth.round_bf16(synth.normal(65, "w", (N, K), 0, 0.2))
+    got = ops.gemm(to_dev(wide, "bf16")[:, :K], to_dev(w, "bf16"))
+    _status_ok()
+    ref = wide[:, :K].astype(np.float64) @ w.astype(np.float64).T
+    g = to_np(got)
+    assert rel_l2(g, ref) <= 5e-3
+    # every element is the correctly rounded fp32-accumulated product: within one bf16 step of the exact value
+    assert np.max(np.abs(g - ref) / (np.abs(ref) + 1e-2)) <= 2.0 ** -7
+
+
 def test_gemm_tcgen05_bias_epilogue_and_strides():
     import torch
     from helixml_b200 import _lib, ops

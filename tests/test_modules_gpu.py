@@ -327,7 +327,7 @@ def test_byte_lm_full_size_config3_sampled_sequences():
 
 def test_byte_lm_small_batch_runs_the_lookback_scan():
     """Four sequences per GPU is what one of eight GPUs gets of configuration 3's batch: too few chains for one pass,
-    so the blocks run the look-back form of the scan (two launches), still with the dt projection inside."""
+    so the blocks run the look-back form of the scan (two launches) after a dt_proj GEMM of its own."""
     import torch
     from helixml_b200 import _lib, nn
     nl, M, B, L = 3, 768, 4, 1024
@@ -342,7 +342,7 @@ def test_byte_lm_small_batch_runs_the_lookback_scan():
     logits = torch.empty((B, L, 256), dtype=torch.bfloat16, device="cuda")
     lm.forward_device(tok_d.data_ptr(), logits.data_ptr(), B, L, torch.cuda.current_stream().cuda_stream)
     _lib.check_device()
-    assert lm.launches_per_forward == 1 + nl * 7 + 2  # norm, in_proj, conv, x_proj, aggregate pass, output pass, out_proj
+    assert lm.launches_per_forward == 1 + nl * 8 + 2  # norm, in_proj, conv, x_proj, dt_proj, aggregate pass, output pass, out_proj
     ref = cbind.byte_lm(tok, emb_q, layers_q, normf, 16, 4)
     g = logits.float().cpu().numpy()
     assert rel_l2(g, ref) <= BF16_TOL
