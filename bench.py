@@ -531,6 +531,8 @@ def run_lm(args, cfg, name):
     strong = args.scaling == "strong"
     nn.manual_seed(cfg["seed"])          # same weights on every rank: a replica per GPU
     lm = nn.ByteLM(cfg["n_layer"], cfg["d_model"], cfg["d_state"], cfg["d_conv"], cfg["expand"], nn.Device.cuda(local), nn.BF16)
+    if args.no_graph:
+        lm.forward_graph(False)
     if strong:
         # ONE batch of GB sequences, rank r prefills its contiguous block of rows (no collective on the path)
         r0, r1 = shard.batch_shard(GB, world, rank)
@@ -660,6 +662,7 @@ def run_lm(args, cfg, name):
                      "compute_roof": scan_compute_roof(B * L * E, N, 0, scan_bytes, peaks["hbm_gbs"], pipe_rates(),
                                                        scan_ms)},
             "gemm": {"tflops": gemm_tflops, "frac_of_sustained_peak": gemm_tflops / peaks["bf16_tflops_sustained"], "ms_total": gemm_ms},
+            "forward_as": "plain launches" if args.no_graph else "one CUDA graph replay per step (captured on the second call)",
             "parity_checked": parity,
             "cpu_baseline": cpu, "cpu_baseline_1core": cpu1, "e2e": e2e, "gpu_launches": args.steps * launches, "clocks": clocks,
             "device_status": status,
@@ -812,6 +815,7 @@ def main():
     ap.add_argument("--gather-groups", type=int, default=2, help="row groups whose pushes overlap the next group's scan")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="lm workloads: plain launches instead of the replayed CUDA graph of the forward")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of one sequence of the timed path")
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="lm workloads at N > 1: one batch sharded by rows (strong) or the whole batch on every rank (weak)")

@@ -195,6 +195,7 @@ _PROTOS = {
     "hx_byte_lm_prefill_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "hx_byte_lm_decode_step_device": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p]),
     "hx_byte_lm_decode_graph": (C.c_int, [C.c_void_p, C.c_int32]),
+    "hx_byte_lm_forward_graph": (C.c_int, [C.c_void_p, C.c_int32]),
     "hx_byte_lm_launches_per_decode_step": (C.c_int64, [C.c_void_p]),
     "hx_byte_lm_profile": (C.c_int, [C.c_void_p, C.c_int32]),
     "hx_byte_lm_profile_read": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_int32)]),

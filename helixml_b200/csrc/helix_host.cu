@@ -551,7 +551,41 @@ struct ByteLM::Profile {
     }
 };
 
+// Captured forwards, keyed by what a graph bakes in: the caller's two pointers, the shape and whether the decode
+// state is kept.  `seen` counts plain runs of a key: the first call runs as plain launches (it also sets the
+// kernels' attributes), the second is captured.
+struct ByteLM::FwdGraphs {
+    struct Entry {
+        const void *tok = nullptr;
+        void *logits = nullptr;
+        int64_t batch = 0, seq_len = 0;
+        bool keep = false;
+        int seen = 0;
+        cudaGraphExec_t exec = nullptr;
+        uint64_t used = 0;
+    };
+    std::vector<Entry> entries;
+    cudaStream_t capture_stream = nullptr;
+    uint64_t tick = 0;
+    void clear() {
+        for (auto &e : entries)
+            if (e.exec) cudaGraphExecDestroy(e.exec);
+        entries.clear();
+    }
+    ~FwdGraphs() {
+        clear();
+        if (capture_stream) cudaStreamDestroy(capture_stream);
+    }
+};
+
+void ByteLM::set_forward_graph(bool enable) {
+    std::lock_guard<std::recursive_mutex> lock(mu_);
+    forward_graph_ = enable;
+    if (!enable && fwd_) fwd_->clear();
+}
+
 ByteLM::~ByteLM() {
+    delete fwd_;
     delete buf_;
     delete prof_;
     delete dec_;
@@ -610,6 +644,10 @@ Result<std::unique_ptr<ByteLM>> ByteLM::create(int64_t n_layer, int64_t d_model,
 }
 
 Result<Unit> ByteLM::parameters_updated() {
+    {
+        std::lock_guard<std::recursive_mutex> lock(mu_);
+        if (fwd_) fwd_->clear();  // a captured forward bakes in the kernel choice the parameters imply
+    }
     for (auto &b : blocks) HELIX_TRY(b->parameters_updated());
     return Unit{};
 }
@@ -753,6 +791,71 @@ Result<Unit> ByteLM::run_layers(const uint8_t *tokens_dev, void *logits_dev, int
     std::lock_guard<std::recursive_mutex> lock(mu_);
     if (batch <= 0 || seq_len <= 0) return err(HX_ERR_INVALID_DIMENSION, "ByteLM: batch and seq_len must be positive");
     HELIX_TRY(use_device(device_));
+    const bool had_buffers = buf_ && buf_->batch == batch && buf_->seq_len == seq_len;
+    HELIX_TRY(ensure_buffers(batch, seq_len));
+    if (!had_buffers && fwd_) fwd_->clear();  // the graphs point into the old activation buffers
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing((cudaStream_t)stream, &cap);
+    if (!forward_graph_ || prof_ || cap != cudaStreamCaptureStatusNone)
+        return run_layers_plain(tokens_dev, logits_dev, batch, seq_len, stream, keep_state);
+    if (keep_state) {
+        const bool had_decode = dec_ && dec_->batch == batch;
+        HELIX_TRY(ensure_decode(batch));  // allocate outside any capture
+        if (!had_decode && fwd_) fwd_->clear();  // graphs that keep the state point into the old state buffers
+        dec_->steps = 0;
+    }
+    if (!fwd_) fwd_ = new FwdGraphs();
+    FwdGraphs::Entry *e = nullptr;
+    for (auto &c : fwd_->entries)
+        if (c.tok == tokens_dev && c.logits == logits_dev && c.batch == batch && c.seq_len == seq_len && c.keep == keep_state) e = &c;
+    if (!e) {
+        if (fwd_->entries.size() >= 4) {  // drop the least recently used
+            size_t lru = 0;
+            for (size_t i = 1; i < fwd_->entries.size(); ++i)
+                if (fwd_->entries[i].used < fwd_->entries[lru].used) lru = i;
+            if (fwd_->entries[lru].exec) cudaGraphExecDestroy(fwd_->entries[lru].exec);
+            fwd_->entries.erase(fwd_->entries.begin() + lru);
+        }
+        FwdGraphs::Entry n;
+        n.tok = tokens_dev; n.logits = logits_dev; n.batch = batch; n.seq_len = seq_len; n.keep = keep_state;
+        fwd_->entries.push_back(n);
+        e = &fwd_->entries.back();
+    }
+    e->used = ++fwd_->tick;
+    if (!e->exec && e->seen >= 1) {
+        if (!fwd_->capture_stream && cudaStreamCreateWithFlags(&fwd_->capture_stream, cudaStreamNonBlocking) != cudaSuccess)
+            return err(HX_ERR_BACKEND, "ByteLM: cannot create the capture stream");
+        if (cudaStreamBeginCapture(fwd_->capture_stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess)
+            return err(HX_ERR_BACKEND, "ByteLM: cudaStreamBeginCapture failed");
+        auto r = run_layers_plain(tokens_dev, logits_dev, batch, seq_len, fwd_->capture_stream, keep_state);
+        cudaGraph_t graph = nullptr;
+        const cudaError_t ce = cudaStreamEndCapture(fwd_->capture_stream, &graph);
+        if (!r.ok()) {
+            if (graph) cudaGraphDestroy(graph);
+            return r.error();
+        }
+        if (ce != cudaSuccess || !graph) {
+            cudaGetLastError();
+            return err(HX_ERR_BACKEND, "ByteLM: stream capture of the forward failed");
+        }
+        const cudaError_t ie = cudaGraphInstantiate(&e->exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ie != cudaSuccess) {
+            e->exec = nullptr;
+            cudaGetLastError();
+            return err(HX_ERR_BACKEND, "ByteLM: cudaGraphInstantiate of the forward failed");
+        }
+    }
+    if (e->exec) {
+        if (cudaGraphLaunch(e->exec, (cudaStream_t)stream) != cudaSuccess) return err(HX_ERR_BACKEND, "ByteLM: graph launch failed");
+        return Unit{};
+    }
+    e->seen += 1;
+    return run_layers_plain(tokens_dev, logits_dev, batch, seq_len, stream, keep_state);
+}
+
+Result<Unit> ByteLM::run_layers_plain(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream,
+                                      bool keep_state) {
     HELIX_TRY(ensure_buffers(batch, seq_len));
     if (keep_state) {
         HELIX_TRY(ensure_decode(batch));
@@ -1015,6 +1118,14 @@ hx_status hx_byte_lm_decode_step_device(hx_module *m, const uint8_t *tokens_dev,
     HX_REQUIRE(lm != nullptr, HX_ERR_UNSUPPORTED_OPERATION, "decode step on a module that is not a ByteLM");
     auto r = lm->decode_step_device(tokens_dev, logits_dev, batch, stream);
     HX_RETURN_IF_ERR(r);
+    return HX_OK;
+}
+
+hx_status hx_byte_lm_forward_graph(hx_module *m, int32_t enable) {
+    HX_REQUIRE(m != nullptr, HX_ERR_INVALID_INPUT, "hx_byte_lm_forward_graph: module is NULL");
+    auto *lm = dynamic_cast<helix::ByteLM *>(m->m.get());
+    HX_REQUIRE(lm != nullptr, HX_ERR_UNSUPPORTED_OPERATION, "forward graph on a module that is not a ByteLM");
+    lm->set_forward_graph(enable != 0);
     return HX_OK;
 }
 

@@ -248,6 +248,10 @@ class ByteLM : public Module {
     Result<Unit> prefill_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream);
     Result<Unit> decode_step_device(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, void *stream);
     void set_decode_graph(bool enable) { decode_graph_ = enable; }
+    // forward_device / prefill_device / forward_host replay a CUDA graph of the whole forward from the second call
+    // with the same (tokens, logits, batch, seq_len) on: 150 to 200 dependent kernels become one launch, which is
+    // what a small batch (a few sequences per GPU) is bound by.  Off: plain launches.
+    void set_forward_graph(bool enable);
     int64_t launches_per_decode_step() const;
     // per-stage CUDA-event timing (see hx_byte_lm_profile in the C header)
     Result<Unit> set_profile(bool enable);
@@ -276,6 +280,11 @@ class ByteLM : public Module {
     struct Decode;
     Decode *dec_ = nullptr;
     bool decode_graph_ = true;
+    struct FwdGraphs;
+    FwdGraphs *fwd_ = nullptr;
+    bool forward_graph_ = true;
+    Result<Unit> run_layers_plain(const uint8_t *tokens_dev, void *logits_dev, int64_t batch, int64_t seq_len, void *stream,
+                                  bool keep_state);
     struct Profile;
     Profile *prof_ = nullptr;
     // The activation buffers, the decode state and the profile belong to the module: every call that touches them

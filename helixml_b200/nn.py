@@ -390,6 +390,10 @@ class ByteLM(Module):
         L.check(L.lib().hx_byte_lm_decode_step_device(self._h, C.c_void_p(tokens_ptr), C.c_void_p(logits_ptr), batch,
                                                       C.c_void_p(stream)))
 
+    def forward_graph(self, enable: bool) -> None:
+        """Replay of a captured CUDA graph of the whole forward from the second identical call on (default on)."""
+        L.check(L.lib().hx_byte_lm_forward_graph(self._h, 1 if enable else 0))
+
     def decode_graph(self, enable: bool) -> None:
         L.check(L.lib().hx_byte_lm_decode_graph(self._h, 1 if enable else 0))
 

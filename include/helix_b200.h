@@ -529,6 +529,11 @@ HX_API hx_status hx_byte_lm_forward_host(hx_module *m, const uint8_t *tokens_hos
                                   int64_t seq_len, void *stream);
 HX_API hx_status hx_byte_lm_forward_device(hx_module *m, const uint8_t *tokens_dev, void *logits_dev, int64_t batch,
                                     int64_t seq_len, void *stream);
+/* From the second call with the same (tokens pointer, logits pointer, batch, seq_len) on, the three forward calls
+ * above and the prefill below replay a CUDA graph of the whole forward (one launch instead of 150 to 200 dependent
+ * kernels: what a batch of a few sequences per GPU is bound by).  hx_byte_lm_forward_graph(m, 0) keeps plain
+ * launches; a stream that is itself being captured, and the per-stage profile, always get plain launches. */
+HX_API hx_status hx_byte_lm_forward_graph(hx_module *m, int32_t enable);
 /* Serving with state: hx_byte_lm_prefill_device is hx_byte_lm_forward_device that also keeps, per layer, the
  * scan's final state and the conv window; hx_byte_lm_decode_step_device then advances every sequence of that
  * batch by one token: tokens_dev [batch] u8 in, logits_dev [batch, 256] (model dtype) out, state updated in the

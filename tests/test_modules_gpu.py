@@ -375,3 +375,51 @@ def test_byte_lm_handle_shared_by_two_threads():
         t.join()
     assert not errors, errors
     assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1])
+
+
+@pytest.mark.parametrize("dtype_name", ["f32", "bf16"])
+def test_byte_lm_forward_graph_replay_equals_plain_launches(dtype_name):
+    """The second and later calls of forward_device with the same buffers replay a captured graph of the whole
+    forward: same bits as plain launches, also after the tokens in the buffer changed, after a different shape was
+    run in between, and for the prefill that keeps the decode state."""
+    import torch
+    from helixml_b200 import _lib, nn
+    bf = dtype_name == "bf16"
+    M, nl, B, L = 128, 3, 2, 200
+    emb, layers, normf = _lm_weights(13, nl, M)
+    td = torch.bfloat16 if bf else torch.float32
+    lm = nn.ByteLM(nl, M, dtype=nn.BF16 if bf else nn.F32)
+    lm.load_weights(emb, layers, normf)
+    toks = [torch.from_numpy(synth.random_bytes(13, f"t{i}", (B, L))).cuda() for i in range(3)]
+    buf = torch.empty_like(toks[0])
+    out = torch.empty(B, L, 256, device="cuda", dtype=td)
+    lm.forward_graph(False)
+    want = []
+    for t in toks:
+        buf.copy_(t)
+        lm.forward_device(buf.data_ptr(), out.data_ptr(), B, L)
+        torch.cuda.synchronize()
+        want.append(out.clone())
+    lm.forward_graph(True)
+    for rnd in range(2):
+        for i, t in enumerate(toks):  # call 1 plain, call 2 captures, later calls replay
+            buf.copy_(t)
+            lm.forward_device(buf.data_ptr(), out.data_ptr(), B, L)
+            torch.cuda.synchronize()
+            assert torch.equal(out, want[i]), (rnd, i)
+        # another shape in between drops the graphs (they point into the old activation buffers)
+        small = torch.empty(1, 64, 256, device="cuda", dtype=td)
+        lm.forward_device(toks[0][:1, :64].contiguous().data_ptr(), small.data_ptr(), 1, 64)
+    # prefill with state through the graph, then a decode step: same as with plain launches
+    nxt = torch.from_numpy(synth.random_bytes(13, "nxt", (B,))).cuda()
+    res = []
+    for graph in (False, True):
+        lm.forward_graph(graph)
+        for _ in range(3):
+            lm.prefill_device(toks[1].data_ptr(), out.data_ptr(), B, L)
+        lg = torch.empty(B, 256, device="cuda", dtype=td)
+        lm.decode_step_device(nxt.data_ptr(), lg.data_ptr(), B)
+        torch.cuda.synchronize()
+        res.append((out.clone(), lg.clone()))
+    assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
+    assert _lib.device_status() == 0
