@@ -176,6 +176,9 @@ _PROTOS = {
     "hx_s4_block_new": (C.c_int, [C.c_int64, C.c_int64, C.c_int32, C.POINTER(C.c_void_p)]),
     "hx_linear_new": (C.c_int, [C.c_int64, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.POINTER(C.c_void_p)]),
     "hx_rmsnorm_new": (C.c_int, [C.c_int64, C.c_float, C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_sequential_new": (C.c_int, [C.c_int32, C.POINTER(C.c_void_p)]),
+    "hx_sequential_add": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "hx_sequential_len": (C.c_int32, [C.c_void_p]),
     "hx_byte_lm_new": (C.c_int, [C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int32,
                                  C.POINTER(C.c_void_p)]),
     "hx_module_forward": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)]),

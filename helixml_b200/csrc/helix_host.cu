@@ -509,6 +509,35 @@ std::vector<DeviceTensor *> MambaBlock::parameters_mut() {
     return {&W_in, &conv_w, &conv_b, &W_x, &W_dt, &b_dt, &A, &D, &W_out};
 }
 
+// ------------------------------------------------------------------------------------------ Sequential
+Result<DeviceTensor> Sequential::forward(const DeviceTensor &input) const {
+    auto cur = input.clone();  // `let mut output = input.clone()` (crates/nn/src/lib.rs:605)
+    if (!cur.ok()) return cur.error();
+    DeviceTensor t = std::move(cur.value());
+    for (const auto &m : modules_) {
+        auto r = m->forward(t);
+        if (!r.ok()) return r.error();
+        t = std::move(r.value());
+    }
+    return t;
+}
+std::vector<const DeviceTensor *> Sequential::parameters() const {
+    std::vector<const DeviceTensor *> p;
+    for (const auto &m : modules_)
+        for (auto *t : static_cast<const Module *>(m.get())->parameters()) p.push_back(t);
+    return p;
+}
+std::vector<DeviceTensor *> Sequential::parameters_mut() {
+    std::vector<DeviceTensor *> p;
+    for (auto &m : modules_)
+        for (auto *t : m->parameters_mut()) p.push_back(t);
+    return p;
+}
+Result<Unit> Sequential::parameters_updated() {
+    for (auto &m : modules_) HELIX_TRY(m->parameters_updated());
+    return Unit{};
+}
+
 // ------------------------------------------------------------------------------------------ ByteLM
 struct ByteLM::Buffers {
     int64_t batch = 0, seq_len = 0;
@@ -1119,6 +1148,28 @@ hx_status hx_byte_lm_decode_step_device(hx_module *m, const uint8_t *tokens_dev,
     auto r = lm->decode_step_device(tokens_dev, logits_dev, batch, stream);
     HX_RETURN_IF_ERR(r);
     return HX_OK;
+}
+
+hx_status hx_sequential_new(int32_t device_id, hx_module **out) {
+    HX_REQUIRE(out != nullptr, HX_ERR_INVALID_INPUT, "hx_sequential_new: out is NULL");
+    *out = new hx_module{std::unique_ptr<helix::Module>(new helix::Sequential(dev_of(device_id)))};
+    return HX_OK;
+}
+
+hx_status hx_sequential_add(hx_module *seq, hx_module *child) {
+    HX_REQUIRE(seq && child && seq != child, HX_ERR_INVALID_INPUT, "hx_sequential_add: bad arguments");
+    auto *s = dynamic_cast<helix::Sequential *>(seq->m.get());
+    HX_REQUIRE(s != nullptr, HX_ERR_UNSUPPORTED_OPERATION, "hx_sequential_add on a module that is not a Sequential");
+    HX_REQUIRE(child->m != nullptr, HX_ERR_INVALID_INPUT, "hx_sequential_add: the child handle is empty");
+    HX_REQUIRE(child->m->device() == s->device(), HX_ERR_DEVICE_MISMATCH, "hx_sequential_add: child on another device");
+    s->add(std::move(child->m));  // the Sequential owns the module now
+    delete child;
+    return HX_OK;
+}
+
+int32_t hx_sequential_len(const hx_module *seq) {
+    auto *s = seq ? dynamic_cast<const helix::Sequential *>(seq->m.get()) : nullptr;
+    return s ? (int32_t)s->len() : -1;
 }
 
 hx_status hx_byte_lm_forward_graph(hx_module *m, int32_t enable) {

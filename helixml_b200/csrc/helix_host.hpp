@@ -226,6 +226,25 @@ class MambaBlock : public Module {
     Device device_;
 };
 
+// nn::Sequential (crates/nn/src/lib.rs:577-661): an ordered list of modules, forward chains them, parameters
+// concatenates theirs.  add() takes ownership, like the reference's Box<dyn Module>.
+class Sequential : public Module {
+  public:
+    explicit Sequential(const Device &device) : device_(device) {}
+    void add(std::unique_ptr<Module> m) { modules_.push_back(std::move(m)); }
+    size_t len() const { return modules_.size(); }
+    Result<DeviceTensor> forward(const DeviceTensor &input) const override;
+    std::vector<const DeviceTensor *> parameters() const override;
+    std::vector<DeviceTensor *> parameters_mut() override;
+    Result<Unit> parameters_updated() override;
+    const Device &device() const override { return device_; }
+    const char *name() const override { return "Sequential"; }
+
+  private:
+    std::vector<std::unique_ptr<Module>> modules_;
+    Device device_;
+};
+
 // Byte-level LM: tied embedding [256, M], n_layer x (RMSNorm -> MambaBlock -> residual add), final
 // RMSNorm, logits = h . emb^T.  forward takes U8 tokens [B, L] and returns logits [B, L, 256].
 class ByteLM : public Module {

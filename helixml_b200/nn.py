@@ -341,6 +341,23 @@ class RMSNorm(Module):
         super().__init__(h)
 
 
+class Sequential(Module):
+    """nn::Sequential (crates/nn/src/lib.rs:577-661): `Sequential::new(&device)`, `add(module)`, `len()`.  add takes
+    ownership of the module, as the reference's `Box<dyn Module>` does: the Python object given is emptied."""
+
+    def __init__(self, device: Device = Device(0)):
+        h = C.c_void_p()
+        L.check(L.lib().hx_sequential_new(device.index, C.byref(h)))
+        super().__init__(h)
+
+    def add(self, module: Module) -> None:
+        L.check(L.lib().hx_sequential_add(self._h, module._h))
+        module._h = None  # consumed
+
+    def __len__(self) -> int:
+        return int(L.lib().hx_sequential_len(self._h))
+
+
 class ByteLM(Module):
     """Byte-level LM: tied embedding, n_layer x (RMSNorm + MambaBlock + residual), final norm, logits.
     parameters(): embedding, then per layer [norm_w, *MambaBlock.PARAMS], then norm_f."""

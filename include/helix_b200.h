@@ -512,6 +512,12 @@ HX_API hx_status hx_s4_block_new(int64_t d_model, int64_t d_state, int32_t devic
 HX_API hx_status hx_linear_new(int64_t in_features, int64_t out_features, int32_t bias, int32_t dtype,
                         int32_t device_id, hx_module **out);
 HX_API hx_status hx_rmsnorm_new(int64_t d_model, float eps, int32_t device_id, hx_module **out);
+/* nn::Sequential (crates/nn/src/lib.rs:577-661): Sequential::new(&device), add(module), len(); forward chains the
+ * modules, parameters concatenates theirs.  hx_sequential_add takes ownership: the child handle is consumed (do not
+ * use or free it afterwards), like the reference's Box<dyn Module>. */
+HX_API hx_status hx_sequential_new(int32_t device_id, hx_module **out);
+HX_API hx_status hx_sequential_add(hx_module *seq, hx_module *child);
+HX_API int32_t hx_sequential_len(const hx_module *seq);
 /* The byte-level LM of examples/ssm_byte_lm widened to n_layer x (RMSNorm + MambaBlock + residual), tied
  * embedding [256, d_model] (examples/ssm_byte_lm/src/main.rs:104-130). */
 HX_API hx_status hx_byte_lm_new(int64_t n_layer, int64_t d_model, int64_t d_state, int64_t d_conv, int64_t expand,

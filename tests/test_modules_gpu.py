@@ -423,3 +423,30 @@ def test_byte_lm_forward_graph_replay_equals_plain_launches(dtype_name):
         res.append((out.clone(), lg.clone()))
     assert torch.equal(res[0][0], res[1][0]) and torch.equal(res[0][1], res[1][1])
     assert _lib.device_status() == 0
+
+
+def test_sequential_chains_modules():
+    """nn::Sequential (crates/nn/src/lib.rs:577-661): add() in order, forward chains, parameters concatenates.  The
+    reference's own test builds Linear -> activation -> Linear and checks the output shape (lib.rs:1296-1313); here
+    the numbers are checked against the oracle as well."""
+    from helixml_b200 import _lib, nn
+    nn.manual_seed(21)
+    seq = nn.Sequential()
+    l1, norm, l2 = nn.Linear(48, 96, True), nn.RMSNorm(96), nn.Linear(96, 24, True)
+    w1, b1 = [p.numpy() for p in l1.parameters()]
+    wn = norm.parameters()[0].numpy()
+    w2, b2 = [p.numpy() for p in l2.parameters()]
+    for m in (l1, norm, l2):
+        seq.add(m)
+    assert len(seq) == 3 and seq.name == "Sequential" and len(seq.parameters()) == 5
+    assert l1._h is None  # consumed by add
+    x = synth.normal(21, "x", (10, 48))
+    got = seq(nn.Tensor.from_numpy(x)).numpy()
+    ref = cbind.linear(cbind.rmsnorm(cbind.linear(x, w1, b1), wn), w2, b2)
+    assert got.shape == (10, 24) and fp32_tol_err(got, ref) <= FP32_TOL
+    # an error inside the chain comes back as the module's error
+    with pytest.raises(_lib.HxError) as e:
+        seq(nn.Tensor.from_numpy(synth.normal(21, "bad", (10, 50))))
+    assert e.value.variant == "ShapeMismatch"
+    empty = nn.Sequential()
+    assert len(empty) == 0 and np.array_equal(empty(nn.Tensor.from_numpy(x)).numpy(), x)
