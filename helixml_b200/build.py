@@ -36,8 +36,8 @@ def _stale(target: str, deps) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def _compile(src: str, obj: str, verbose: bool) -> str:
-    cmd = ["nvcc", *NVCC_FLAGS, "-c", src, "-o", obj]
+def _compile(src: str, obj: str, verbose: bool, defines=()) -> str:
+    cmd = ["nvcc", *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     r = subprocess.run(cmd, capture_output=True, text=True)
@@ -46,7 +46,7 @@ def _compile(src: str, obj: str, verbose: bool) -> str:
     return r.stderr if verbose else ""
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, defines=()) -> str:
     os.makedirs(OBJ, exist_ok=True)
     srcs = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     hdrs = _headers()
@@ -59,7 +59,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
             jobs.append((s, o))
     if jobs:
         with cf.ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
-            for out in ex.map(lambda so: _compile(so[0], so[1], verbose), jobs):
+            for out in ex.map(lambda so: _compile(so[0], so[1], verbose, defines), jobs):
                 if out:
                     print(out, file=sys.stderr)
     if force or jobs or _stale(LIB, objs):
@@ -75,5 +75,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--define", action="append", default=[], help="NAME=VALUE passed to nvcc as -D (tuning macros of the kernels)")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.define))

@@ -7,6 +7,15 @@
 
 #include "hx_common.cuh"
 
+// 1: HX_SCAN_AUTO lets the one-pass scan compute the dt projection itself; 0: a dt_proj kernel of its own.
+// Measured over the 24 blocks of the byte LM at 32 x 2048 x 1536: fused 12.5 ms; unfused 10.2 ms of scan + 1.5 ms of
+// dt_proj (the unfused kernel holds 32 KB of shared memory against 65 KB, so a chain's next segment is resident
+// and prefetched when its predecessor ends, and it gains from the larger register budget where the fused one does
+// not).  HX_SCAN_DIRECT / HX_SCAN_LOOKBACK as explicit variants still fuse.
+#ifndef HX_BLOCK_FUSE_DT_AUTO
+#define HX_BLOCK_FUSE_DT_AUTO 0
+#endif
+
 namespace hx {
 namespace block {
 
@@ -83,7 +92,7 @@ static bool fuses_dt(const hx_mamba_block_args *a, int W, int splits) {
     // time, 12.9 against 11.5 + 1.5 ms over 24 blocks at 32 x 2048 x 1536, and the fused form moves 0.4 GB less).  The look-back form has CTAs to spare and lives on occupancy: with
     // the projection's weight and fp32 dt tiles in shared memory 3 CTAs fit an SM, without them 7, and measured at
     // 4 to 16 rows of 2048 x 1536 the unfused form with a dt_proj GEMM of its own is the faster one.
-    return hx::scan::auto_kind(&sa) == hx::scan::ScanKind::Direct;
+    return HX_BLOCK_FUSE_DT_AUTO && hx::scan::auto_kind(&sa) == hx::scan::ScanKind::Direct;
 }
 
 }  // namespace block

@@ -31,6 +31,22 @@
 //           with outputs like MODE 0.
 #pragma once
 
+// Tuning macros (python -m helixml_b200.build --define NAME=VALUE).
+// Second argument of __launch_bounds__ for the one-pass / chained kernels and for the look-back passes (0 = none).
+// With 1 the compiler schedules for the registers of a single resident CTA and uses about 100 instead of 70: the
+// unfused one-pass kernel gets 10 % faster (455 -> 409 us at 49 152 chains, 3 to 4 CTAs still fit an SM); the
+// look-back passes, which live on occupancy, are best left alone (a budget for 5 or 6 CTAs per SM spills and is
+// 2-5 % slower).
+#ifndef HX_SCAN_MINB_CHAINED
+#define HX_SCAN_MINB_CHAINED 1
+#endif
+#ifndef HX_SCAN_UNROLL
+#define HX_SCAN_UNROLL 8
+#endif
+#ifndef HX_SCAN_MINB_LOOKBACK
+#define HX_SCAN_MINB_LOOKBACK 0
+#endif
+
 namespace hx {
 namespace scan {
 
@@ -57,6 +73,9 @@ struct DirectCfg {
     static constexpr int NB = NWARP / WPB;             // boxes per CTA
     static constexpr int DT = NB * BOXC;               // channels per CTA
     static constexpr int THREADS = (NWARP + 1) * 32;
+    // second argument of __launch_bounds__ (0 = none): the register budget the compiler schedules for
+    static constexpr int UNROLL = HX_SCAN_UNROLL;
+    static constexpr int MIN_CTAS = (MODE_ != 0 && !FUSEDT_) ? HX_SCAN_MINB_LOOKBACK : HX_SCAN_MINB_CHAINED;
     static constexpr int X_BYTES = (TC + 3) * 128;
     static constexpr int ROW_BYTES = TC * 128;
     static constexpr int DTROW = FUSEDT ? BOXC * 4 + 32 : 128;            // bytes per dt row (fp32 + pad when produced here:
@@ -89,7 +108,7 @@ template <> __device__ __forceinline__ float ld_chan1<__nv_bfloat16>(const char 
 }
 
 template <typename T, typename Cfg>
-__global__ void __launch_bounds__(Cfg::THREADS)
+__global__ void __launch_bounds__(Cfg::THREADS, Cfg::MIN_CTAS)
 scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_dt,
                    const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_B,
                    const __grid_constant__ CUtensorMap tm_C, const __grid_constant__ CUtensorMap tm_dtlow,
@@ -507,7 +526,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         }
 
 // unrolled by 8: 4 is 10 % slower, 16 no faster (measured at 49 152 chains)
-#pragma unroll 8
+#pragma unroll(Cfg::UNROLL)
         for (int t = 0; t < steps; ++t) {
             float xc[CPL], dr[CPL], zr[CPL];
             if constexpr (CPL == 2) {

@@ -957,12 +957,15 @@ static hx_status launch_lookback_pair(const TiledParams &p, const CUtensorMap *m
     return launch_direct_inst<T, 1, true, STD, 2, FUSEDT, false, BLOCK, 2>(p, maps, grid, st, y, y_bs, y_rs);
 }
 
+#ifndef HX_SCAN_CPL2_MIN_WARPS
+#define HX_SCAN_CPL2_MIN_WARPS 8.0
+#endif
 // channels per lane for the direct kernel: 2 when that still leaves about two warps per scheduler
 static int choose_cpl(const hx_scan_args *a) {
     if (a->io_dtype != HX_BF16) return 1;
     if (a->reserved % 10 == 1 || a->reserved % 10 == 2) return a->reserved % 10;
     const double chains = (double)a->batch * a->d_inner;
-    return chains / 64.0 >= 8.0 * sm_count() ? 2 : 1;
+    return chains / 64.0 >= HX_SCAN_CPL2_MIN_WARPS * sm_count() ? 2 : 1;
 }
 
 // What the look-back form supports: geometric A, and where the dt projection is fused the block's configuration.
