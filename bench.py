@@ -68,7 +68,7 @@ def measured_peaks():
 # otherwise `traffic` is null (a run cannot measure it: ncu is not part of a timed run).
 NCU_TRAFFIC = {
     ("lm_cfg3", "scan_direct_kernel (chained segments, dt projection inside)"):
-        {"bytes": 608_549_120, "capture": "ncu --set full, one launch inside the 24-block step: 413.6 MB read + 194.9 MB written"},
+        {"bytes": 608_478_976, "capture": "ncu --set full, one launch inside the 24-block step: 413.7 MB read + 194.8 MB written"},
     ("scan_cfg2", "scan_tiled_kernel"):
         {"bytes": 791_900_000, "capture": "ncu --set full, one launch: 608.9 MB read + 182.9 MB written"},
 }
@@ -630,7 +630,7 @@ def run_lm(args, cfg, name):
         elif per_block == 8:
             scan_kernel = "scan_direct_kernel (look-back: aggregate pass + output pass), dt_proj GEMM before it"
         else:
-            scan_kernel = "selective scan (one launch), dt_proj GEMM before it"
+            scan_kernel = "scan_direct_kernel (chained segments), dt_proj kernel before it"
         traffic, traffic_src = ncu_traffic(name, scan_kernel) if world == 1 else (None, "single-GPU captures only")
         # the scan is the largest single stage (and the top entry of the ncu launch list); the GEMMs, five
         # shapes of one kernel, are reported beside it under "gemm"
@@ -639,7 +639,8 @@ def run_lm(args, cfg, name):
             roof = {"bound": "hbm", "kernel": scan_kernel, "achieved": scan_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": scan_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
                     "algorithmic_bytes_per_launch": scan_bytes, "launch_ms": scan_ms, "traffic": traffic, "traffic_source": traffic_src,
-                    "note": "per call of the scan stage (all its launches); algorithmic bytes are those of the unfused operation"}
+                    "note": "per call of the scan stage (all its launches, the dt_proj kernel not included); algorithmic "
+                            "bytes are those of the selective scan: u, dt, z read, y written, B and C read once"}
         else:
             roof = {"bound": "tensor", "kernel": "gemm_tc_kernel (all projections)", "achieved": gemm_tflops,
                     "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": gemm_tflops / peaks["bf16_tflops_sustained"],

@@ -3,7 +3,8 @@
 // 128 x 256 tcgen05 tile kernel, whose main loop is a single k-block here, spends its time in the epilogue
 // (87 us for 65 536 x 1536 x 48 against 31 us of stores at the measured copy bandwidth).
 //
-// A CTA owns RT row tiles of 16 rows and all N columns.  Its A rows ([RT * 16, K], a few KB) are staged in shared
+// A CTA owns RT row tiles of 16 rows (2 to 8, chosen so that the grid is a whole number of waves) and all N
+// columns.  Its A rows ([RT * 16, K], a few KB) are staged in shared
 // memory once.  A warp takes blocks of 64 columns: it loads the W fragments of the block into registers once
 // (8 column tiles x K / 16 k-steps x 2 registers), then runs over the CTA's row tiles with mma.sync.m16n8k16
 // (bf16 in, fp32 accumulate), rounds the 16 x 64 result to bf16 into a small per-warp staging tile and writes it
@@ -15,13 +16,15 @@ namespace gemm {
 
 constexpr int kLowkWarps = 8;
 
-template <int KS, int RT>  // KS: k-steps of 16 (K <= 16 KS); RT: row tiles of 16 per CTA
+constexpr int kLowkMaxRowTiles = 8;
+
+template <int KS>  // KS: k-steps of 16 (K <= 16 KS); RT: row tiles of 16 per CTA (<= kLowkMaxRowTiles)
 __global__ void __launch_bounds__(kLowkWarps * 32)
 gemm_lowk_kernel(const __nv_bfloat16 *__restrict__ A, int64_t lda, const __nv_bfloat16 *__restrict__ W, int64_t ldw,
-                 __nv_bfloat16 *__restrict__ C, int64_t ldc, int M, int N, int K) {
+                 __nv_bfloat16 *__restrict__ C, int64_t ldc, int M, int N, int K, int RT) {
     constexpr int AK = KS * 16 + 8;              // A row pitch in elements: the pad spreads the fragment loads over the banks
     constexpr int SP = 64 + 8;                   // staging row pitch
-    __shared__ __align__(16) __nv_bfloat16 sA[RT * 16 * AK];
+    __shared__ __align__(16) __nv_bfloat16 sA[kLowkMaxRowTiles * 16 * AK];
     __shared__ __align__(16) __nv_bfloat16 sOut[kLowkWarps][16 * SP];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tid = lane & 3;
     const int m0 = blockIdx.x * RT * 16;
@@ -99,19 +102,23 @@ hx_status launch_lowk(const void *A, int64_t lda, const void *W, int64_t ldw, vo
     auto a = static_cast<const __nv_bfloat16 *>(A), w = static_cast<const __nv_bfloat16 *>(W);
     auto c = static_cast<__nv_bfloat16 *>(C);
     const int ks = (K + 15) / 16;
-    // 128 rows per CTA when that still gives every SM a few CTAs, 32 rows otherwise
-    const bool big = (M + 127) / 128 >= 2 * sm_count();
-#define HX_LOWK(KS)                                                                                                          \
-    do {                                                                                                                     \
-        if (big) gemm_lowk_kernel<KS, 8><<<(unsigned)((M + 127) / 128), kLowkWarps * 32, 0, st>>>(a, lda, w, ldw, c, ldc, M, N, K); \
-        else gemm_lowk_kernel<KS, 2><<<(unsigned)((M + 31) / 32), kLowkWarps * 32, 0, st>>>(a, lda, w, ldw, c, ldc, M, N, K);       \
-        return check_launch("gemm_lowk_kernel");                                                                             \
-    } while (0)
-    if (ks == 1) HX_LOWK(1);
-    if (ks == 2) HX_LOWK(2);
-    if (ks == 3) HX_LOWK(3);
-    HX_LOWK(4);
-#undef HX_LOWK
+    // Row tiles per CTA: the kernel is bound by its stores and two CTAs fit an SM, so the grid should be a whole
+    // number of waves of 2 x SMs CTAs; among 2 .. 8 tiles take the count with the least waves x tiles.
+    const int slots = 2 * sm_count();
+    int rt = 2;
+    long best = -1;
+    for (int r = 2; r <= kLowkMaxRowTiles; ++r) {
+        const long ctas = ((long)M + 16 * r - 1) / (16 * r);
+        const long cost = ((ctas + slots - 1) / slots) * r;
+        if (best < 0 || cost < best || (cost == best && r > rt)) { best = cost; rt = r; }
+    }
+    const unsigned grid = (unsigned)(((long)M + 16 * rt - 1) / (16 * rt));
+    const dim3 block(kLowkWarps * 32);
+    if (ks == 1) gemm_lowk_kernel<1><<<grid, block, 0, st>>>(a, lda, w, ldw, c, ldc, M, N, K, rt);
+    else if (ks == 2) gemm_lowk_kernel<2><<<grid, block, 0, st>>>(a, lda, w, ldw, c, ldc, M, N, K, rt);
+    else if (ks == 3) gemm_lowk_kernel<3><<<grid, block, 0, st>>>(a, lda, w, ldw, c, ldc, M, N, K, rt);
+    else gemm_lowk_kernel<4><<<grid, block, 0, st>>>(a, lda, w, ldw, c, ldc, M, N, K, rt);
+    return check_launch("gemm_lowk_kernel");
 }
 
 }  // namespace gemm

@@ -264,7 +264,7 @@ def _per_position_worst(got, ref):
 
 def test_mamba_block_full_size_config3_shape_sampled_rows():
     """One block at the benchmark's shape, [32, 2048, 768] bf16: the path the byte LM times (tensor-core GEMMs, the
-    one-lane-per-channel scan with the dt projection inside and chained sequence segments).  Batch rows are
+    dt projection as a kernel of its own, the one-lane-per-channel scan with chained sequence segments).  Batch rows are
     independent, so the oracle runs on the first and the last row; the gate is applied to the rows as a whole and
     to every position by itself (a lost carry would spoil the positions after one segment boundary)."""
     import torch
@@ -283,7 +283,7 @@ def test_mamba_block_full_size_config3_shape_sampled_rows():
     a.W_dt = dev["W_dt"].data_ptr()
     n = C.c_int32(0)
     _lib.check(_lib.lib().hx_mamba_block_kernel_launches(C.byref(a), C.byref(n)))
-    assert n.value == 5  # in_proj, conv, x_proj, scan with the dt projection inside, out_proj
+    assert n.value == 6  # in_proj, conv, x_proj, dt_proj, scan (one pass, chained segments), out_proj
     rows = [0, B - 1]
     ref = cbind.mamba_block(x[rows], wq, 16, 4)
     g = got[rows].float().cpu().numpy()
@@ -294,7 +294,8 @@ def test_mamba_block_full_size_config3_shape_sampled_rows():
 def test_byte_lm_full_size_config3_sampled_sequences():
     """Benchmark configuration 3 at full size: 24 blocks, d_model 768, batch 32 x 2048 bytes, bf16 -- the very call
     bench.py times.  The logits of the first and the last sequence are compared with the CPU oracle of the whole
-    model (rows are independent); the launch count shows that every block ran the fused-dt scan."""
+    model (rows are independent); the launch count shows that every block ran the one-pass scan after a dt_proj
+    kernel (the look-back form would be one launch more, the fused dt projection one less)."""
     import torch
     from helixml_b200 import _lib, nn
     nl, M, B, L = 24, 768, 32, 2048
@@ -309,7 +310,7 @@ def test_byte_lm_full_size_config3_sampled_sequences():
     logits = torch.empty((B, L, 256), dtype=torch.bfloat16, device="cuda")
     lm.forward_device(tok_d.data_ptr(), logits.data_ptr(), B, L, torch.cuda.current_stream().cuda_stream)
     _lib.check_device()
-    assert lm.launches_per_forward == 1 + nl * 6 + 2  # norm + 5 kernels per block: the dt projection is in the scan
+    assert lm.launches_per_forward == 1 + nl * 7 + 2  # norm, in_proj, conv, x_proj, dt_proj, scan, out_proj per block
     rows = [0, B - 1]
     ref = cbind.byte_lm(tok[rows], emb_q, layers_q, normf, 16, 4)
     g = logits[rows].float().cpu().numpy()
