@@ -813,7 +813,7 @@ def main():
     ap.add_argument("--shard", default="auto", choices=["auto", "none", "channels"],
                     help="auto: configuration 4 is sharded by channels when N > 1")
     ap.add_argument("--no-gather", action="store_true", help="channel shard: skip the all-gather of y")
-    ap.add_argument("--gather-groups", type=int, default=2, help="row groups whose pushes overlap the next group's scan")
+    ap.add_argument("--gather-groups", type=int, default=1, help="row groups whose pushes overlap the next group's scan")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="lm workloads: plain launches instead of the replayed CUDA graph of the forward")
