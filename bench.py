@@ -67,8 +67,13 @@ def measured_peaks():
 # capture of this workload.  A figure is reported only while the kernel that ran is the kernel that was captured;
 # otherwise `traffic` is null (a run cannot measure it: ncu is not part of a timed run).
 NCU_TRAFFIC = {
+    ("lm_cfg3", "scan_direct_kernel (chained segments), dt_proj kernel before it"):
+        {"bytes": 816_670_720, "capture": "ncu --set full, one launch inside the 24-block step: 614.7 MB read + 201.9 MB written"},
     ("lm_cfg3", "scan_direct_kernel (chained segments, dt projection inside)"):
         {"bytes": 608_478_976, "capture": "ncu --set full, one launch inside the 24-block step: 413.7 MB read + 194.8 MB written"},
+    ("scan_cfg2", "scan_direct_kernel (look-back: aggregate pass + output pass)"):
+        {"bytes": 1_108_681_472, "capture": "ncu --set full, both launches of one call: 304.2 + 4.6 MB (aggregate pass) and "
+                                            "617.2 + 182.7 MB (output pass)"},
     ("scan_cfg2", "scan_tiled_kernel"):
         {"bytes": 791_900_000, "capture": "ncu --set full, one launch: 608.9 MB read + 182.9 MB written"},
 }
@@ -790,12 +795,24 @@ def run_kernels(args, name):
         # the reference's own criterion shapes (benches/src/neural_networks.rs:11-51): S4Block::new(512, 64) and
         # MambaBlock::new(512, 64, 4, 2) forward on [seq, 512], seq 64 / 128 / 256, f32.  There the S4 forward is
         # input.clone() and the Mamba forward out_proj(silu(gate(x))); here they are the real recurrences.
+        # Module::forward returns a finished tensor (it allocates its result and synchronises), so these are host
+        # wall-clock times per call, as criterion measures them.
+        def wall(fn):
+            for _ in range(warm):
+                fn()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                fn()
+            torch.cuda.synchronize()
+            return (time.perf_counter() - t0) / reps * 1e3
+
+        s4 = nn.S4Block(512, 64)
+        mb = nn.MambaBlock(512, 64, 4, 2, nn.Device.cuda(0))
         for seq in (64, 128, 256):
             x = nn.Tensor.from_numpy(synth.normal(1, f"x{seq}", (seq, 512)))
-            s4 = nn.S4Block(512, 64)
-            mb = nn.MambaBlock(512, 64, 4, 2, nn.Device.cuda(0))
-            emit(f"S4Block(512, 64).forward [{seq}, 512]", timed(lambda: s4.forward(x)))
-            emit(f"MambaBlock(512, 64, 4, 2).forward [{seq}, 512]", timed(lambda: mb.forward(x)))
+            emit(f"S4Block(512, 64).forward [{seq}, 512]", wall(lambda: s4.forward(x)), timing="host wall clock per call")
+            emit(f"MambaBlock(512, 64, 4, 2).forward [{seq}, 512]", wall(lambda: mb.forward(x)), timing="host wall clock per call")
     assert _lib.device_status() == 0
 
 
