@@ -622,12 +622,18 @@ def run_lm(args, cfg, name):
         scan_bytes = scan_algorithmic_bytes(B, L, E, N, 0)
         scan_ms = stage_ms["scan"] / cfg["n_layer"]
         scan_gbs = scan_bytes / (scan_ms * 1e-3) / 1e9
-        gemm_ms = sum(stage_ms[k] for k in ("in_proj", "x_proj", "dt_proj", "out_proj", "lm_head"))
-        gemm_tflops = lm_flops_per_token(cfg) * B * L / (gemm_ms * 1e-3) / 1e12
+        # the tensor-core (tcgen05) projections; dt_proj is counted with them only while it runs as one of them
+        fused_dt = stage_ms["dt_proj"] < 0.008 * cfg["n_layer"]
+        dt_is_tile_gemm = False  # K = dt_rank <= 64 goes to the store-shaped kernel, reported on its own below
+        gemm_keys = ("in_proj", "x_proj", "out_proj", "lm_head") + (("dt_proj",) if dt_is_tile_gemm else ())
+        gemm_ms = sum(stage_ms[k] for k in gemm_keys)
+        M_, E_ = cfg["d_model"], cfg["d_model"] * cfg["expand"]
+        dt_flops_tok = cfg["n_layer"] * 2 * ((M_ + 15) // 16) * E_
+        gemm_tflops = (lm_flops_per_token(cfg) - dt_flops_tok) * B * L / (gemm_ms * 1e-3) / 1e12
         # launches per block beyond norm + in_proj + conv + x_proj + out_proj: 1 = one-pass scan with the dt
         # projection inside, 2 = look-back scan (aggregate pass + output pass), or dt_proj GEMM + scan
         per_block = (launches - 3) // cfg["n_layer"]
-        fused = stage_ms["dt_proj"] < 0.008 * cfg["n_layer"]   # only the event marks: no GEMM ran in that stage
+        fused = fused_dt   # only the event marks: no kernel ran in that stage
         if fused and per_block == 6:
             scan_kernel = "scan_direct_kernel (chained segments, dt projection inside)"
         elif fused:
@@ -640,6 +646,7 @@ def run_lm(args, cfg, name):
         # the scan is the largest single stage (and the top entry of the ncu launch list); the GEMMs, five
         # shapes of one kernel, are reported beside it under "gemm"
         dominant_scan = stage_ms["scan"] >= max(stage_ms[k] for k in ("in_proj", "x_proj", "dt_proj", "out_proj", "lm_head"))
+        dt_bytes = B * L * E_ * 2
         if dominant_scan:
             roof = {"bound": "hbm", "kernel": scan_kernel, "achieved": scan_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": scan_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
@@ -667,7 +674,12 @@ def run_lm(args, cfg, name):
             "scan": {"gbs": scan_gbs, "frac_of_hbm_peak": scan_gbs / peaks["hbm_gbs"], "ms_per_launch": scan_ms,
                      "compute_roof": scan_compute_roof(B * L * E, N, 0, scan_bytes, peaks["hbm_gbs"], pipe_rates(),
                                                        scan_ms)},
-            "gemm": {"tflops": gemm_tflops, "frac_of_sustained_peak": gemm_tflops / peaks["bf16_tflops_sustained"], "ms_total": gemm_ms},
+            "gemm": {"tflops": gemm_tflops, "frac_of_sustained_peak": gemm_tflops / peaks["bf16_tflops_sustained"], "ms_total": gemm_ms,
+                     "covers": "in_proj, x_proj, out_proj, tied head (tcgen05 kernels)"},
+            "dt_proj": None if fused_dt else {"kernel": "gemm_lowk_kernel (K = dt_rank: bound by writing its result)",
+                                              "ms_total": stage_ms["dt_proj"],
+                                              "store_gbs": dt_bytes * cfg["n_layer"] / (stage_ms["dt_proj"] * 1e-3) / 1e9,
+                                              "frac_of_hbm_peak": dt_bytes * cfg["n_layer"] / (stage_ms["dt_proj"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
             "forward_as": "plain launches" if args.no_graph else "one CUDA graph replay per step (captured on the second call)",
             "parity_checked": parity,
             "cpu_baseline": cpu, "cpu_baseline_1core": cpu1, "e2e": e2e, "gpu_launches": args.steps * launches, "clocks": clocks,
