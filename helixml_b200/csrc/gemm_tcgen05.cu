@@ -16,6 +16,7 @@
 // Every wait is bounded; a wait that runs out raises the per-device status word, the CTA drains,
 // frees its tensor memory and returns.
 #include <atomic>
+#include <cstdlib>
 #include "gemm.cuh"
 #include "hx_tma.cuh"
 
@@ -26,6 +27,9 @@ namespace gemm {
 __device__ int g_gemm_status = 0;
 constexpr int kWaitGemm = 32;
 constexpr int BM = 128, BK = 64;
+#ifndef HX_GEMM_PAIR_DEFAULT
+#define HX_GEMM_PAIR_DEFAULT 1
+#endif
 
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     for (int i = 0; i < kMaxTries; ++i) {
@@ -77,24 +81,69 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-template <int BN> struct TcCfg {
-    static constexpr int STAGES = BN == 256 ? 4 : 6;
+// ---- CTA pairs (PAIR = 1): two CTAs of a cluster share one [256 x BN] tile.  Each CTA loads its own 128 rows of A
+// and HALF of the W tile (BN/2 rows); the leader (cluster rank 0) issues tcgen05.mma.cta_group::2 (M = 256), which
+// reads both CTAs' shared memory at the same offsets and leaves rows r*128.. of the tile in CTA r's tensor memory.
+// Per FLOP a CTA pulls two thirds of the operand bytes of the single-CTA form, and the ring holds six stages.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into this CTA's shared memory whose completion is counted on a barrier of either CTA of the pair
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *m, uint32_t bar_cluster, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(c0), "r"(c1), "r"(bar_cluster)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrives on ONE barrier (of either CTA, by its shared::cluster address) when the pair's MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
+}
+
+template <int BN, int PAIR = 0> struct TcCfg {
+    static constexpr int STAGES = PAIR ? 6 : (BN == 256 ? 4 : 6);
     static constexpr int A_BYTES = BM * BK * 2;
-    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int B_ROWS = PAIR ? BN / 2 : BN;   // W rows this CTA loads per stage
+    static constexpr int B_BYTES = B_ROWS * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int TMEM_COLS = 2 * BN;
     static constexpr int OUT_STAGE_BYTES = 32 * 128;  // one epilogue warp's [32 rows x 128 bytes] staging tile
-    static constexpr int OUT_BYTES = 4 * 2 * OUT_STAGE_BYTES;
+    static constexpr int OUT_BUFS = 2;                // staging tiles per epilogue warp (more of them change nothing)
+    static constexpr int OUT_BYTES = 4 * OUT_BUFS * OUT_STAGE_BYTES;
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + OUT_BYTES + 256 + 1024;
+    static_assert(SMEM_BYTES <= 232448, "more shared memory than a CTA can have");
+    static_assert((2 * STAGES + 4) * 8 + 8 <= 256, "barrier block too small");
     static constexpr int THREADS = 192;
 };
 
-template <int BN, typename TC, int EPI>
-__global__ void __launch_bounds__(192, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
-               const __grid_constant__ CUtensorMap tm_c, const float *bias, TC *C, int64_t ldc, int M, int N, int K, int epi_col0,
-               int vec_ok) {
-    using Cfg = TcCfg<BN>;
+template <int BN, typename TC, int EPI, int PAIR>
+__device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tm_a, const CUtensorMap &tm_w, const CUtensorMap &tm_c,
+                                             const float *bias, TC *C, int64_t ldc, int M, int N, int K, int epi_col0,
+                                             int vec_ok) {
+    using Cfg = TcCfg<BN, PAIR>;
+    constexpr int TILE_M = PAIR ? 2 * BM : BM;   // rows of C one tile covers (both CTAs of a pair)
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ __align__(16) char smem_raw[];
     char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);  // keeps the shared address space
@@ -110,9 +159,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     auto bar_acc_empty = [&](int a) { return bar0 + 8u * (2 * STAGES + 2 + a); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int num_m = (M + BM - 1) / BM, num_n = (N + BN - 1) / BN;
+    const int num_m = (M + TILE_M - 1) / TILE_M, num_n = (N + BN - 1) / BN;
     const int tiles = num_m * num_n;
     const int kblocks = (K + BK - 1) / BK;
+    // a pair walks the tile list together: cluster i is CTAs 2i and 2i+1
+    const uint32_t crank = PAIR ? cluster_ctarank() : 0u;
+    const int tile0 = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -121,16 +174,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_acc_full(a), 1);
-            mbar_init(bar_acc_empty(a), 4);
+            mbar_init(bar_acc_empty(a), PAIR ? 8 : 4);   // the leader's barrier also counts the peer's epilogue warps
         }
         *abort_flag = 0;
         mbar_fence_init();
     }
+    if constexpr (PAIR) {
+        // the peer is running and its barriers are initialised before anything is allocated or signalled across
+        __syncthreads();
+        cluster_sync_all();
+    }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"((uint32_t)Cfg::TMEM_COLS)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (PAIR) {
+            // one warp of EACH CTA of the pair performs the allocation (and, below, the release) together
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -144,26 +210,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             tma_prefetch_desc(&tm_w);
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                const int m0 = (tile / num_n) * BM, n0 = (tile % num_n) * BN;
+            for (int tile = tile0; tile < tiles && ok; tile += tile_step) {
+                const int m0 = (tile / num_n) * TILE_M + (int)crank * BM, n0 = (tile % num_n) * BN + (int)crank * Cfg::B_ROWS;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!wait_or_abort(bar_empty(s), ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
                     const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    mbar_expect_tx(bar_full(s), Cfg::STAGE_BYTES);
-                    tma_load_2d(sa, &tm_a, bar_full(s), kb * BK, m0);
-                    tma_load_2d(sa + Cfg::A_BYTES, &tm_w, bar_full(s), kb * BK, n0);
+                    if constexpr (PAIR) {
+                        // both CTAs' bytes are counted on the LEADER's full barrier, which its MMA lane waits on
+                        const uint32_t full_leader = map_to_cta(bar_full(s), 0);
+                        if (crank == 0) mbar_expect_tx(bar_full(s), 2 * Cfg::STAGE_BYTES);
+                        tma_load_2d_pair(sa, &tm_a, full_leader, kb * BK, m0);
+                        tma_load_2d_pair(sa + Cfg::A_BYTES, &tm_w, full_leader, kb * BK, n0);
+                    } else {
+                        mbar_expect_tx(bar_full(s), Cfg::STAGE_BYTES);
+                        tma_load_2d(sa, &tm_a, bar_full(s), kb * BK, m0);
+                        tma_load_2d(sa + Cfg::A_BYTES, &tm_w, bar_full(s), kb * BK, n0);
+                    }
                 }
             }
         }
     } else if (warp == 1) {
         // ============================================================ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && crank == 0) {   // in a pair only the leader issues
             constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                                       ((uint32_t)(BM >> 4) << 24);
+                                       ((uint32_t)(TILE_M >> 4) << 24);
             int it = 0, tc = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tc) {
+            for (int tile = tile0; tile < tiles && ok; tile += tile_step, ++tc) {
                 const int acc = tc & 1;
                 if (!wait_or_abort(bar_acc_empty(acc), ((tc >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after();
@@ -174,12 +248,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
                     const uint64_t da = make_smem_desc(sa), db = make_smem_desc(sa + Cfg::A_BYTES);
+                    if constexpr (PAIR) {
 #pragma unroll
-                    for (int k = 0; k < BK / 16; ++k)
-                        umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
-                    umma_commit(bar_empty(s));  // the stage is free once these MMAs have read it
+                        for (int k = 0; k < BK / 16; ++k)
+                            umma_bf16_pair(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+                        umma_commit_pair(map_to_cta(bar_empty(s), 0));  // the stage is free in both CTAs once these
+                        umma_commit_pair(map_to_cta(bar_empty(s), 1));  // MMAs have read it
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < BK / 16; ++k)
+                            umma_bf16(d_tmem, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
+                        umma_commit(bar_empty(s));  // the stage is free once these MMAs have read it
+                    }
                 }
-                if (ok) umma_commit(bar_acc_full(acc));
+                if (ok) {
+                    if constexpr (PAIR) {
+                        umma_commit_pair(map_to_cta(bar_acc_full(acc), 0));
+                        umma_commit_pair(map_to_cta(bar_acc_full(acc), 1));
+                    } else {
+                        umma_commit(bar_acc_full(acc));
+                    }
+                }
             }
         }
     } else {
@@ -187,9 +276,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
         const int wq = warp & 3;  // TMEM lane quarter this warp may read
         int tc = 0, sc = 0;       // tiles done; staged blocks issued (selects the staging buffer)
         bool ok = true;
-        for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++tc) {
+        for (int tile = tile0; tile < tiles && ok; tile += tile_step, ++tc) {
             const int acc = tc & 1;
-            const int m0 = (tile / num_n) * BM, n0 = (tile % num_n) * BN;
+            const int m0 = (tile / num_n) * TILE_M + (int)crank * BM, n0 = (tile % num_n) * BN;
             if (!wait_or_abort(bar_acc_full(acc), (tc >> 1) & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const int m = m0 + wq * 32 + lane;
@@ -197,12 +286,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                 // Coalesced path: 128 bytes of each of the warp's 32 rows go to a swizzled staging tile and
                 // leave with one TMA store; out-of-range rows and columns are clipped by the tensor map.
                 constexpr int CPB = 128 / (int)sizeof(TC);  // columns per staged block: 64 bf16 / 32 fp32
-                char *my_stage = out_stage + (warp - 2) * 2 * Cfg::OUT_STAGE_BYTES;
+                char *my_stage = out_stage + (warp - 2) * Cfg::OUT_BUFS * Cfg::OUT_STAGE_BYTES;
 #pragma unroll 1
                 for (int cb = 0; cb < BN / CPB; ++cb) {
                     const int nb = n0 + cb * CPB;
                     if (nb >= N) break;  // warp-uniform
-                    char *buf = my_stage + (sc & 1) * Cfg::OUT_STAGE_BYTES;
+                    char *buf = my_stage + (sc % Cfg::OUT_BUFS) * Cfg::OUT_STAGE_BYTES;
                     ++sc;
                     // both halves of the block are fetched from tensor memory before anything waits
                     constexpr int HALVES = CPB / 32;
@@ -210,7 +299,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
 #pragma unroll
                     for (int half = 0; half < HALVES; ++half)
                         tmem_ld32(tmem_base + acc * BN + cb * CPB + half * 32 + ((uint32_t)(wq * 32) << 16), r[half]);
-                    if (lane == 0) tma_store_wait_read<1>();  // the store that last read this buffer is done
+                    if (lane == 0) tma_store_wait_read<Cfg::OUT_BUFS - 1>();  // the store that last read this buffer is done
                     tmem_ld_wait();
                     __syncwarp();
 #pragma unroll
@@ -252,8 +341,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        if constexpr (EPI == kEpiAccumulate) tma_reduce_add_2d(&tm_c, smem_u32(buf), nb, m0 + wq * 32);
-                        else tma_store_2d(&tm_c, smem_u32(buf), nb, m0 + wq * 32);
+                        if (m0 + wq * 32 < M) {   // a box that starts below the last row has nothing to write
+                            if constexpr (EPI == kEpiAccumulate) tma_reduce_add_2d(&tm_c, smem_u32(buf), nb, m0 + wq * 32);
+                            else tma_store_2d(&tm_c, smem_u32(buf), nb, m0 + wq * 32);
+                        }
                         tma_store_commit();
                     }
                 }
@@ -281,7 +372,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_acc_empty(acc));
+            if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(map_to_cta(bar_acc_empty(acc), 0));
+                else mbar_arrive(bar_acc_empty(acc));
+            }
         }
         if (lane == 0) tma_store_wait_all<0>();  // staging tiles must outlive their TMA stores
     }
@@ -289,11 +383,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__
     // teardown: everybody meets, then the allocating warp frees tensor memory
     tc_fence_before();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();   // the peer no longer reads tensor memory or signals this CTA's barriers
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
-                     : "memory");
+        if constexpr (PAIR)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
     }
+    if constexpr (PAIR) {
+        __syncthreads();
+        cluster_sync_all();   // neither CTA leaves while the other still releases tensor memory
+    }
+}
+
+template <int BN, typename TC, int EPI>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+               const __grid_constant__ CUtensorMap tm_c, const float *bias, TC *C, int64_t ldc, int M, int N, int K, int epi_col0,
+               int vec_ok) {
+    gemm_tc_body<BN, TC, EPI, 0>(tm_a, tm_w, tm_c, bias, C, ldc, M, N, K, epi_col0, vec_ok);
+}
+
+// The same kernel run by CTA pairs: grid = 2 x pairs, cluster (2, 1, 1).
+template <int BN, typename TC, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+                    const __grid_constant__ CUtensorMap tm_c, const float *bias, TC *C, int64_t ldc, int M, int N, int K,
+                    int epi_col0, int vec_ok) {
+    gemm_tc_body<BN, TC, EPI, 1>(tm_a, tm_w, tm_c, bias, C, ldc, M, N, K, epi_col0, vec_ok);
 }
 
 template <int BN, typename TC, int EPI>
@@ -312,6 +432,61 @@ static hx_status launch_tc_inst(const CUtensorMap &ma, const CUtensorMap &mw, co
     const int grid = tiles < sm_count() ? tiles : sm_count();
     kern<<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(ma, mw, mc, bias, static_cast<TC *>(C), ldc, M, N, K, epi_col0, vec_ok);
     return check_launch("gemm_tc_kernel");
+}
+
+// How many CTA pairs of the pair kernel can be resident at once on the current device (0: pairs cannot be used).
+template <int BN, typename TC, int EPI> static int pair_capacity() {
+    using Cfg = TcCfg<BN, 1>;
+    static std::atomic<int> cap[64];   // 0 = not asked yet, -1 = unusable, else pairs
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    int c = cap[dev].load(std::memory_order_acquire);
+    if (c == 0) {
+        auto kern = gemm_tc_pair_kernel<BN, TC, EPI>;
+        c = -1;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) == cudaSuccess) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2 * sm_count());
+            cfg.blockDim = dim3(Cfg::THREADS);
+            cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+            cudaLaunchAttribute at;
+            at.id = cudaLaunchAttributeClusterDimension;
+            at.val.clusterDim.x = 2;
+            at.val.clusterDim.y = 1;
+            at.val.clusterDim.z = 1;
+            cfg.attrs = &at;
+            cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) c = n;
+        }
+        (void)cudaGetLastError();
+        cap[dev].store(c, std::memory_order_release);
+    }
+    return c > 0 ? c : 0;
+}
+
+template <int BN, typename TC, int EPI>
+static hx_status launch_tc_pair_inst(const CUtensorMap &ma, const CUtensorMap &mw, const CUtensorMap &mc, const float *bias,
+                                     void *C, int64_t ldc, int M, int N, int K, int epi_col0, int pairs, cudaStream_t st) {
+    using Cfg = TcCfg<BN, 1>;
+    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    const int grid = 2 * (tiles < pairs ? tiles : pairs);
+    gemm_tc_pair_kernel<BN, TC, EPI><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>(ma, mw, mc, bias, static_cast<TC *>(C), ldc, M,
+                                                                                 N, K, epi_col0, 1);
+    return check_launch("gemm_tc_pair_kernel");
+}
+
+// 0: single CTAs only; 1: CTA pairs where they measured faster; 2: wherever the shape allows.  HX_GEMM_PAIR in the
+// environment sets the initial mode.
+static std::atomic<int> g_pair_mode{-1};   // -1: not set through hx_gemm_pair_mode
+static int pair_mode() {
+    const int m = g_pair_mode.load(std::memory_order_relaxed);
+    if (m >= 0) return m;
+    static const int mode = [] {
+        const char *e = getenv("HX_GEMM_PAIR");
+        return e ? atoi(e) : HX_GEMM_PAIR_DEFAULT;
+    }();
+    return mode;
 }
 
 template <int BN, typename TC>
@@ -341,6 +516,12 @@ hx_status read_status_gemm(int *v, bool clear) {
 }
 
 }  // namespace hx
+
+extern "C" hx_status hx_gemm_pair_mode(int32_t mode, int32_t *pairs) {
+    if (mode >= 0) hx::gemm::g_pair_mode.store(mode > 2 ? 2 : mode, std::memory_order_relaxed);
+    if (pairs) *pairs = hx::gemm::pair_capacity<256, __nv_bfloat16, hx::gemm::kEpiNone>();
+    return HX_OK;
+}
 
 extern "C" hx_status hx_gemm_bf16(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias, void *C,
                                   int64_t ldc, int32_t c_dtype, int32_t M, int32_t N, int32_t K, int32_t epilogue,
@@ -377,7 +558,16 @@ extern "C" hx_status hx_gemm_bf16_cols(const void *A, int64_t lda, const void *W
     if (K <= 64 && M > 64 && N % 8 == 0 && N >= 64 && c_dtype == HX_BF16 && bias == nullptr && epilogue == kEpiNone &&
         (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * 2) % 16 == 0)
         return launch_lowk(A, lda, W, ldw, C, ldc, M, N, K, st);
-    const int BN = N > 128 ? 256 : 128;
+    // tile width: 256 columns, or 128 where N is small or where the narrower tiles fill the last wave so much better
+    // that it outweighs their lower arithmetic intensity (a few thousand rows: 8192 x 768 is 192 wide tiles = 2 waves
+    // of 148, but 384 narrow ones = 3 half-cost waves)
+    int BN = N > 128 ? 256 : 128;
+    if (BN == 256) {
+        const int sms = hx::sm_count();
+        const int64_t mt = (M + BM - 1) / BM;
+        const int64_t w256 = (mt * ((N + 255) / 256) + sms - 1) / sms, w128 = (mt * ((N + 127) / 128) + sms - 1) / sms;
+        if ((double)w128 * 0.55 < (double)w256 * 0.95) BN = 128;
+    }
     CUtensorMap ma, mw;
     const uint64_t dims_a[2] = {(uint64_t)K, (uint64_t)M}, dims_w[2] = {(uint64_t)K, (uint64_t)N};
     const uint64_t str_a[1] = {(uint64_t)lda * 2}, str_w[1] = {(uint64_t)ldw * 2};
@@ -393,6 +583,28 @@ extern "C" hx_status hx_gemm_bf16_cols(const void *A, int64_t lda, const void *W
         const uint64_t str_c[1] = {(uint64_t)ldc * es};
         const uint32_t box_c[2] = {(uint32_t)(128 / es), 32};
         if ((s = hx::encode_tensor_map(&mc, c_dtype, 2, C, dims_c, str_c, box_c, true)) != HX_OK) return s;
+    }
+    // CTA pairs for the wide shapes: [256 x 256] tiles, each CTA loading 128 rows of the W tile.  Measured against
+    // single CTAs on a B200 (65 536 rows, sustained): equal within 2 % where C is written (K = 768: 257 against 253 us),
+    // 5-7 % faster for the accumulating epilogue at K = 1536 (142-145 against 150-152 us), slower for a few thousand
+    // rows; so mode 1 takes pairs for the accumulating epilogue on at least four waves of pair tiles, mode 2 wherever
+    // the shape allows.
+    const int pm = pair_mode();
+    if (BN == 256 && vec_ok && pm != 0 && M >= 4 * BM && (epilogue == kEpiNone || (epilogue == kEpiAccumulate && c_dtype == HX_F32))) {
+        const int64_t pair_tiles = (int64_t)((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+        int pairs = 0;
+        if (epilogue == kEpiAccumulate) pairs = pair_capacity<256, float, kEpiAccumulate>();
+        else if (pm >= 2) pairs = c_dtype == HX_BF16 ? pair_capacity<256, __nv_bfloat16, kEpiNone>() : pair_capacity<256, float, kEpiNone>();
+        if (pairs > 0 && (pm >= 2 || pair_tiles >= 4 * (int64_t)pairs)) {
+            CUtensorMap mwh;
+            const uint32_t box_wh[2] = {(uint32_t)BK, (uint32_t)(BN / 2)};
+            if ((s = hx::encode_tensor_map(&mwh, HX_BF16, 2, W, dims_w, str_w, box_wh, true)) != HX_OK) return s;
+            if (epilogue == kEpiAccumulate)
+                return launch_tc_pair_inst<256, float, kEpiAccumulate>(ma, mwh, mc, bias, C, ldc, M, N, K, epi_col0, pairs, st);
+            if (c_dtype == HX_BF16)
+                return launch_tc_pair_inst<256, __nv_bfloat16, kEpiNone>(ma, mwh, mc, bias, C, ldc, M, N, K, epi_col0, pairs, st);
+            return launch_tc_pair_inst<256, float, kEpiNone>(ma, mwh, mc, bias, C, ldc, M, N, K, epi_col0, pairs, st);
+        }
     }
     if (BN == 256) {
         if (c_dtype == HX_BF16) return launch_tc_epi<256, __nv_bfloat16>(ma, mw, mc, bias, C, ldc, M, N, K, vec_ok, epilogue, epi_col0, st);

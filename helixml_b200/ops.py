@@ -200,6 +200,15 @@ def gemm(a, w, bias=None, out_dtype=None, epilogue=L.EPI_NONE, tensor_cores=None
     return c
 
 
+def gemm_pair_mode(mode: int = -1) -> int:
+    """Tile form of the wide tensor-core shapes (hx_gemm_pair_mode): 0 single CTAs, 1 CTA pairs where they measured
+    faster (the default), 2 pairs wherever the shape allows; a negative mode only asks.  Returns how many CTA pairs
+    the current device holds at once (0: pairs unusable there)."""
+    n = C.c_int32(0)
+    L.check(L.lib().hx_gemm_pair_mode(mode, C.byref(n)))
+    return n.value
+
+
 def gemm_acc(a, w, c):
     """c += a @ w.T (hx_gemm_bf16_acc): a [M, K], w [N, K] bf16, c [M, N] fp32, updated in place."""
     M, K = a.shape

@@ -320,6 +320,15 @@ HX_API hx_status hx_gemm_bf16_cols(const void *A, int64_t lda, const void *W, in
  * reduce), so a block's out_proj can accumulate straight into the fp32 residual stream. */
 HX_API hx_status hx_gemm_bf16_acc(const void *A, int64_t lda, const void *W, int64_t ldw, float *C, int64_t ldc,
                            int32_t M, int32_t N, int32_t K, void *stream);
+/* Tile form of the tcgen05 kernel for wide shapes (N > 128, at least 512 rows, TMA-storable C, epilogue none or the
+ * accumulating one).  CTA pairs: two CTAs of a thread-block cluster share a [256 x 256] tile, each loads its 128 rows
+ * of A and HALF of the W tile, the leader issues tcgen05.mma.cta_group::2.  mode 0: one CTA per [128 x 256] tile
+ * always; 1 (the build's default): pairs where they measured faster (the accumulating epilogue on at least four
+ * waves of pair tiles); 2: pairs wherever the shape allows; a negative mode changes nothing.  *pairs (may be NULL)
+ * receives how many pairs the current device can hold at once (0: the pair kernel cannot be used there and single
+ * CTAs run whatever the mode).  Process-wide; HX_GEMM_PAIR in the environment sets the initial mode.  Results are
+ * bit-identical in every mode (each element is one k-ascending tensor-memory sum).  No counterpart in the reference. */
+HX_API hx_status hx_gemm_pair_mode(int32_t mode, int32_t *pairs);
 /* Same contract on CUDA cores in fp32 (any alignment, fp32 or bf16 operands): the small-shape and
  * fp32 path (the reference is fp32 throughout). */
 HX_API hx_status hx_gemm_simt(const void *A, int64_t lda, const void *W, int64_t ldw, const float *bias,

@@ -216,7 +216,8 @@ def test_gemm_activation_on_a_column_range(M):
     assert e.value.variant == "InvalidInput"
 
 
-@pytest.mark.parametrize("M,N,K", [(300, 768, 1536), (129, 136, 72), (4096, 256, 768), (40, 768, 64), (513, 80, 1536)])
+@pytest.mark.parametrize("M,N,K", [(300, 768, 1536), (129, 136, 72), (4096, 256, 768), (40, 768, 64), (513, 80, 1536),
+                                   (8192, 768, 256)])   # the last: narrow tiles chosen for a fuller last wave
 def test_gemm_accumulates_into_fp32(M, N, K):
     """C += A W^T: the epilogue adds its tiles into C (TMA reduce on the tensor-core path, plain read-modify-write
     on the few-rows and unaligned paths); twice in a row to see that nothing is overwritten."""
@@ -239,6 +240,38 @@ def test_gemm_accumulates_into_fp32(M, N, K):
     ops.gemm_acc(to_dev(a, "bf16"), to_dev(w, "bf16"), view)
     assert fp32_tol_err(to_np(view), c0 + prod) <= FP32_TOL
     assert float(wide[:, 0].abs().max()) == 0.0 and float(wide[:, N + 1:].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 256, 64), (1000, 3072, 768), (777, 768, 1536), (2178, 520, 200), (4096, 256, 768),
+                                   (20000, 768, 1536)])
+def test_gemm_cta_pairs_match_single_ctas(M, N, K):
+    """The CTA-pair form of the tensor-core kernel (tcgen05.mma.cta_group::2 on [256 x 256] tiles, each CTA loading
+    half of the W tile) against the oracle's Linear, and bit for bit against single CTAs: every element is the same
+    k-ascending sum in tensor memory, whichever CTA holds it.  Row counts that leave the second CTA of the last pair
+    partly or wholly out of range are among the cases."""
+    import torch
+    from helixml_b200 import ops
+    assert ops.gemm_pair_mode(-1) > 0, "the pair kernel cannot be resident on this device"
+    a = synth.round_bf16(synth.normal(66, "a", (M, K)))
+    w = synth.round_bf16(synth.normal(66, "w", (N, K), 0, 0.05))
+    c0 = synth.normal(66, "c", (M, N))
+    ad, wd = to_dev(a, "bf16"), to_dev(w, "bf16")
+    ref = a.astype(np.float64) @ w.astype(np.float64).T
+    got = {}
+    try:
+        for mode in (2, 0):
+            ops.gemm_pair_mode(mode)
+            c = to_dev(c0)
+            ops.gemm_acc(ad, wd, c)
+            got[mode] = (ops.gemm(ad, wd, out_dtype=torch.float32), ops.gemm(ad, wd), c)
+            _status_ok()
+    finally:
+        ops.gemm_pair_mode(1)
+    assert fp32_tol_err(to_np(got[2][0]), ref) <= FP32_TOL
+    assert rel_l2(to_np(got[2][1]), ref) <= 5e-3
+    assert fp32_tol_err(to_np(got[2][2]), c0 + ref) <= FP32_TOL
+    for x, y in zip(got[2], got[0]):
+        assert torch.equal(x, y)
 
 
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
