@@ -710,8 +710,10 @@ def run_reference_lm(args, cfg, name):
     print(json.dumps(line))
 
 
-GEMM_SHAPES = {"in_proj": (65536, 3072, 768), "out_proj": (65536, 768, 1536), "x_proj": (65536, 80, 1536),
-               "dt_proj": (65536, 1536, 48), "lm_head": (65536, 256, 768)}
+GEMM_SHAPES = {"in_proj": (65536, 3072, 768), "out_proj": (65536, 768, 1536), "out_proj_acc": (65536, 768, 1536),
+               "x_proj": (65536, 80, 1536), "dt_proj": (65536, 1536, 48), "lm_head": (65536, 256, 768),
+               "in_proj_8k": (8192, 3072, 768), "out_proj_acc_8k": (8192, 768, 1536),   # _8k, _16k: one GPU's share
+               "in_proj_16k": (16384, 3072, 768), "out_proj_acc_16k": (16384, 768, 1536)}  # of 8 and of 4
 
 
 def run_kernels(args, name):
@@ -746,11 +748,26 @@ def run_kernels(args, name):
             M, N, K = GEMM_SHAPES[case]
             a = (torch.randn(M, K, device="cuda") * 0.5).to(torch.bfloat16)
             w = (torch.randn(N, K, device="cuda") * 0.05).to(torch.bfloat16)
-            c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-            ms = timed(lambda: ops.gemm(a, w, out=c))
+            acc = "_acc" in case   # the block's out_proj: adds into an fp32 C
+            c = torch.zeros(M, N, device="cuda", dtype=torch.float32 if acc else torch.bfloat16)
+            call = (lambda: ops.gemm_acc(a, w, c)) if acc else (lambda: ops.gemm(a, w, out=c))
+            ms = timed(call)
+            if acc:
+                c.zero_()
+                call()
             err = (c[:256].float() - a[:256].float() @ w.float().t()).abs().max().item()
             tf = 2 * M * N * K / ms / 1e9
-            emit(case, ms, M=M, N=N, K=K, tflops=tf, frac_of_burst_peak=tf / peaks["bf16_tflops"], max_abs_err_256_rows=err)
+            extra = {}
+            if args.compare:
+                # the same shape with single CTAs only, with CTA pairs wherever allowed, and through the vendor library
+                # (torch.matmul, bf16 result): yardsticks, not paths of this repository
+                for label, mode in (("us_single_ctas", 0), ("us_cta_pairs", 2)):
+                    ops.gemm_pair_mode(mode)
+                    extra[label] = timed(call) * 1e3
+                ops.gemm_pair_mode(1)
+                cl, wt = torch.empty(M, N, device="cuda", dtype=torch.bfloat16), w.t()
+                extra["us_vendor_library_bf16_out"] = timed(lambda: torch.matmul(a, wt, out=cl)) * 1e3
+            emit(case, ms, M=M, N=N, K=K, tflops=tf, frac_of_burst_peak=tf / peaks["bf16_tflops"], max_abs_err_256_rows=err, **extra)
     elif name == "kernels_conv":
         B, L, E = 32, 2048, 1536
         xz = torch.randn(B, L, 2 * E, device="cuda").to(torch.bfloat16)
@@ -850,6 +867,8 @@ def main():
     ap.add_argument("--scaling", default="strong", choices=["strong", "weak"],
                     help="lm workloads at N > 1: one batch sharded by rows (strong) or the whole batch on every rank (weak)")
     ap.add_argument("cases", nargs="*", help="kernels_gemm: shapes to time (default all)")
+    ap.add_argument("--compare", action="store_true",
+                    help="kernels_gemm: also time single CTAs, CTA pairs and the vendor library's GEMM on each shape")
     ap.add_argument("--batch", type=int, default=0, help="override the workload's batch (to look at one GPU's share of a sharded batch)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]

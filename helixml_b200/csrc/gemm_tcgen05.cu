@@ -476,8 +476,8 @@ static hx_status launch_tc_pair_inst(const CUtensorMap &ma, const CUtensorMap &m
     return check_launch("gemm_tc_pair_kernel");
 }
 
-// 0: single CTAs only; 1: CTA pairs where they measured faster; 2: wherever the shape allows.  HX_GEMM_PAIR in the
-// environment sets the initial mode.
+// 0: single CTAs only; 1: CTA pairs where they measured faster; 2: pairs wherever the shape allows.
+// HX_GEMM_PAIR in the environment sets the initial mode.
 static std::atomic<int> g_pair_mode{-1};   // -1: not set through hx_gemm_pair_mode
 static int pair_mode() {
     const int m = g_pair_mode.load(std::memory_order_relaxed);
@@ -558,16 +558,7 @@ extern "C" hx_status hx_gemm_bf16_cols(const void *A, int64_t lda, const void *W
     if (K <= 64 && M > 64 && N % 8 == 0 && N >= 64 && c_dtype == HX_BF16 && bias == nullptr && epilogue == kEpiNone &&
         (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * 2) % 16 == 0)
         return launch_lowk(A, lda, W, ldw, C, ldc, M, N, K, st);
-    // tile width: 256 columns, or 128 where N is small or where the narrower tiles fill the last wave so much better
-    // that it outweighs their lower arithmetic intensity (a few thousand rows: 8192 x 768 is 192 wide tiles = 2 waves
-    // of 148, but 384 narrow ones = 3 half-cost waves)
-    int BN = N > 128 ? 256 : 128;
-    if (BN == 256) {
-        const int sms = hx::sm_count();
-        const int64_t mt = (M + BM - 1) / BM;
-        const int64_t w256 = (mt * ((N + 255) / 256) + sms - 1) / sms, w128 = (mt * ((N + 127) / 128) + sms - 1) / sms;
-        if ((double)w128 * 0.55 < (double)w256 * 0.95) BN = 128;
-    }
+    const int BN = N > 128 ? 256 : 128;
     CUtensorMap ma, mw;
     const uint64_t dims_a[2] = {(uint64_t)K, (uint64_t)M}, dims_w[2] = {(uint64_t)K, (uint64_t)N};
     const uint64_t str_a[1] = {(uint64_t)lda * 2}, str_w[1] = {(uint64_t)ldw * 2};
@@ -585,22 +576,24 @@ extern "C" hx_status hx_gemm_bf16_cols(const void *A, int64_t lda, const void *W
         if ((s = hx::encode_tensor_map(&mc, c_dtype, 2, C, dims_c, str_c, box_c, true)) != HX_OK) return s;
     }
     // CTA pairs for the wide shapes: [256 x 256] tiles, each CTA loading 128 rows of the W tile.  Measured against
-    // single CTAs on a B200 (65 536 rows, sustained): equal within 2 % where C is written (K = 768: 257 against 253 us),
-    // 5-7 % faster for the accumulating epilogue at K = 1536 (142-145 against 150-152 us), slower for a few thousand
-    // rows; so mode 1 takes pairs for the accumulating epilogue on at least four waves of pair tiles, mode 2 wherever
-    // the shape allows.
+    // single CTAs on a B200 (65 536 rows, sustained): equal within 2 % where C is written (K = 768: 253-257 against
+    // 248-253 us), 5-10 % faster for the accumulating epilogue at K = 1536 (134-145 against 145-152 us; 3.35 against
+    // 3.72 ms over the 24 blocks of the byte-LM step), slower below four waves of tiles.  [256 x 128] pair tiles
+    // were measured too and dropped (in_proj 388 us: the pair instruction does not speed up with the narrower N).
+    // Mode 1 therefore takes pairs for the accumulating epilogue on at least four waves of them, mode 2 wherever the
+    // shape allows.
     const int pm = pair_mode();
     if (BN == 256 && vec_ok && pm != 0 && M >= 4 * BM && (epilogue == kEpiNone || (epilogue == kEpiAccumulate && c_dtype == HX_F32))) {
+        const bool accum = epilogue == kEpiAccumulate;
         const int64_t pair_tiles = (int64_t)((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
         int pairs = 0;
-        if (epilogue == kEpiAccumulate) pairs = pair_capacity<256, float, kEpiAccumulate>();
+        if (accum) pairs = pair_capacity<256, float, kEpiAccumulate>();
         else if (pm >= 2) pairs = c_dtype == HX_BF16 ? pair_capacity<256, __nv_bfloat16, kEpiNone>() : pair_capacity<256, float, kEpiNone>();
         if (pairs > 0 && (pm >= 2 || pair_tiles >= 4 * (int64_t)pairs)) {
             CUtensorMap mwh;
             const uint32_t box_wh[2] = {(uint32_t)BK, (uint32_t)(BN / 2)};
             if ((s = hx::encode_tensor_map(&mwh, HX_BF16, 2, W, dims_w, str_w, box_wh, true)) != HX_OK) return s;
-            if (epilogue == kEpiAccumulate)
-                return launch_tc_pair_inst<256, float, kEpiAccumulate>(ma, mwh, mc, bias, C, ldc, M, N, K, epi_col0, pairs, st);
+            if (accum) return launch_tc_pair_inst<256, float, kEpiAccumulate>(ma, mwh, mc, bias, C, ldc, M, N, K, epi_col0, pairs, st);
             if (c_dtype == HX_BF16)
                 return launch_tc_pair_inst<256, __nv_bfloat16, kEpiNone>(ma, mwh, mc, bias, C, ldc, M, N, K, epi_col0, pairs, st);
             return launch_tc_pair_inst<256, float, kEpiNone>(ma, mwh, mc, bias, C, ldc, M, N, K, epi_col0, pairs, st);
