@@ -625,20 +625,24 @@ def run_lm(args, cfg, name):
         # the tensor-core (tcgen05) projections; dt_proj is counted with them only while it runs as one of them
         fused_dt = stage_ms["dt_proj"] < 0.008 * cfg["n_layer"]
         dt_is_tile_gemm = False  # K = dt_rank <= 64 goes to the store-shaped kernel, reported on its own below
-        gemm_keys = ("in_proj", "x_proj", "out_proj", "lm_head") + (("dt_proj",) if dt_is_tile_gemm else ())
+        fused_cx = stage_ms["x_proj"] < 0.008 * cfg["n_layer"]   # only the event marks: conv and x_proj were one kernel
+        gemm_keys = ("in_proj", "out_proj", "lm_head") + (() if fused_cx else ("x_proj",)) + (("dt_proj",) if dt_is_tile_gemm else ())
         gemm_ms = sum(stage_ms[k] for k in gemm_keys)
         M_, E_ = cfg["d_model"], cfg["d_model"] * cfg["expand"]
         dt_flops_tok = cfg["n_layer"] * 2 * ((M_ + 15) // 16) * E_
-        gemm_tflops = (lm_flops_per_token(cfg) - dt_flops_tok) * B * L / (gemm_ms * 1e-3) / 1e12
-        # launches per block beyond norm + in_proj + conv + x_proj + out_proj: 1 = one-pass scan with the dt
-        # projection inside, 2 = look-back scan (aggregate pass + output pass), or dt_proj GEMM + scan
+        xp_flops_tok = cfg["n_layer"] * 2 * E_ * ((M_ + 15) // 16 + 2 * cfg["d_state"]) if fused_cx else 0
+        gemm_tflops = (lm_flops_per_token(cfg) - dt_flops_tok - xp_flops_tok) * B * L / (gemm_ms * 1e-3) / 1e12
+        # launches per block beyond norm, in_proj, conv (+ x_proj in the same kernel, or a GEMM of its own) and
+        # out_proj: 1 = one-pass scan with the dt projection inside; 2 = dt_proj kernel + one-pass scan, or look-back
+        # scan (aggregate pass + output pass) with the dt projection inside; 3 = dt_proj kernel + look-back scan
         per_block = (launches - 3) // cfg["n_layer"]
+        scan_launches = per_block - 4 - (0 if fused_cx else 1)
         fused = fused_dt   # only the event marks: no kernel ran in that stage
-        if fused and per_block == 6:
+        if fused and scan_launches == 1:
             scan_kernel = "scan_direct_kernel (chained segments, dt projection inside)"
         elif fused:
             scan_kernel = "scan_direct_kernel (look-back: aggregate pass + output pass, dt projection inside)"
-        elif per_block == 8:
+        elif scan_launches == 3:
             scan_kernel = "scan_direct_kernel (look-back: aggregate pass + output pass), dt_proj GEMM before it"
         else:
             scan_kernel = "scan_direct_kernel (chained segments), dt_proj kernel before it"
@@ -675,11 +679,12 @@ def run_lm(args, cfg, name):
                      "compute_roof": scan_compute_roof(B * L * E, N, 0, scan_bytes, peaks["hbm_gbs"], pipe_rates(),
                                                        scan_ms)},
             "gemm": {"tflops": gemm_tflops, "frac_of_sustained_peak": gemm_tflops / peaks["bf16_tflops_sustained"], "ms_total": gemm_ms,
-                     "covers": "in_proj, x_proj, out_proj, tied head (tcgen05 kernels)"},
+                     "covers": "in_proj, out_proj, tied head" + ("" if fused_cx else ", x_proj") + " (tcgen05 kernels)"},
             "dt_proj": None if fused_dt else {"kernel": "gemm_lowk_kernel (K = dt_rank: bound by writing its result)",
                                               "ms_total": stage_ms["dt_proj"],
                                               "store_gbs": dt_bytes * cfg["n_layer"] / (stage_ms["dt_proj"] * 1e-3) / 1e9,
                                               "frac_of_hbm_peak": dt_bytes * cfg["n_layer"] / (stage_ms["dt_proj"] * 1e-3) / 1e9 / peaks["hbm_gbs"]},
+            "conv_x_proj": "one kernel (conv_xproj_kernel; its time is under conv_silu)" if fused_cx else "conv kernel + GEMM",
             "forward_as": "plain launches" if args.no_graph else "one CUDA graph replay per step (captured on the second call)",
             "parity_checked": parity,
             "cpu_baseline": cpu, "cpu_baseline_1core": cpu1, "e2e": e2e, "gpu_launches": args.steps * launches, "clocks": clocks,

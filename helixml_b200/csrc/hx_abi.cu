@@ -128,11 +128,12 @@ hx_status hx_memset(void *dptr, int value, size_t bytes, void *stream) {
 hx_status hx_device_status(int32_t *status, int32_t clear) {
     HX_REQUIRE(status != nullptr, HX_ERR_INVALID_INPUT, "hx_device_status: status is NULL");
     HX_CUDA(cudaDeviceSynchronize());
-    int a = 0, b = 0;
+    int a = 0, b = 0, c = 0;
     hx_status s = hx::read_status_scan(&a, clear != 0);
     if (s != HX_OK) return s;
     if ((s = hx::read_status_gemm(&b, clear != 0)) != HX_OK) return s;
-    *status = a | b;
+    if ((s = hx::read_status_convx(&c, clear != 0)) != HX_OK) return s;
+    *status = a | b | c;
     return HX_OK;
 }
 
@@ -142,9 +143,9 @@ hx_status hx_device_check(void) {
     if (s != HX_OK) return s;
     if (st == 0) return HX_OK;
     return hx::fail(HX_ERR_BACKEND,
-                    "a bounded device-side wait ran out (status 0x%x:%s%s%s%s%s%s); outputs since the last check are not valid", st,
+                    "a bounded device-side wait ran out (status 0x%x:%s%s%s%s%s%s%s); outputs since the last check are not valid", st,
                     (st & 1) ? " tile load" : "", (st & 2) ? " stage release" : "", (st & 4) ? " output tile" : "",
-                    (st & 8) ? " output release" : "", (st & 16) ? " segment carry" : "", (st & 32) ? " GEMM pipeline" : "");
+                    (st & 8) ? " output release" : "", (st & 16) ? " segment carry" : "", (st & 32) ? " GEMM pipeline" : "", (st & 64) ? " conv + x_proj pipeline" : "");
 }
 
 hx_status hx_stream_synchronize(void *stream) {

@@ -56,6 +56,7 @@ ScanKind auto_kind(const hx_scan_args *a);
 // optionally clear) them.  hx_device_status() ORs them together.
 hx_status read_status_scan(int *v, bool clear);
 hx_status read_status_gemm(int *v, bool clear);
+hx_status read_status_convx(int *v, bool clear);
 
 // ---------------------------------------------------------------- device-side helpers
 template <typename T> __device__ __forceinline__ float ld_f32(const T *p);

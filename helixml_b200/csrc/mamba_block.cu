@@ -15,6 +15,10 @@
 #ifndef HX_BLOCK_FUSE_DT_AUTO
 #define HX_BLOCK_FUSE_DT_AUTO 0
 #endif
+// 1: conv + SiLU and x_proj as one kernel where its conditions hold; 0: always two kernels.
+#ifndef HX_BLOCK_FUSE_CONV_XPROJ
+#define HX_BLOCK_FUSE_CONV_XPROJ 1
+#endif
 
 namespace hx {
 namespace block {
@@ -95,6 +99,19 @@ static bool fuses_dt(const hx_mamba_block_args *a, int W, int splits) {
     return HX_BLOCK_FUSE_DT_AUTO && hx::scan::auto_kind(&sa) == hx::scan::ScanKind::Direct;
 }
 
+// True when conv + SiLU and x_proj run as one kernel (hx_conv1d_silu_xproj_fwd's conditions on the block's buffers;
+// the workspace slices are 256-byte aligned).
+static bool fuses_conv_xproj(const hx_mamba_block_args *a, int W) {
+#if HX_BLOCK_FUSE_CONV_XPROJ
+    auto al16 = [](const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    return a->io_dtype == HX_BF16 && a->d_conv == 4 && a->d_inner % 64 == 0 && W % 8 == 0 && W <= 256 && al16(a->conv_w) &&
+           (!a->conv_b || al16(a->conv_b)) && al16(a->W_x);
+#else
+    (void)a; (void)W;
+    return false;
+#endif
+}
+
 }  // namespace block
 }  // namespace hx
 
@@ -112,7 +129,7 @@ hx_status hx_mamba_block_kernel_launches(const hx_mamba_block_args *a, int32_t *
     HX_REQUIRE(launches != nullptr, HX_ERR_INVALID_INPUT, "launches is NULL");
     hx_status s = hx::block::validate(a);
     if (s != HX_OK) return s;
-    // in_proj, conv, x_proj, dt_proj (unless fused into the scan), scan, out_proj
+    // in_proj, conv, x_proj (one kernel with the conv where it can be), dt_proj (unless fused into the scan), scan, out_proj
     if (a->batch == 0 || a->seq_len == 0) {
         *launches = 0;
         return HX_OK;
@@ -125,7 +142,7 @@ hx_status hx_mamba_block_kernel_launches(const hx_mamba_block_args *a, int32_t *
     const bool lookback = l.splits > 1 && a->d_state == 16 &&
                           (a->scan_variant == HX_SCAN_LOOKBACK ||
                            (a->scan_variant == HX_SCAN_AUTO && hx::scan::auto_kind(&sa) == hx::scan::ScanKind::LookBack));
-    *launches = (fused ? 5 : 6) + (lookback ? 1 : 0);
+    *launches = (fused ? 5 : 6) + (lookback ? 1 : 0) - (hx::block::fuses_conv_xproj(a, (int)l.W) ? 1 : 0);
     return HX_OK;
 }
 
@@ -176,12 +193,22 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
         return s;
     mark(1);
     // 2. u = silu(conv(xs)), xs = xz[:, :E]            [T, E]
-    if ((s = hx_conv1d_silu_fwd(xz, (int64_t)a->seq_len * 2 * E, 2 * E, a->conv_w, a->conv_b, u, (int64_t)a->seq_len * E,
-                                E, a->batch, a->seq_len, E, a->d_conv, a->io_dtype, stream)) != HX_OK)
-        return s;
-    mark(2);
     // 3. [dt_low | B | C] = u W_x^T                     [T, R + 2N]
-    if ((s = gemm(u, E, a->W_x, E, dbc, W, (int)T, W, E)) != HX_OK) return s;
+    // One kernel does both where it can (the conv's tile of u is the tensor core's A operand, so u is not read
+    // back); otherwise the conv kernel and a GEMM.
+    if (fuses_conv_xproj(a, W)) {
+        if ((s = hx_conv1d_silu_xproj_fwd(xz, (int64_t)a->seq_len * 2 * E, 2 * E, a->conv_w, a->conv_b, a->W_x, E, u,
+                                          (int64_t)a->seq_len * E, E, dbc, W, a->batch, a->seq_len, E, a->d_conv, W,
+                                          a->io_dtype, stream)) != HX_OK)
+            return s;
+        mark(2);
+    } else {
+        if ((s = hx_conv1d_silu_fwd(xz, (int64_t)a->seq_len * 2 * E, 2 * E, a->conv_w, a->conv_b, u, (int64_t)a->seq_len * E,
+                                    E, a->batch, a->seq_len, E, a->d_conv, a->io_dtype, stream)) != HX_OK)
+            return s;
+        mark(2);
+        if ((s = gemm(u, E, a->W_x, E, dbc, W, (int)T, W, E)) != HX_OK) return s;
+    }
     mark(3);
     // 4. dt_lin = dt_low W_dt^T                          [T, E]   (bias and softplus happen inside the scan)
     // With bf16 operands and enough chains for the one-lane-per-channel scan, the projection is done inside the

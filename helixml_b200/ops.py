@@ -154,6 +154,23 @@ def conv1d_silu(x, conv_w, conv_b=None, out=None):
     return u
 
 
+def conv1d_silu_xproj(x, conv_w, conv_b, w_x, out_u=None, out_xdbl=None):
+    """u = silu(conv(x)) and x_dbl = u @ w_x.T in one kernel (hx_conv1d_silu_xproj_fwd): x [B, L, E] bf16 (a strided
+    half of the in_proj output is fine), conv_w [E, 4] fp32, w_x [n_out, E] bf16.  Returns (u, x_dbl [B, L, n_out]);
+    raises UnsupportedOperation for shapes the fused kernel does not take."""
+    Bsz, Lq, Dm = x.shape
+    n_out = w_x.shape[0]
+    u = out_u if out_u is not None else torch.empty((Bsz, Lq, Dm), dtype=x.dtype, device=x.device)
+    xd = out_xdbl if out_xdbl is not None else torch.empty((Bsz, Lq, n_out), dtype=x.dtype, device=x.device)
+    xb, xr = _view3(x)
+    ub, ur = _view3(u)
+    if not xd.is_contiguous():
+        raise L.HxError(1, "x_dbl must be contiguous")
+    L.check(L.lib().hx_conv1d_silu_xproj_fwd(_p(x), xb, xr, _p(_f32(conv_w)), _p(_f32(conv_b)), _p(w_x), w_x.stride(0), _p(u), ub,
+                                             ur, _p(xd), n_out, Bsz, Lq, Dm, conv_w.shape[1], n_out, _dt(x), _stream()))
+    return u, xd
+
+
 def s4_diag(u, A, Bp, Cp, delta, D=None):
     Bsz, Lq, Dm = u.shape
     u = u.contiguous()

@@ -264,6 +264,20 @@ HX_API hx_status hx_conv1d_silu_fwd(const void *x, int64_t x_batch_stride, int64
                              int32_t seq_len, int32_t d_inner, int32_t d_conv, int32_t io_dtype,
                              void *stream);
 
+/* The conv + SiLU above and the x_proj product that follows it in a Mamba block, in one kernel (bf16):
+ *   u = silu(conv(x)) [batch, seq_len, d_inner];  x_dbl[b*seq_len + t, 0:n_out] = u[b,t,:] . W_x^T, W_x [n_out, d_inner]
+ * (nn::ssm::MambaBlock::conv1d + silu + x_proj, crates/nn/src/ssm.rs:467-471 and the x_proj Linear of forward_mamba).
+ * The tile of u the conv produces in shared memory is the tensor core's A operand, so u is written once for the scan
+ * and not read back.  Takes bf16, d_conv 4, d_inner a multiple of 64, n_out a multiple of 8 up to 256, conv_w / conv_b
+ * / x_dbl 16-byte aligned, x_dbl_row_stride (elements) a multiple of 8, x / u / W_x meeting the TMA rules (16-byte
+ * aligned bases and row strides); anything else returns HX_ERR_UNSUPPORTED_OPERATION and the caller runs
+ * hx_conv1d_silu_fwd and hx_gemm_bf16.  u equals hx_conv1d_silu_fwd's bit for bit. */
+HX_API hx_status hx_conv1d_silu_xproj_fwd(const void *x, int64_t x_batch_stride, int64_t x_row_stride,
+                                   const float *conv_w, const float *conv_b, const void *W_x, int64_t ldw,
+                                   void *u, int64_t u_batch_stride, int64_t u_row_stride, void *x_dbl,
+                                   int64_t x_dbl_row_stride, int32_t batch, int32_t seq_len, int32_t d_inner,
+                                   int32_t d_conv, int32_t n_out, int32_t io_dtype, void *stream);
+
 /* ---- diagonal S4 recurrence, one (abar, bbar, C) triple per (channel, state):
  *   h_t = exp(delta[d] A[d,n]) h_{t-1} + delta[d] Bp[d,n] u[b,t,d];  y = sum_n Cp[d,n] h_t[n] + Dskip[d] u.
  * Stands in for nn::ssm::S4Block::forward_ssm + discretize (crates/nn/src/ssm.rs:103-186) in the

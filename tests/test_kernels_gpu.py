@@ -79,6 +79,52 @@ def test_conv1d_silu(dtype, B, L, D, K):
         assert fp32_tol_err(to_np(got), ref) <= FP32_TOL
 
 
+@pytest.mark.parametrize("B,L,E,NO", [(1, 128, 64, 16), (2, 300, 128, 80), (1, 5, 64, 40), (3, 1000, 1536, 80), (1, 257, 256, 256),
+                                      (2, 131, 192, 8)])
+def test_conv_silu_and_x_proj_in_one_kernel(B, L, E, NO):
+    """hx_conv1d_silu_xproj_fwd (the conv's tile of u is the tensor core's A operand) against the oracle's conv + SiLU
+    and Linear, with x a strided half of a wider buffer as in the block; u must equal the conv kernel's bit for bit.
+    Sequence lengths that are not multiples of the 128-step tile and output widths that are not multiples of 16 are
+    among the cases."""
+    import torch
+    from helixml_b200 import ops
+    xz = synth.round_bf16(synth.normal(67, "xz", (B, L, 2 * E)))
+    cw = synth.uniform(67, "cw", (E, 4), -0.5, 0.5)
+    cb = synth.normal(67, "cb", (E,), 0, 0.1)
+    wx = synth.round_bf16(synth.normal(67, "wx", (NO, E), 0, 0.05))
+    xz_d = to_dev(xz, "bf16")
+    x_d = xz_d[:, :, :E]
+    u = torch.full((B, L, E), 7.0, device="cuda", dtype=torch.bfloat16)
+    xd = torch.full((B, L, NO), 7.0, device="cuda", dtype=torch.bfloat16)
+    ops.conv1d_silu_xproj(x_d, to_dev(cw), to_dev(cb), to_dev(wx, "bf16"), out_u=u, out_xdbl=xd)
+    _status_ok()
+    u_ref = cbind.conv_silu(np.ascontiguousarray(xz[:, :, :E]), cw, cb)
+    assert rel_l2(to_np(u), u_ref) <= BF16_TOL
+    u_sep = ops.conv1d_silu(x_d, to_dev(cw), to_dev(cb))
+    assert torch.equal(u, u_sep)
+    # x_dbl from the bf16 u the kernel itself produced: fp32 accumulation leaves only the output rounding
+    ub = to_np(u).astype(np.float64).reshape(B * L, E)
+    ref = (ub @ wx.astype(np.float64).T).reshape(B, L, NO)
+    assert rel_l2(to_np(xd), ref) <= 5e-3
+    # without a bias
+    u2, xd2 = ops.conv1d_silu_xproj(x_d, to_dev(cw), None, to_dev(wx, "bf16"))
+    _status_ok()
+    assert torch.equal(u2, ops.conv1d_silu(x_d, to_dev(cw), None))
+
+
+def test_conv_silu_and_x_proj_rejects_what_it_does_not_take():
+    import torch
+    from helixml_b200 import _lib, ops
+    x = torch.zeros(1, 16, 96, device="cuda", dtype=torch.bfloat16)   # d_inner not a multiple of 64
+    with pytest.raises(_lib.HxError) as e:
+        ops.conv1d_silu_xproj(x, torch.zeros(96, 4, device="cuda"), None, torch.zeros(16, 96, device="cuda", dtype=torch.bfloat16))
+    assert e.value.variant == "UnsupportedOperation"
+    x = torch.zeros(1, 16, 64, device="cuda", dtype=torch.bfloat16)   # three taps
+    with pytest.raises(_lib.HxError) as e:
+        ops.conv1d_silu_xproj(x, torch.zeros(64, 3, device="cuda"), None, torch.zeros(16, 64, device="cuda", dtype=torch.bfloat16))
+    assert e.value.variant == "UnsupportedOperation"
+
+
 def test_rmsnorm_and_residual():
     import torch
     from helixml_b200 import ops
