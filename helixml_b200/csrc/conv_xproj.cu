@@ -5,7 +5,8 @@
 // block of the byte LM); here the tile of u the conv produces in shared memory IS the GEMM's A operand, so u is
 // written once (the scan reads it) and never read back.
 //
-// One CTA per 128 consecutive steps of one sequence, all channels, walked in blocks of 64 channels:
+// One CTA per 128 consecutive steps of one sequence (64 where that leaves SMs idle), all channels, walked in blocks
+// of 64 channels:
 //   warp 0      TMA producer: [131 steps x 64 channels] boxes of x (3 steps of history in front; steps before the
 //               sequence start are zero-filled by TMA, which is the conv's causal padding) and [n_out x 64] boxes
 //               of W_x (128-byte swizzle), each in a small ring.
@@ -34,14 +35,9 @@ using namespace hx::tc;
 __device__ int g_cx_status = 0;
 constexpr int kWaitConvX = 64;
 
-#ifndef HX_CX_TM
-#define HX_CX_TM 128
-#endif
-constexpr int TM = HX_CX_TM;       // steps per CTA: 64 or 128.  The MMA is always M = 128; with 64 steps its upper 64
-                                   // rows read whatever follows the tile in shared memory and their results are dropped
-constexpr int MMA_M = 128;
 constexpr int KC = 64;             // channels per block (128 bytes of bf16: one swizzle row)
 constexpr int HALO = 3;            // history steps of a 4-tap causal conv
+constexpr int MMA_M = 128;
 #ifndef HX_CX_XS
 #define HX_CX_XS 3
 #endif
@@ -53,24 +49,25 @@ constexpr int HALO = 3;            // history steps of a 4-tap causal conv
 #endif
 constexpr int XS = HX_CX_XS, WS = HX_CX_WS;   // ring depths of the x boxes and the W_x boxes
 constexpr int AB = HX_CX_AB;                   // u tiles: one being written, the others read by the MMA / the store
-constexpr int A_BYTES = TM * KC * 2;
-constexpr int X_BOX_ROWS = TM + HALO;
-constexpr int X_BOX_BYTES = X_BOX_ROWS * KC * 2;
-constexpr int X_STAGE_BYTES = (X_BOX_BYTES + 127) / 128 * 128;
 constexpr int COMPUTE_THREADS = 256;
-constexpr int ROWS_PER_THREAD = TM / (COMPUTE_THREADS / 32);
-
-#ifndef HX_CX_CTAS
-#define HX_CX_CTAS 2
-#endif
-constexpr int CTAS_PER_SM = HX_CX_CTAS;
-static_assert(TM == 64 || TM == 128, "64 or 128 steps per CTA");
 constexpr int THREADS = 64 + COMPUTE_THREADS;
 constexpr int NBARS = 2 * XS + 2 * WS + 2 * AB + 1;
 
+// TM = steps per CTA: 128, or 64 where 128-step tiles would leave SMs without a CTA.  The MMA is always M = 128; with
+// 64 steps its upper 64 rows read whatever follows the tile in shared memory and their results are dropped.
+template <int TM> struct Cfg {
+    static_assert(TM == 64 || TM == 128, "64 or 128 steps per CTA");
+    static constexpr int A_BYTES = TM * KC * 2;
+    static constexpr int X_BOX_ROWS = TM + HALO;
+    static constexpr int X_BOX_BYTES = X_BOX_ROWS * KC * 2;
+    static constexpr int X_STAGE_BYTES = (X_BOX_BYTES + 127) / 128 * 128;
+    static constexpr int ROWS_PER_THREAD = TM / (COMPUTE_THREADS / 32);
+    static constexpr int CTAS_PER_SM = TM == 64 ? 3 : 2;
+};
+
 __host__ __device__ constexpr int w_stage_bytes(int n_out) { return (n_out * KC * 2 + 1023) / 1024 * 1024; }
-__host__ __device__ constexpr int smem_bytes(int n_out) {
-    return AB * A_BYTES + WS * w_stage_bytes(n_out) + XS * X_STAGE_BYTES + 256 + 1024;
+template <int TM> __host__ __device__ constexpr int smem_bytes(int n_out) {
+    return AB * Cfg<TM>::A_BYTES + WS * w_stage_bytes(n_out) + XS * Cfg<TM>::X_STAGE_BYTES + 256 + 1024;
 }
 
 __device__ __forceinline__ bool wait_or_abort(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
@@ -96,11 +93,14 @@ __device__ __forceinline__ bool compute_sync_or(bool v) {
     return r != 0;
 }
 
-__global__ void __launch_bounds__(THREADS, CTAS_PER_SM)
+template <int TM>
+__global__ void __launch_bounds__(THREADS, Cfg<TM>::CTAS_PER_SM)
 conv_xproj_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w,
                   const __grid_constant__ CUtensorMap tm_u, const float *__restrict__ cw, const float *__restrict__ cb,
                   __nv_bfloat16 *__restrict__ xd, int64_t ldxd, int L, int E, int n_out, int n_mma, int tiles_per_seq,
                   uint32_t tmem_cols) {
+    constexpr int A_BYTES = Cfg<TM>::A_BYTES, X_BOX_BYTES = Cfg<TM>::X_BOX_BYTES, X_STAGE_BYTES = Cfg<TM>::X_STAGE_BYTES;
+    constexpr int ROWS_PER_THREAD = Cfg<TM>::ROWS_PER_THREAD;
     extern __shared__ __align__(16) char smem_raw[];
     char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     const int wbytes = w_stage_bytes(n_mma);   // n_mma: n_out rounded up to the MMA's multiple of 16 (rows >= n_out are zero)
@@ -299,6 +299,47 @@ hx_status read_status_convx(int *v, bool clear) {
 
 }  // namespace hx
 
+namespace hx {
+namespace cx {
+
+template <int TM>
+static hx_status launch(const void *x, int64_t x_batch_stride, int64_t x_row_stride, const float *conv_w, const float *conv_b,
+                        const void *W_x, int64_t ldw, void *u, int64_t u_batch_stride, int64_t u_row_stride, void *x_dbl,
+                        int64_t x_dbl_row_stride, int batch, int seq_len, int d_inner, int n_out, cudaStream_t st) {
+    CUtensorMap mx, mw, mu;
+    hx_status s;
+    const uint64_t dims_x[3] = {(uint64_t)d_inner, (uint64_t)seq_len, (uint64_t)batch};
+    const uint64_t str_x[2] = {(uint64_t)x_row_stride * 2, (uint64_t)x_batch_stride * 2};
+    const uint32_t box_x[3] = {(uint32_t)KC, (uint32_t)Cfg<TM>::X_BOX_ROWS, 1};
+    if ((s = encode_tensor_map(&mx, HX_BF16, 3, x, dims_x, str_x, box_x, false)) != HX_OK) return s;
+    const int n_mma = (n_out + 15) / 16 * 16;   // W_x rows past n_out are out of range for TMA and read as zeros
+    const uint64_t dims_w[2] = {(uint64_t)d_inner, (uint64_t)n_out};
+    const uint64_t str_w[1] = {(uint64_t)ldw * 2};
+    const uint32_t box_w[2] = {(uint32_t)KC, (uint32_t)n_mma};
+    if ((s = encode_tensor_map(&mw, HX_BF16, 2, W_x, dims_w, str_w, box_w, true)) != HX_OK) return s;
+    const uint64_t str_u[2] = {(uint64_t)u_row_stride * 2, (uint64_t)u_batch_stride * 2};
+    const uint32_t box_u[3] = {(uint32_t)KC, (uint32_t)TM, 1};
+    if ((s = encode_tensor_map(&mu, HX_BF16, 3, u, dims_x, str_u, box_u, true)) != HX_OK) return s;
+    const int smem = smem_bytes<TM>(n_mma);
+    static std::atomic<int> attr_set[64];  // largest size the attribute was set to, per device
+    int dev = 0;
+    HX_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && attr_set[dev].load(std::memory_order_acquire) < smem) {
+        HX_CUDA(cudaFuncSetAttribute(conv_xproj_kernel<TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_set[dev].store(smem, std::memory_order_release);
+    }
+    uint32_t cols = 32;
+    while ((int)cols < n_mma) cols *= 2;
+    const int tiles_per_seq = (seq_len + TM - 1) / TM;
+    conv_xproj_kernel<TM><<<batch * tiles_per_seq, THREADS, smem, st>>>(mx, mw, mu, conv_w, conv_b, static_cast<__nv_bfloat16 *>(x_dbl),
+                                                                       x_dbl_row_stride, seq_len, d_inner, n_out, n_mma,
+                                                                       tiles_per_seq, cols);
+    return check_launch("conv_xproj_kernel");
+}
+
+}  // namespace cx
+}  // namespace hx
+
 extern "C" hx_status hx_conv1d_silu_xproj_fwd(const void *x, int64_t x_batch_stride, int64_t x_row_stride, const float *conv_w,
                                               const float *conv_b, const void *W_x, int64_t ldw, void *u, int64_t u_batch_stride,
                                               int64_t u_row_stride, void *x_dbl, int64_t x_dbl_row_stride, int32_t batch,
@@ -313,36 +354,17 @@ extern "C" hx_status hx_conv1d_silu_xproj_fwd(const void *x, int64_t x_batch_str
     // what the kernel is written for; a caller that gets this status runs hx_conv1d_silu_fwd and hx_gemm_bf16
     if (!(io_dtype == HX_BF16 && d_conv == 4 && d_inner % KC == 0 && n_out % 8 == 0 && n_out <= 256 && al16(conv_w) &&
           (!conv_b || al16(conv_b)) && al16(x_dbl) && (x_dbl_row_stride * 2) % 16 == 0 && x_dbl_row_stride >= n_out &&
-          (int64_t)batch * ((seq_len + TM - 1) / TM) <= 0x7fffffff))
+          (int64_t)batch * ((seq_len + 63) / 64) <= 0x7fffffff))
         return hx::fail(HX_ERR_UNSUPPORTED_OPERATION,
                         "hx_conv1d_silu_xproj_fwd takes bf16, d_conv 4, d_inner a multiple of 64, n_out a multiple of 8 up to 256 "
                         "and 16-byte aligned operands");
-    CUtensorMap mx, mw, mu;
-    hx_status s;
-    const uint64_t dims_x[3] = {(uint64_t)d_inner, (uint64_t)seq_len, (uint64_t)batch};
-    const uint64_t str_x[2] = {(uint64_t)x_row_stride * 2, (uint64_t)x_batch_stride * 2};
-    const uint32_t box_x[3] = {(uint32_t)KC, (uint32_t)X_BOX_ROWS, 1};
-    if ((s = hx::encode_tensor_map(&mx, HX_BF16, 3, x, dims_x, str_x, box_x, false)) != HX_OK) return s;
-    const uint64_t dims_w[2] = {(uint64_t)d_inner, (uint64_t)n_out};
-    const uint64_t str_w[1] = {(uint64_t)ldw * 2};
-    const int n_mma = (n_out + 15) / 16 * 16;   // W_x rows past n_out are out of range for TMA and read as zeros
-    const uint32_t box_w[2] = {(uint32_t)KC, (uint32_t)n_mma};
-    if ((s = hx::encode_tensor_map(&mw, HX_BF16, 2, W_x, dims_w, str_w, box_w, true)) != HX_OK) return s;
-    const uint64_t str_u[2] = {(uint64_t)u_row_stride * 2, (uint64_t)u_batch_stride * 2};
-    const uint32_t box_u[3] = {(uint32_t)KC, (uint32_t)TM, 1};
-    if ((s = hx::encode_tensor_map(&mu, HX_BF16, 3, u, dims_x, str_u, box_u, true)) != HX_OK) return s;
-    const int smem = smem_bytes(n_mma);
-    static std::atomic<int> attr_set[64];  // largest size the attribute was set to, per device
-    int dev = 0;
-    HX_CUDA(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && attr_set[dev].load(std::memory_order_acquire) < smem) {
-        HX_CUDA(cudaFuncSetAttribute(conv_xproj_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-        attr_set[dev].store(smem, std::memory_order_release);
-    }
-    uint32_t cols = 32;
-    while ((int)cols < n_mma) cols *= 2;
-    const int tiles_per_seq = (seq_len + TM - 1) / TM;
-    conv_xproj_kernel<<<batch * tiles_per_seq, THREADS, smem, (cudaStream_t)stream>>>(
-        mx, mw, mu, conv_w, conv_b, static_cast<__nv_bfloat16 *>(x_dbl), x_dbl_row_stride, seq_len, d_inner, n_out, n_mma, tiles_per_seq, cols);
-    return hx::check_launch("conv_xproj_kernel");
+    // 128-step tiles, or 64-step ones where the long tiles would leave SMs without a CTA (a CTA walks its channels
+    // one block after the other, so a short grid is bound by that chain: 33.7 against 25.5 us at 4 x 2048 x 1536)
+    const int64_t long_tiles = (int64_t)batch * ((seq_len + 127) / 128);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (long_tiles < hx::sm_count())
+        return launch<64>(x, x_batch_stride, x_row_stride, conv_w, conv_b, W_x, ldw, u, u_batch_stride, u_row_stride, x_dbl,
+                          x_dbl_row_stride, batch, seq_len, d_inner, n_out, st);
+    return launch<128>(x, x_batch_stride, x_row_stride, conv_w, conv_b, W_x, ldw, u, u_batch_stride, u_row_stride, x_dbl,
+                       x_dbl_row_stride, batch, seq_len, d_inner, n_out, st);
 }

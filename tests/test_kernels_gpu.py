@@ -80,12 +80,12 @@ def test_conv1d_silu(dtype, B, L, D, K):
 
 
 @pytest.mark.parametrize("B,L,E,NO", [(1, 128, 64, 16), (2, 300, 128, 80), (1, 5, 64, 40), (3, 1000, 1536, 80), (1, 257, 256, 256),
-                                      (2, 131, 192, 8)])
+                                      (2, 131, 192, 8), (20, 1000, 64, 24)])   # the last: enough tiles for the 128-step form
 def test_conv_silu_and_x_proj_in_one_kernel(B, L, E, NO):
     """hx_conv1d_silu_xproj_fwd (the conv's tile of u is the tensor core's A operand) against the oracle's conv + SiLU
     and Linear, with x a strided half of a wider buffer as in the block; u must equal the conv kernel's bit for bit.
-    Sequence lengths that are not multiples of the 128-step tile and output widths that are not multiples of 16 are
-    among the cases."""
+    Sequence lengths that are not multiples of the tile (64 steps on short grids, 128 otherwise) and output widths
+    that are not multiples of 16 are among the cases."""
     import torch
     from helixml_b200 import ops
     xz = synth.round_bf16(synth.normal(67, "xz", (B, L, 2 * E)))
