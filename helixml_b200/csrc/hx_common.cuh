@@ -50,6 +50,7 @@ hx_status residual_add(float *resid, const void *x, int x_dtype, int64_t n, cuda
 namespace scan {
 enum class ScanKind { Tiled, Direct, LookBack };
 ScanKind auto_kind(const hx_scan_args *a);
+int auto_channels_per_lane(const hx_scan_args *a);  // 1 or 2: what the one-lane-per-channel kernel would run with
 }  // namespace scan
 
 // Translation units with bounded device-side waits keep a status word each; these read (and

@@ -7,13 +7,13 @@
 
 #include "hx_common.cuh"
 
-// 1: HX_SCAN_AUTO lets the one-pass scan compute the dt projection itself; 0: a dt_proj kernel of its own.
-// Measured over the 24 blocks of the byte LM at 32 x 2048 x 1536: fused 12.5 ms; unfused 10.2 ms of scan + 1.5 ms of
-// dt_proj (the unfused kernel holds 32 KB of shared memory against 65 KB, so a chain's next segment is resident
-// and prefetched when its predecessor ends, and it gains from the larger register budget where the fused one does
-// not).  HX_SCAN_DIRECT / HX_SCAN_LOOKBACK as explicit variants still fuse.
+// HX_SCAN_AUTO: 0 = dt_proj is a kernel of its own; 1 = the one-pass scan computes the dt projection itself; 2 = the
+// look-back form does too.  Measured over the 24 blocks of the byte LM at 32 x 2048 x 1536 (ms): scan with the
+// projection inside as tcgen05.mma into tensor memory 10.7; scan 10.1 + dt_proj kernel 1.6; the earlier fused form
+// (mma.sync in the producer warp, an fp32 dt tile in shared memory) 12.5-13.2.  At 4 / 8 / 16 rows (look-back form) the
+// step is 4.60 / 7.64 / 13.73 ms fused against 4.66 / 7.79 / 14.05.
 #ifndef HX_BLOCK_FUSE_DT_AUTO
-#define HX_BLOCK_FUSE_DT_AUTO 0
+#define HX_BLOCK_FUSE_DT_AUTO 2
 #endif
 // 1: conv + SiLU and x_proj as one kernel where its conditions hold; 0: always two kernels.
 #ifndef HX_BLOCK_FUSE_CONV_XPROJ
@@ -92,11 +92,14 @@ static bool fuses_dt(const hx_mamba_block_args *a, int W, int splits) {
     if (a->scan_variant != HX_SCAN_AUTO) return false;
     hx_scan_args sa = scan_shape(a);
     sa.seq_splits = splits;
-    // AUTO fuses only into the one-pass kernel (there the fused form and a dt_proj kernel + unfused scan take the same
-    // time, 12.9 against 11.5 + 1.5 ms over 24 blocks at 32 x 2048 x 1536, and the fused form moves 0.4 GB less).  The look-back form has CTAs to spare and lives on occupancy: with
-    // the projection's weight and fp32 dt tiles in shared memory 3 CTAs fit an SM, without them 7, and measured at
-    // 4 to 16 rows of 2048 x 1536 the unfused form with a dt_proj GEMM of its own is the faster one.
-    return HX_BLOCK_FUSE_DT_AUTO && hx::scan::auto_kind(&sa) == hx::scan::ScanKind::Direct;
+    // AUTO fuses where the scan runs one lane per channel (the one-pass kernel below the chain count that switches it
+    // to two channels per lane, and the look-back form): there the projection is a tcgen05.mma into tensor memory.
+    // With two channels per lane it would be the producer warp's mma.sync through shared memory, which is slower than
+    // a dt_proj kernel of its own.
+    const hx::scan::ScanKind kind = hx::scan::auto_kind(&sa);
+    if (kind == hx::scan::ScanKind::Direct) return HX_BLOCK_FUSE_DT_AUTO >= 1 && hx::scan::auto_channels_per_lane(&sa) == 1;
+    if (kind == hx::scan::ScanKind::LookBack) return HX_BLOCK_FUSE_DT_AUTO >= 2 && a->a_geometric != 0;
+    return false;
 }
 
 // True when conv + SiLU and x_proj run as one kernel (hx_conv1d_silu_xproj_fwd's conditions on the block's buffers;

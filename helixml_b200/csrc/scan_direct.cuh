@@ -12,6 +12,10 @@
 //   * the point-wise math (conv, SiLU, softplus, decay, gate) runs in-line, packed f32x2 over the channel
 //     pair when CPL == 2; with geometric A the 16 decays are powers of one exponential;
 //   * no shuffles, no shared-memory traffic between lanes.
+// The block's call can leave the dt projection to this kernel (dt = dt_low . W_dt^T, no dt tensor in memory): with one
+// lane per channel the producer lane issues tcgen05.mma with the CTA's [128 channels x rank] W_dt tile as the M
+// operand and the chunk's [16 steps x rank] dt_low rows as the N operand, so the accumulator's lane is the consumer
+// lane that owns the channel and a consumer warp fetches its 16 steps of dt with one tcgen05.ld (FUSEDT == 2).
 // A warp therefore covers 32*CPL channels; a CTA has 4 such warps plus the producer warp, which issues the
 // TMA loads (unswizzled 128-byte-wide boxes: every warp-wide access is one contiguous row) and widens B/C to
 // fp32 once per CTA.  y needs no staging: each step a warp writes one contiguous run of 32*CPL channels
@@ -43,6 +47,10 @@
 #ifndef HX_SCAN_UNROLL
 #define HX_SCAN_UNROLL 8
 #endif
+// 1: whole 16-step chunks run fully unrolled and branch-free; 0: the step loop unrolled by HX_SCAN_UNROLL.
+#ifndef HX_SCAN_FULL_UNROLL
+#define HX_SCAN_FULL_UNROLL 1
+#endif
 #ifndef HX_SCAN_MINB_LOOKBACK
 #define HX_SCAN_MINB_LOOKBACK 0
 #endif
@@ -50,14 +58,20 @@
 namespace hx {
 namespace scan {
 
-template <typename T, int CPL_, bool GEOM_, bool STD_, int STAGES_, bool FUSEDT_ = false, bool ZGATE_ = false,
+template <typename T, int CPL_, bool GEOM_, bool STD_, int STAGES_, int FUSEDT_ = 0, bool ZGATE_ = false,
           bool BLOCK_ = false, int MODE_ = 0>
 struct DirectCfg {
     static constexpr int MODE = MODE_;                 // 0 chained segments, 1 aggregate pass, 2 output pass (see above)
     static constexpr bool BLOCK = BLOCK_;              // the Mamba block's call: no conv (u is given), gate and softplus
                                                        // present, all known at compile time
     static constexpr bool ZGATE = ZGATE_;              // z is known at compile time to hold silu(z) already
-    static constexpr bool FUSEDT = FUSEDT_;            // dt = dt_low . W_dt^T computed by the producer warp (bf16 only)
+    // dt = dt_low . W_dt^T computed inside the kernel (bf16 only).  1: the producer warp runs mma.sync and writes an fp32
+    // dt tile to shared memory.  2: one producer lane issues tcgen05.mma with the CTA's W_dt tile as the M = 128 operand
+    // (one row per channel) and the chunk's dt_low rows as the N = 16 operand; the accumulator's lane IS the consumer
+    // lane that owns the channel, so a consumer warp fetches its 16 steps of dt with one tcgen05.ld and no dt ever
+    // touches shared memory (one lane per channel only).
+    static constexpr int FUSEDT = FUSEDT_;
+    static constexpr int TMEM_COLS = STAGES_ * 16 <= 32 ? 32 : 64;   // FUSEDT == 2: STAGES accumulators of TC columns
     static constexpr int RP = 64;                      // columns of the dt_low / W_dt tiles (dt_rank <= 64, zero filled)
     static constexpr int CPL = CPL_;
     static constexpr bool GEOM = GEOM_;
@@ -75,12 +89,13 @@ struct DirectCfg {
     static constexpr int THREADS = (NWARP + 1) * 32;
     // second argument of __launch_bounds__ (0 = none): the register budget the compiler schedules for
     static constexpr int UNROLL = HX_SCAN_UNROLL;
+    static constexpr int REM_UNROLL = HX_SCAN_FULL_UNROLL ? 1 : HX_SCAN_UNROLL;  // the loop whole chunks do not take
     static constexpr int MIN_CTAS = (MODE_ != 0 && !FUSEDT_) ? HX_SCAN_MINB_LOOKBACK : HX_SCAN_MINB_CHAINED;
     static constexpr int X_BYTES = (TC + 3) * 128;
     static constexpr int ROW_BYTES = TC * 128;
-    static constexpr int DTROW = FUSEDT ? BOXC * 4 + 32 : 128;            // bytes per dt row (fp32 + pad when produced here:
+    static constexpr int DTROW = FUSEDT == 1 ? BOXC * 4 + 32 : 128;       // bytes per dt row (fp32 + pad when produced here:
                                                                           // the pad spreads the producer's stores over banks)
-    static constexpr int DTT_BYTES = TC * DTROW;
+    static constexpr int DTT_BYTES = FUSEDT == 2 ? 0 : TC * DTROW;        // no dt rows at all when dt arrives in registers
     static constexpr int BOX_BYTES = X_BYTES + ROW_BYTES + DTT_BYTES;     // x, z, dt of one box
     static constexpr int BC_BYTES = (TC * 16 * ES + 127) / 128 * 128;
     static constexpr int BCF_BYTES = TC * 16 * 4;
@@ -90,8 +105,10 @@ struct DirectCfg {
     static constexpr int STAGE_BYTES = FUSEDT ? (STAGE_RAW + 1023) / 1024 * 1024 : STAGE_RAW;  // swizzled tile first
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + WDT_BYTES + 128 + (FUSEDT ? 1024 : 128);
     static_assert(WC * ES <= 128, "a warp's channels must fit one 128-byte box");
-    static_assert(3 * STAGES + 1 <= 16, "barrier area too small");
+    static_assert(3 * STAGES + 2 <= 12, "barrier area too small");
     static_assert(!FUSEDT || sizeof(T) == 2, "the fused dt projection takes bf16 operands");
+    static_assert(FUSEDT != 2 || (CPL_ == 1 && DT == 128 && STAGES_ * TC <= TMEM_COLS),
+                  "the tensor-memory form maps channel c of the CTA to accumulator lane c");
     static_assert(MODE == 0 || GEOM, "the look-back passes need geometric A");
 };
 
@@ -115,7 +132,8 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                    const __grid_constant__ CUtensorMap tm_wdt, const TiledParams p, T *__restrict__ yg, const int64_t y_bs,
                    const int64_t y_rs) {
     constexpr int CPL = Cfg::CPL, TC = Cfg::TC, STAGES = Cfg::STAGES, NW = Cfg::NWARP, NB = Cfg::NB, ES = Cfg::ES;
-    constexpr bool GEOM = Cfg::GEOM, FAST = Cfg::FAST, STD = Cfg::STD, FUSEDT = Cfg::FUSEDT;
+    constexpr bool GEOM = Cfg::GEOM, FAST = Cfg::FAST, STD = Cfg::STD;
+    constexpr int FUSEDT = Cfg::FUSEDT;
     constexpr bool BLOCK = Cfg::BLOCK;
     constexpr int MODE = Cfg::MODE;
     const bool has_conv = !BLOCK && (STD || p.K > 0), has_z = MODE != 1 && (STD || BLOCK || p.has_z),
@@ -135,6 +153,8 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     auto bar_ready = [&](int s) { return bar0 + 8u * (STAGES + s); };
     auto bar_empty = [&](int s) { return bar0 + 8u * (2 * STAGES + s); };
     const uint32_t bar_w = bar0 + 8u * (3 * STAGES);  // W_dt tile landed
+    const uint32_t bar_tdone = bar0 + 8u * (3 * STAGES + 1);  // FUSEDT == 2: consumer warps are done with tensor memory
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 12);
     // stage layout: [dt_low tile (fused dt only, 1024-aligned for its swizzle)] [boxes] [B, C raw] [B, C fp32]
     constexpr int OFF_DTLOW = 0, OFF_BOX0 = Cfg::DTLOW_BYTES;
     constexpr int OFF_BC = OFF_BOX0 + NB * Cfg::BOX_BYTES, OFF_C = OFF_BC + Cfg::BC_BYTES, OFF_BF = OFF_C + Cfg::BC_BYTES,
@@ -153,13 +173,28 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(bar_full(s), 1);
-            mbar_init(bar_ready(s), 1);
+            mbar_init(bar_ready(s), FUSEDT == 2 ? 2 : 1);  // the producer warp's arrival, and the MMA's commit
             mbar_init(bar_empty(s), NW);
         }
         mbar_init(bar_w, 1);
+        mbar_init(bar_tdone, NW);
         mbar_fence_init();
     }
+    uint32_t tmem_base = 0;
+    if constexpr (FUSEDT == 2) {
+        if (warp == NW) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                         "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
+        tc::tc_fence_before();
+    }
     __syncthreads();
+    if constexpr (FUSEDT == 2) {
+        tc::tc_fence_after();
+        tmem_base = *tmem_slot;
+    }
 
     if (warp == NW) {
         // ================================================================ producer warp
@@ -211,7 +246,19 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 const bool ok = mbar_wait(bar_full(s), (i / STAGES) & 1);
                 if (!__all_sync(0xffffffffu, ok)) { fail_code = kWaitFull; break; }
                 char *st = stage_base + s * Cfg::STAGE_BYTES;
-                if constexpr (FUSEDT) {
+                if constexpr (FUSEDT == 2) {
+                    // dt^T[DT channels][16 steps] = W_dt[DT][RP] . dt_low[16][RP]^T into tensor memory: lane = channel
+                    if (lane == 0) {
+                        tc::tc_fence_after();
+                        const uint64_t da = tc::make_smem_desc(smem_u32(wdt_tile));
+                        const uint64_t db = tc::make_smem_desc(smem_u32(st + OFF_DTLOW));
+                        const uint32_t idesc = tc::idesc_bf16(128, TC);
+                        const int ksteps = (p.dt_rank + 15) >> 4;
+                        for (int k = 0; k < ksteps; ++k)
+                            tc::umma_bf16(tmem_base + s * TC, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, k ? 1u : 0u);
+                        tc::umma_commit(bar_ready(s));
+                    }
+                } else if constexpr (FUSEDT == 1) {
                     // dt[16 steps][DT channels] = dt_low[16][RP] . W_dt[DT][RP]^T on the tensor cores
                     // (mma.sync m16n8k16, bf16 in, fp32 out), written as the fp32 dt tile of every box
                     constexpr int RPB = Cfg::RP * 2;  // row bytes of both operand tiles
@@ -297,6 +344,15 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             // let loads already in flight land before the CTA's shared memory goes away
             for (int i = 0; i < issued; ++i) mbar_wait(bar_full(i % STAGES), (i / STAGES) & 1);
         }
+        if constexpr (FUSEDT == 2) {
+            // tensor memory goes back once the consumer warps have read their last chunk (a bounded wait: a consumer
+            // that gave up never arrives)
+            if (lane == 0) mbar_wait(bar_tdone, 0);
+            __syncwarp();
+            tc::tc_fence_after();
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS)
+                         : "memory");
+        }
         return;
     }
 
@@ -360,6 +416,13 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             constexpr int DROW = Cfg::DTROW;
             const float4 *sBf = reinterpret_cast<const float4 *>(stage_base + s * Cfg::STAGE_BYTES + OFF_BF);
             const int steps = min(TC, t_seg1 - (t_seg0 + c * TC));
+            uint32_t dtreg[16];
+            if constexpr (FUSEDT == 2) {
+                // this lane's channel, the chunk's 16 steps: one row of the accumulator
+                tc::tc_fence_after();
+                tc::tmem_ld16(tmem_base + s * TC + ((uint32_t)(warp * 32) << 16), dtreg);
+                tc::tmem_ld_wait();
+            }
             // conv window for the walk backwards: x of the three steps that follow the row read next
             float xa[CPL], xb[CPL], xc3[CPL];
 #pragma unroll
@@ -368,14 +431,13 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 xb[e] = ld_chan1<T>(sx + (steps + 1) * 128 + e * ES);
                 xc3[e] = ld_chan1<T>(sx + steps * 128 + e * ES);
             }
-#pragma unroll 8
-            for (int tt = 0; tt < steps; ++tt) {
-                const int t = steps - 1 - tt;
+            auto back_step = [&](const int t, const float dt_reg) {
                 float xn[CPL], dr[CPL];
 #pragma unroll
                 for (int e = 0; e < CPL; ++e) {
                     xn[e] = ld_chan1<T>(sx + t * 128 + e * ES);  // x three steps before step t
-                    if constexpr (FUSEDT) dr[e] = *reinterpret_cast<const float *>(sd + t * DROW + e * 4);
+                    if constexpr (FUSEDT == 2) dr[e] = dt_reg;
+                    else if constexpr (FUSEDT == 1) dr[e] = *reinterpret_cast<const float *>(sd + t * DROW + e * 4);
                     else dr[e] = ld_chan1<T>(sd + t * DROW + e * ES);
                 }
                 float4 Bv[4];
@@ -426,7 +488,22 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                         q[e][2 * k + 1] = fma2(a[2 * k + 1], make_float2(Bv[k].z, Bv[k].w), q[e][2 * k + 1]);
                     }
                 }
+            };
+            // whole chunks fully unrolled, the ragged one through the plain loop (see the output pass below)
+            if (steps == TC && (FUSEDT == 2 || HX_SCAN_FULL_UNROLL)) {
+#pragma unroll
+                for (int t = TC - 1; t >= 0; --t) back_step(t, FUSEDT == 2 ? __uint_as_float(dtreg[t]) : 0.f);
+            } else if constexpr (FUSEDT == 2) {
+                float dtl[TC];
+#pragma unroll
+                for (int t = 0; t < TC; ++t) dtl[t] = __uint_as_float(dtreg[t]);
+#pragma unroll 1
+                for (int t = steps - 1; t >= 0; --t) back_step(t, dtl[t]);
+            } else {
+#pragma unroll(Cfg::REM_UNROLL)
+                for (int tt = 0; tt < steps; ++tt) back_step(steps - 1 - tt, 0.f);
             }
+            if constexpr (FUSEDT == 2) tc::tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty(s));
         }
@@ -438,6 +515,9 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
 #pragma unroll
             for (int j = 0; j < 8; ++j) dst[j] = q[e][j];
             p.sdt[ci] = sacc[e];
+        }
+        if constexpr (FUSEDT == 2) {
+            if (lane == 0) mbar_arrive(bar_tdone);
         }
         return;
     }
@@ -511,6 +591,13 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         const float4 *sCf = reinterpret_cast<const float4 *>(stage_base + s * Cfg::STAGE_BYTES + OFF_CF);
         const int steps = min(TC, t_seg1 - (t_seg0 + i * TC));
         T *yrow = yg + (int64_t)b * y_bs + (int64_t)(t_seg0 + i * TC) * y_rs + dch;  // this lane's first output
+        uint32_t dtreg[16];
+        if constexpr (FUSEDT == 2) {
+            // this lane's channel, the chunk's 16 steps: one row of the accumulator
+            tc::tc_fence_after();
+            tc::tmem_ld16(tmem_base + s * TC + ((uint32_t)(warp * 32) << 16), dtreg);
+            tc::tmem_ld_wait();
+        }
 
         // conv window: the three steps before the chunk come from the halo rows
         float xw[CPL][3];
@@ -525,14 +612,12 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             }
         }
 
-// unrolled by 8: 4 is 10 % slower, 16 no faster (measured at 49 152 chains)
-#pragma unroll(Cfg::UNROLL)
-        for (int t = 0; t < steps; ++t) {
+        auto fwd_step = [&](const int t, const float dt_reg) {
             float xc[CPL], dr[CPL], zr[CPL];
             if constexpr (CPL == 2) {
                 const float2 vx = ld_chan2<T>(sx + (t + 3) * 128);
                 float2 vd;
-                if constexpr (FUSEDT) vd = *reinterpret_cast<const float2 *>(sd + t * DROW);
+                if constexpr (FUSEDT == 1) vd = *reinterpret_cast<const float2 *>(sd + t * DROW);
                 else vd = ld_chan2<T>(sd + t * DROW);
                 xc[0] = vx.x; xc[1] = vx.y; dr[0] = vd.x; dr[1] = vd.y;
                 if (has_z) {
@@ -541,7 +626,8 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 }
             } else {
                 xc[0] = ld_chan1<T>(sx + (t + 3) * 128);
-                if constexpr (FUSEDT) dr[0] = *reinterpret_cast<const float *>(sd + t * DROW);
+                if constexpr (FUSEDT == 2) dr[0] = dt_reg;
+                else if constexpr (FUSEDT == 1) dr[0] = *reinterpret_cast<const float *>(sd + t * DROW);
                 else dr[0] = ld_chan1<T>(sd + t * DROW);
                 if (has_z) zr[0] = ld_chan1<T>(sz + t * 128);
             }
@@ -636,7 +722,25 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             } else {
                 if (dch < p.D) st_f32(yp, yout[0]);
             }
+        };
+        // Whole chunks run fully unrolled with no test between the steps: a loop bound or a predicate per step keeps the
+        // compiler from moving a step's loads and special-function results above the previous step's arithmetic, and
+        // costs a sixth of the kernel.  The one ragged chunk of a segment takes the plain loop (with dt in registers,
+        // FUSEDT == 2, through a local copy: there the step index has to be a compile-time constant).
+        if (steps == TC && (FUSEDT == 2 || HX_SCAN_FULL_UNROLL)) {
+#pragma unroll
+            for (int t = 0; t < TC; ++t) fwd_step(t, FUSEDT == 2 ? __uint_as_float(dtreg[t]) : 0.f);
+        } else if constexpr (FUSEDT == 2) {
+            float dtl[TC];
+#pragma unroll
+            for (int t = 0; t < TC; ++t) dtl[t] = __uint_as_float(dtreg[t]);
+#pragma unroll 1
+            for (int t = 0; t < steps; ++t) fwd_step(t, dtl[t]);
+        } else {
+#pragma unroll(Cfg::REM_UNROLL)
+            for (int t = 0; t < steps; ++t) fwd_step(t, 0.f);
         }
+        if constexpr (FUSEDT == 2) tc::tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_empty(s));
     }
@@ -660,6 +764,9 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
             const int fidx = ((seg * p.B + b) * gridDim.x + tile) * 8 + warp;
             asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.flags + fidx), "r"(p.epoch) : "memory");
         }
+    }
+    if constexpr (FUSEDT == 2) {
+        if (lane == 0) mbar_arrive(bar_tdone);
     }
 }
 

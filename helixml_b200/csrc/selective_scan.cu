@@ -26,6 +26,7 @@
 #include <vector>
 
 #include "hx_tma.cuh"
+#include "hx_tcgen05.cuh"
 
 namespace hx {
 namespace scan {
@@ -928,7 +929,7 @@ static hx_status launch_tiled(const hx_scan_args *a, bool split, cudaStream_t st
 }
 
 
-template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2, bool FUSEDT = false, bool ZGATE = false, bool BLOCK = false,
+template <typename T, int CPL, bool GEOM, bool STD, int STAGES = 2, int FUSEDT = 0, bool ZGATE = false, bool BLOCK = false,
           int MODE = 0>
 static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *maps, dim3 grid, cudaStream_t st, void *y,
                                     int64_t y_bs, int64_t y_rs) {
@@ -948,7 +949,7 @@ static hx_status launch_direct_inst(const TiledParams &p, const CUtensorMap *map
 
 // The two launches of the look-back form: the aggregate pass over segments 0 .. S-2, then the output pass over
 // all S segments (stream order is the only dependency between them).
-template <typename T, bool STD, bool FUSEDT, bool BLOCK>
+template <typename T, bool STD, int FUSEDT, bool BLOCK>
 static hx_status launch_lookback_pair(const TiledParams &p, const CUtensorMap *maps, dim3 grid, cudaStream_t st, void *y,
                                       int64_t y_bs, int64_t y_rs) {
     dim3 g1(grid.x, grid.y, grid.z - 1);
@@ -957,6 +958,16 @@ static hx_status launch_lookback_pair(const TiledParams &p, const CUtensorMap *m
     return launch_direct_inst<T, 1, true, STD, 2, FUSEDT, false, BLOCK, 2>(p, maps, grid, st, y, y_bs, y_rs);
 }
 
+// 1: the fused dt projection of the block's one-lane-per-channel scan runs as tcgen05.mma into tensor memory; 0: as
+// mma.sync in the producer warp, through a shared-memory tile.
+#ifndef HX_SCAN_FUSEDT_TC
+#define HX_SCAN_FUSEDT_TC 1
+#endif
+// ring stages of that form: with two, the chain load -> MMA -> commit of the next chunk does not always fit under the
+// 16 steps of the current one (10.90 against 10.74 ms over the 24 blocks of the byte LM)
+#ifndef HX_SCAN_FUSEDT_STAGES
+#define HX_SCAN_FUSEDT_STAGES 3
+#endif
 #ifndef HX_SCAN_CPL2_MIN_WARPS
 #define HX_SCAN_CPL2_MIN_WARPS 8.0
 #endif
@@ -1072,11 +1083,14 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
     void *yv = a->y;
     const int64_t ybs = a->y_batch_stride, yrs = a->y_row_stride;
     if (form == 1) {
-        if (fused_dt) return launch_lookback_pair<__nv_bfloat16, false, true, true>(p, maps, grid, st, yv, ybs, yrs);
-        if (blockp) return launch_lookback_pair<__nv_bfloat16, false, false, true>(p, maps, grid, st, yv, ybs, yrs);
-        if (bf && stdp) return launch_lookback_pair<__nv_bfloat16, true, false, false>(p, maps, grid, st, yv, ybs, yrs);
-        if (bf) return launch_lookback_pair<__nv_bfloat16, false, false, false>(p, maps, grid, st, yv, ybs, yrs);
-        return launch_lookback_pair<float, false, false, false>(p, maps, grid, st, yv, ybs, yrs);
+        if (fused_dt) {
+            if (HX_SCAN_FUSEDT_TC) return launch_lookback_pair<__nv_bfloat16, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
+            return launch_lookback_pair<__nv_bfloat16, false, 1, true>(p, maps, grid, st, yv, ybs, yrs);
+        }
+        if (blockp) return launch_lookback_pair<__nv_bfloat16, false, 0, true>(p, maps, grid, st, yv, ybs, yrs);
+        if (bf && stdp) return launch_lookback_pair<__nv_bfloat16, true, 0, false>(p, maps, grid, st, yv, ybs, yrs);
+        if (bf) return launch_lookback_pair<__nv_bfloat16, false, 0, false>(p, maps, grid, st, yv, ybs, yrs);
+        return launch_lookback_pair<float, false, 0, false>(p, maps, grid, st, yv, ybs, yrs);
     }
 #define HX_DIRECT_CASE(T, CPL)                                                                                         \
     do {                                                                                                               \
@@ -1093,24 +1107,27 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
         // in_proj has already applied it
         if (p.z_gate) {
             if (cpl == 2) {
-                if (geom) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, true, true>(p, maps, grid, st, yv, ybs, yrs);
-                return launch_direct_inst<__nv_bfloat16, 2, false, false, 2, true, true>(p, maps, grid, st, yv, ybs, yrs);
+                if (geom) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, 1, true>(p, maps, grid, st, yv, ybs, yrs);
+                return launch_direct_inst<__nv_bfloat16, 2, false, false, 2, 1, true>(p, maps, grid, st, yv, ybs, yrs);
             }
-            if (geom) return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, true, true>(p, maps, grid, st, yv, ybs, yrs);
-            return launch_direct_inst<__nv_bfloat16, 1, false, false, 2, true, true>(p, maps, grid, st, yv, ybs, yrs);
+            if (geom) return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, 1, true>(p, maps, grid, st, yv, ybs, yrs);
+            return launch_direct_inst<__nv_bfloat16, 1, false, false, 2, 1, true>(p, maps, grid, st, yv, ybs, yrs);
         }
         // the block's own call: every flag is a compile-time constant, which saves the per-point flag tests and the
         // registers of the unused conv window
         if (blockp) {
-            if (cpl == 2) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, true, false, true>(p, maps, grid, st, yv, ybs, yrs);
-            return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, true, false, true>(p, maps, grid, st, yv, ybs, yrs);
+            if (cpl == 2) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, 1, false, true>(p, maps, grid, st, yv, ybs, yrs);
+            // one lane per channel: the projection runs as tcgen05.mma into tensor memory, lane = channel
+            if (HX_SCAN_FUSEDT_TC)
+                return launch_direct_inst<__nv_bfloat16, 1, true, false, HX_SCAN_FUSEDT_STAGES, 2, false, true>(p, maps, grid, st, yv, ybs, yrs);
+            return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, 1, false, true>(p, maps, grid, st, yv, ybs, yrs);
         }
         if (cpl == 2) {
-            if (geom) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
-            return launch_direct_inst<__nv_bfloat16, 2, false, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
+            if (geom) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, 1>(p, maps, grid, st, yv, ybs, yrs);
+            return launch_direct_inst<__nv_bfloat16, 2, false, false, 2, 1>(p, maps, grid, st, yv, ybs, yrs);
         }
-        if (geom) return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
-        return launch_direct_inst<__nv_bfloat16, 1, false, false, 2, true>(p, maps, grid, st, yv, ybs, yrs);
+        if (geom) return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, 1>(p, maps, grid, st, yv, ybs, yrs);
+        return launch_direct_inst<__nv_bfloat16, 1, false, false, 2, 1>(p, maps, grid, st, yv, ybs, yrs);
     }
     if (bf && geom && stdp && a->reserved / 10 == 1) {  // tuning: three stages instead of two
         if (cpl == 2) return launch_direct_inst<__nv_bfloat16, 2, true, true, 3>(p, maps, grid, st, yv, ybs, yrs);
@@ -1118,8 +1135,8 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
     }
     if (blockp) {
         // the block's configuration with dt read from memory: compile-time flags as in the fused form
-        if (cpl == 2) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, false, false, true>(p, maps, grid, st, yv, ybs, yrs);
-        return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, false, false, true>(p, maps, grid, st, yv, ybs, yrs);
+        if (cpl == 2) return launch_direct_inst<__nv_bfloat16, 2, true, false, 2, 0, false, true>(p, maps, grid, st, yv, ybs, yrs);
+        return launch_direct_inst<__nv_bfloat16, 1, true, false, 2, 0, false, true>(p, maps, grid, st, yv, ybs, yrs);
     }
     if (bf) {
         if (cpl == 2) HX_DIRECT_CASE(__nv_bfloat16, 2);
@@ -1135,6 +1152,8 @@ static hx_status launch_direct(const hx_scan_args *a, bool split, cudaStream_t s
 // SM the direct kernel runs them one pass, chained segments evening out the load.  Below that the machine is short
 // of independent work: with geometric A and a split the look-back form runs the segments of a chain at the same
 // time; otherwise the lane-split kernel spreads a chain's states over 2 or 4 lanes.
+int auto_channels_per_lane(const hx_scan_args *a) { return choose_cpl(a); }
+
 ScanKind auto_kind(const hx_scan_args *a) {
     const double warps_per_sm = (double)a->batch * a->d_inner / 32.0 / sm_count();
     if (warps_per_sm >= 8.0) return ScanKind::Direct;

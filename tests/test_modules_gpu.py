@@ -283,7 +283,7 @@ def test_mamba_block_full_size_config3_shape_sampled_rows():
     a.W_dt = dev["W_dt"].data_ptr()
     n = C.c_int32(0)
     _lib.check(_lib.lib().hx_mamba_block_kernel_launches(C.byref(a), C.byref(n)))
-    assert n.value == 5  # in_proj, conv + x_proj (one kernel), dt_proj, scan (one pass, chained segments), out_proj
+    assert n.value == 4  # in_proj, conv + x_proj (one kernel), scan (one pass, chained segments, dt projection inside), out_proj
     rows = [0, B - 1]
     ref = cbind.mamba_block(x[rows], wq, 16, 4)
     g = got[rows].float().cpu().numpy()
@@ -310,7 +310,7 @@ def test_byte_lm_full_size_config3_sampled_sequences():
     logits = torch.empty((B, L, 256), dtype=torch.bfloat16, device="cuda")
     lm.forward_device(tok_d.data_ptr(), logits.data_ptr(), B, L, torch.cuda.current_stream().cuda_stream)
     _lib.check_device()
-    assert lm.launches_per_forward == 1 + nl * 6 + 2  # norm, in_proj, conv + x_proj, dt_proj, scan, out_proj per block
+    assert lm.launches_per_forward == 1 + nl * 5 + 2  # norm, in_proj, conv + x_proj, scan (dt projection inside), out_proj per block
     rows = [0, B - 1]
     ref = cbind.byte_lm(tok[rows], emb_q, layers_q, normf, 16, 4)
     g = logits[rows].float().cpu().numpy()
@@ -328,7 +328,7 @@ def test_byte_lm_full_size_config3_sampled_sequences():
 
 def test_byte_lm_small_batch_runs_the_lookback_scan():
     """Four sequences per GPU is what one of eight GPUs gets of configuration 3's batch: too few chains for one pass,
-    so the blocks run the look-back form of the scan (two launches) after a dt_proj GEMM of its own."""
+    so the blocks run the look-back form of the scan (two launches), each pass computing the dt projection itself."""
     import torch
     from helixml_b200 import _lib, nn
     nl, M, B, L = 3, 768, 4, 1024
@@ -343,7 +343,7 @@ def test_byte_lm_small_batch_runs_the_lookback_scan():
     logits = torch.empty((B, L, 256), dtype=torch.bfloat16, device="cuda")
     lm.forward_device(tok_d.data_ptr(), logits.data_ptr(), B, L, torch.cuda.current_stream().cuda_stream)
     _lib.check_device()
-    assert lm.launches_per_forward == 1 + nl * 7 + 2  # norm, in_proj, conv + x_proj, dt_proj, aggregate pass, output pass, out_proj
+    assert lm.launches_per_forward == 1 + nl * 6 + 2  # norm, in_proj, conv + x_proj, aggregate pass, output pass (dt projection inside both), out_proj
     ref = cbind.byte_lm(tok, emb_q, layers_q, normf, 16, 4)
     g = logits.float().cpu().numpy()
     assert rel_l2(g, ref) <= BF16_TOL
