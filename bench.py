@@ -70,7 +70,7 @@ NCU_TRAFFIC = {
     ("lm_cfg3", "scan_direct_kernel (chained segments), dt_proj kernel before it"):
         {"bytes": 816_670_720, "capture": "ncu --set full, one launch inside the 24-block step: 614.7 MB read + 201.9 MB written"},
     ("lm_cfg3", "scan_direct_kernel (chained segments, dt projection inside)"):
-        {"bytes": 608_478_976, "capture": "ncu --set full, one launch inside the 24-block step: 413.7 MB read + 194.8 MB written"},
+        {"bytes": 607_432_960, "capture": "ncu --set full, one launch inside the 24-block step: 413.5 MB read + 193.9 MB written"},
     ("scan_cfg2", "scan_direct_kernel (look-back: aggregate pass + output pass)"):
         {"bytes": 1_108_681_472, "capture": "ncu --set full, both launches of one call: 304.2 + 4.6 MB (aggregate pass) and "
                                             "617.2 + 182.7 MB (output pass)"},
@@ -655,8 +655,9 @@ def run_lm(args, cfg, name):
             roof = {"bound": "hbm", "kernel": scan_kernel, "achieved": scan_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                     "frac": scan_gbs / peaks["hbm_gbs"], "peak_source": peaks["source"],
                     "algorithmic_bytes_per_launch": scan_bytes, "launch_ms": scan_ms, "traffic": traffic, "traffic_source": traffic_src,
-                    "note": "per call of the scan stage (all its launches, the dt_proj kernel not included); algorithmic "
-                            "bytes are those of the selective scan: u, dt, z read, y written, B and C read once"}
+                    "note": "per call of the scan stage (all its launches; the dt projection is inside them when the kernel "
+                            "name says so, otherwise the dt_proj kernel is not included); algorithmic bytes are those "
+                            "of the selective scan: u, dt, z read, y written, B and C read once"}
         else:
             roof = {"bound": "tensor", "kernel": "gemm_tc_kernel (all projections)", "achieved": gemm_tflops,
                     "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s", "frac": gemm_tflops / peaks["bf16_tflops_sustained"],
