@@ -47,7 +47,11 @@
 #ifndef HX_SCAN_UNROLL
 #define HX_SCAN_UNROLL 8
 #endif
-// 1: whole 16-step chunks run fully unrolled and branch-free; 0: the step loop unrolled by HX_SCAN_UNROLL.
+// Whole 16-step chunks run fully unrolled and branch-free where dt arrives in registers (FUSEDT == 2, which needs it)
+// and, with this macro at 1, in every one-channel-per-lane instantiation; two channels per lane always keep the step
+// loop unrolled by HX_SCAN_UNROLL.  Measured: one channel per lane gains 1-2 % (the block's scan reading dt from memory
+// 10.36 -> 10.13 ms per 24 blocks, configuration 2 in the look-back form 681 -> 654 us); two channels per lane lose
+// 10-16 % (98 304 chains x 2048 steps 781 -> 894 us, 327 680 chains x 16 384 steps 19.3 -> 23.0 ms).
 #ifndef HX_SCAN_FULL_UNROLL
 #define HX_SCAN_FULL_UNROLL 1
 #endif
@@ -89,7 +93,8 @@ struct DirectCfg {
     static constexpr int THREADS = (NWARP + 1) * 32;
     // second argument of __launch_bounds__ (0 = none): the register budget the compiler schedules for
     static constexpr int UNROLL = HX_SCAN_UNROLL;
-    static constexpr int REM_UNROLL = HX_SCAN_FULL_UNROLL ? 1 : HX_SCAN_UNROLL;  // the loop whole chunks do not take
+    static constexpr bool FULL = FUSEDT_ == 2 || (HX_SCAN_FULL_UNROLL && CPL_ == 1);   // whole chunks fully unrolled
+    static constexpr int REM_UNROLL = FULL ? 1 : HX_SCAN_UNROLL;                       // the loop they do not take
     static constexpr int MIN_CTAS = (MODE_ != 0 && !FUSEDT_) ? HX_SCAN_MINB_LOOKBACK : HX_SCAN_MINB_CHAINED;
     static constexpr int X_BYTES = (TC + 3) * 128;
     static constexpr int ROW_BYTES = TC * 128;
@@ -490,7 +495,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
                 }
             };
             // whole chunks fully unrolled, the ragged one through the plain loop (see the output pass below)
-            if (steps == TC && (FUSEDT == 2 || HX_SCAN_FULL_UNROLL)) {
+            if (steps == TC && Cfg::FULL) {
 #pragma unroll
                 for (int t = TC - 1; t >= 0; --t) back_step(t, FUSEDT == 2 ? __uint_as_float(dtreg[t]) : 0.f);
             } else if constexpr (FUSEDT == 2) {
@@ -727,7 +732,7 @@ scan_direct_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_consta
         // compiler from moving a step's loads and special-function results above the previous step's arithmetic, and
         // costs a sixth of the kernel.  The one ragged chunk of a segment takes the plain loop (with dt in registers,
         // FUSEDT == 2, through a local copy: there the step index has to be a compile-time constant).
-        if (steps == TC && (FUSEDT == 2 || HX_SCAN_FULL_UNROLL)) {
+        if (steps == TC && Cfg::FULL) {
 #pragma unroll
             for (int t = 0; t < TC; ++t) fwd_step(t, FUSEDT == 2 ? __uint_as_float(dtreg[t]) : 0.f);
         } else if constexpr (FUSEDT == 2) {
