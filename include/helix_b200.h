@@ -143,9 +143,11 @@ typedef struct hx_scan_args {
     int32_t lanes_per_channel;/* HX_SCAN_TILED / SEQSPLIT: lanes that share one channel's 16 states
                                  (1, 2 or 4; 0 = choose from the problem size) */
     int32_t reserved;         /* tuning selector, 0 = default.  HX_SCAN_DIRECT: channels per lane (1 or 2) */
-    /* Optional fused dt projection (bf16 I/O, HX_SCAN_DIRECT or HX_SCAN_AUTO when it picks that kernel):
-     * when W_dt != NULL the raw step sizes are computed inside the kernel as
-     *   dt_raw[b,t,d] = sum_r dt_low[b,t,r] * W_dt[d,r]      (fp32 accumulation on the tensor cores)
+    /* Optional fused dt projection (bf16 I/O, HX_SCAN_DIRECT / HX_SCAN_LOOKBACK, or HX_SCAN_AUTO when it picks one
+     * of them): when W_dt != NULL the raw step sizes are computed inside the kernel as
+     *   dt_raw[b,t,d] = sum_r dt_low[b,t,r] * W_dt[d,r]      (fp32 accumulation on the tensor cores: tcgen05.mma into
+     *                                                          tensor memory with one channel per lane in the block's
+     *                                                          configuration, mma.sync otherwise)
      * and `dt` is ignored.  dt_low is [batch, seq_len, dt_rank] with its own strides (a column slice of the
      * x_proj output), W_dt is [d_inner, dt_rank] row-major like nn::Linear; dt_rank <= 64 and a multiple of 8.
      * Other kernels report HX_ERR_UNSUPPORTED_OPERATION for it. */
@@ -389,7 +391,8 @@ typedef struct hx_mamba_block_args {
     int32_t scan_variant;     /* hx_scan_variant */
     int32_t a_geometric;      /* as hx_scan_args.a_geometric */
     void **stage_events;      /* NULL, or 7 cudaEvent_t: recorded on `stream` before each of the six stages
-                                 (in_proj, conv, x_proj, dt_proj, scan, out_proj) and after the last one */
+                                 (in_proj, conv, x_proj, dt_proj, scan, out_proj) and after the last one; a stage
+                                 that is done inside its neighbour's kernel shows as the gap between two marks */
     float *h_last;            /* NULL, or [batch, d_inner, d_state] fp32: the scan's state after the last step */
     void *conv_state;         /* NULL, or [batch, 3, d_inner] io dtype: the conv inputs of the last three steps
                                  (oldest first, zeros where seq_len < 3); with h_last, what hx_mamba_block_step
@@ -402,8 +405,10 @@ typedef struct hx_mamba_block_args {
 HX_API hx_status hx_mamba_block_fwd(const hx_mamba_block_args *args, void *stream);
 HX_API hx_status hx_mamba_block_workspace_bytes(const hx_mamba_block_args *args, size_t *bytes);
 /* Kernel launches one hx_mamba_block_fwd call with these arguments makes: 6 (in_proj, conv, x_proj, dt_proj,
- * scan, out_proj), or 5 when the dt projection is computed inside the scan kernel (bf16, d_state 16,
- * dt_rank a multiple of 8 up to 64, and enough batch * d_inner chains for the one-lane-per-channel scan). */
+ * scan, out_proj); one less where conv and x_proj run as one kernel (hx_conv1d_silu_xproj_fwd's conditions), one less
+ * where the dt projection is computed inside the scan kernel (bf16, d_state 16, dt_rank a multiple of 8 up to 64, a
+ * scan that runs one lane per channel), one more where the scan is the look-back form (two passes): 4 on the
+ * benchmark's 32 x 2048 x 768 bf16 block. */
 HX_API hx_status hx_mamba_block_kernel_launches(const hx_mamba_block_args *args, int32_t *launches);
 
 /* ---- single-token decode step of the block: the recurrent form of hx_mamba_block_fwd, continuing from
