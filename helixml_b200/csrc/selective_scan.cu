@@ -965,6 +965,11 @@ static hx_status launch_lookback_pair(const TiledParams &p, const CUtensorMap *m
 #endif
 // ring stages of that form: with two, the chain load -> MMA -> commit of the next chunk does not always fit under the
 // 16 steps of the current one (10.90 against 10.74 ms over the 24 blocks of the byte LM)
+// chained segments: split until the grid is about this many waves of CTA slots (measured at 49 152 chains with the
+// dt projection inside, per 24 blocks: 3 waves = 4 segments 10.98 ms, 6 = 8 segments 10.7-10.8, 12 = 16 segments 11.08)
+#ifndef HX_SCAN_CHAIN_WAVES
+#define HX_SCAN_CHAIN_WAVES 6.0
+#endif
 #ifndef HX_SCAN_FUSEDT_STAGES
 #define HX_SCAN_FUSEDT_STAGES 3
 #endif
@@ -1224,7 +1229,7 @@ int32_t hx_selective_scan_suggest_splits(const hx_scan_args *a) {
     const double ctas = (double)a->batch * ((a->d_inner + tile - 1) / tile);
     const double slots = 3.0 * hx::sm_count();
     if (ctas >= 8.0 * slots) return 1;
-    int want = (int)(6.0 * slots / ctas + 0.999);
+    int want = (int)(HX_SCAN_CHAIN_WAVES * slots / ctas + 0.999);
     int splits = 1;
     while (splits < want && splits < 16) splits *= 2;
     while (splits > 1 && a->seq_len / splits < 128) splits /= 2;  // keep segments long enough to amortise the hand-over
