@@ -199,13 +199,16 @@ hx_status hx_mamba_block_fwd(const hx_mamba_block_args *a, void *stream) {
     // 3. [dt_low | B | C] = u W_x^T                     [T, R + 2N]
     // One kernel does both where it can (the conv's tile of u is the tensor core's A operand, so u is not read
     // back); otherwise the conv kernel and a GEMM.
-    if (fuses_conv_xproj(a, W)) {
-        if ((s = hx_conv1d_silu_xproj_fwd(xz, (int64_t)a->seq_len * 2 * E, 2 * E, a->conv_w, a->conv_b, a->W_x, E, u,
-                                          (int64_t)a->seq_len * E, E, dbc, W, a->batch, a->seq_len, E, a->d_conv, W,
-                                          a->io_dtype, stream)) != HX_OK)
-            return s;
-        mark(2);
-    } else {
+    bool fused_cx = fuses_conv_xproj(a, W);
+    if (fused_cx) {
+        s = hx_conv1d_silu_xproj_fwd(xz, (int64_t)a->seq_len * 2 * E, 2 * E, a->conv_w, a->conv_b, a->W_x, E, u,
+                                     (int64_t)a->seq_len * E, E, dbc, W, a->batch, a->seq_len, E, a->d_conv, W, a->io_dtype,
+                                     stream);
+        if (s == HX_ERR_UNSUPPORTED_OPERATION) fused_cx = false;  // an operand the one kernel does not take: two kernels
+        else if (s != HX_OK) return s;
+        else mark(2);
+    }
+    if (!fused_cx) {
         if ((s = hx_conv1d_silu_fwd(xz, (int64_t)a->seq_len * 2 * E, 2 * E, a->conv_w, a->conv_b, u, (int64_t)a->seq_len * E,
                                     E, a->batch, a->seq_len, E, a->d_conv, a->io_dtype, stream)) != HX_OK)
             return s;
