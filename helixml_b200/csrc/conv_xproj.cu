@@ -12,12 +12,12 @@
 //               of W_x (128-byte swizzle), each in a small ring.
 //   warp 1      allocates tensor memory; one lane issues tcgen05.mma (M = 128, N = n_out, K = 16, four per block)
 //               on the u tile and the W_x tile and commits to the barriers that free them.
-//   warps 2..9  conv + SiLU: a thread owns two adjacent channels and 16 steps, slides its 4-tap window down the
-//               x box and writes bf16 pairs into the u tile in the 128-byte-swizzled K-major layout the tensor core
+//   warps 2..9  conv + SiLU: a thread owns two adjacent channels and 16 steps (8 with 64-step tiles), loads its rows
+//               of the x box, slides the 4-tap window down them and writes bf16 pairs into the u tile in the 128-byte-swizzled K-major layout the tensor core
 //               reads.  The same tile then leaves for global memory with one TMA store.  After the last block
 //               four of these warps drain the accumulator: tcgen05.ld, bf16, 16-byte stores of the x_dbl rows.
-// Two CTAs fit an SM (105 KB of shared memory, 128 columns of tensor memory each), so one CTA's loads and stores
-// run under the other's arithmetic.  The arithmetic of u is that of the strip kernel of elementwise.cu, so u is
+// Two CTAs fit an SM (105 KB of shared memory, 128 columns of tensor memory each; three with 64-step tiles), so one
+// CTA's loads and stores run under the other's arithmetic.  The arithmetic of u is that of the strip kernel of elementwise.cu, so u is
 // bit-identical to it; x_dbl accumulates in fp32 over ascending k like the tcgen05 GEMM.
 // Every wait is bounded; a wait that runs out raises the status word, the CTA drains, frees its tensor memory and
 // returns.
